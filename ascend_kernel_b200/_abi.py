@@ -1,0 +1,82 @@
+"""ctypes binding of the C ABI declared in ``include/b200moe.h``.
+
+The shared library is the product; there is no fallback.  If ``libb200moe.so`` is missing the
+import fails with instructions to build it, and every call raises when the library reports an
+error status.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200moe.so")
+
+# enums of include/b200moe.h
+CT = {"fp8": 0, "fp4": 1, "int8": 2, "int4": 3}
+GROUP_LIST_CUMSUM, GROUP_LIST_COUNTS = 0, 1
+LAYOUT = {"canonical": 0, "ascend": 1}
+FP4_SCALE_NONE, FP4_SCALE_E8M0_PER32 = 0, 1
+STATUS_BYTES = 256
+
+EXPORTS = [
+    "b200moe_grouped_gemm", "b200moe_grouped_gemm_workspace_bytes", "b200moe_grouped_gemv",
+    "b200moe_grouped_gemv_workspace_bytes", "b200moe_fp4_dequant", "b200moe_fp4_layout", "b200moe_silu_mul",
+    "b200moe_gather_rows", "b200moe_combine", "b200moe_read_status", "b200moe_strerror", "b200moe_version",
+]
+
+
+class B200MoeError(RuntimeError):
+    def __init__(self, code: int, what: str):
+        super().__init__(f"{what}: {strerror(code)} (status {code})")
+        self.code = code
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m ascend_kernel_b200.build` "
+            "(there is no CPU or PyTorch fallback for these operators)")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i64, i32, sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+    gemm_args = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, i32, vp, sz, vp]
+    lib.b200moe_grouped_gemm.argtypes = gemm_args
+    lib.b200moe_grouped_gemm.restype = i32
+    lib.b200moe_grouped_gemv.argtypes = gemm_args
+    lib.b200moe_grouped_gemv.restype = i32
+    for f in (lib.b200moe_grouped_gemm_workspace_bytes, lib.b200moe_grouped_gemv_workspace_bytes):
+        f.argtypes = [i64, i64, i64, i64, i32, i32]
+        f.restype = sz
+    lib.b200moe_fp4_dequant.argtypes = [vp, vp, vp, i64, i32, vp]
+    lib.b200moe_fp4_dequant.restype = i32
+    lib.b200moe_fp4_layout.argtypes = [vp, vp, i64, i64, i64, i32, vp]
+    lib.b200moe_fp4_layout.restype = i32
+    lib.b200moe_silu_mul.argtypes = [vp, vp, i64, i64, vp]
+    lib.b200moe_silu_mul.restype = i32
+    lib.b200moe_gather_rows.argtypes = [vp, vp, vp, i64, i64, vp]
+    lib.b200moe_gather_rows.restype = i32
+    lib.b200moe_combine.argtypes = [vp, vp, vp, vp, i64, i64, i64, vp]
+    lib.b200moe_combine.restype = i32
+    lib.b200moe_read_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
+    lib.b200moe_read_status.restype = i32
+    lib.b200moe_strerror.argtypes = [i32]
+    lib.b200moe_strerror.restype = ctypes.c_char_p
+    lib.b200moe_version.argtypes = []
+    lib.b200moe_version.restype = ctypes.c_char_p
+    return lib
+
+
+lib = _load()
+
+
+def strerror(code: int) -> str:
+    return lib.b200moe_strerror(int(code)).decode()
+
+
+def version() -> str:
+    return lib.b200moe_version().decode()
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise B200MoeError(code, what)

@@ -1,0 +1,482 @@
+// Antiquant grouped GEMM for prefill-sized expert batches: persistent, warp-specialised
+// tcgen05 / TMEM kernel fed by TMA (sm_100a).
+//
+//   y[rows of expert g] = bf16( x[rows of expert g] @ dequant(W[g]) ),  fp32 accumulation in TMEM.
+//
+// One CTA per SM walks a static round-robin over output tiles of 128 rows x 256 columns.  The
+// tile list is derived inside the kernel from the device-side group_list (prefix sum over the
+// experts' tile counts kept in shared memory, binary search per tile), so there is no host
+// synchronisation and no schedule in global memory.
+//
+// Warp roles (16 warps):
+//   warp 0      TMA producer of x tiles      (128 rows x 64 k, bf16, 128-byte swizzle, K-major A)
+//   warp 1      TMA producer of packed weight tiles (64 k x 256 n bytes / nibbles, as stored)
+//   warp 2      TMEM allocation + tcgen05.mma issue (one elected lane), UMMA 128x256x16
+//   warps 4-7   epilogue: tcgen05.ld of the accumulator, scale/offset in fp32, bf16 stores
+//   warps 8-15  dequant: packed tile -> bf16 tile in the UMMA MN-major 128-byte-swizzle layout
+// Rings: 4 x-tile stages, 3 packed stages, 3 bf16 weight stages, 2 accumulators of 256 TMEM columns
+// (the epilogue of tile i overlaps the main loop of tile i+1).  Weights never make a round trip
+// through global memory.  Every wait is bounded; on expiry the kernel records an error status,
+// all roles wind down, copies in flight are given time to land and TMEM is released.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200moe {
+
+constexpr int kBM = 128, kBN = 256, kBK = 64;
+constexpr int kNA = 4, kNP = 3, kNB = 3;
+constexpr int kGemmThreads = 512;
+constexpr int kWarpA = 0, kWarpP = 1, kWarpMma = 2, kWarpEpi0 = 4, kWarpDq0 = 8;
+constexpr int kDqWarps = 8;
+constexpr int kSuperRows = 16;  // m-tiles per L2 super-tile
+constexpr int kATileBytes = kBM * kBK * 2;
+constexpr int kBTileBytes = kBK * kBN * 2;
+constexpr uint32_t kTmemCols = 512;
+
+struct GemmArgs {
+    const void* scale;
+    const __nv_bfloat16* offset;
+    const float* rowsum;  // [M] sum_k x[m,k]; only read when offset != nullptr
+    const int64_t* group_list;
+    __nv_bfloat16* y;
+    int M, K, N, G, gl_type;
+    int* status;
+};
+
+template <int MODE>
+struct GmTraits {
+    static constexpr bool kNibbles = (MODE == B200MOE_CT_FP4 || MODE == B200MOE_CT_INT4);
+    static constexpr int kPRowBytes = kNibbles ? kBN / 2 : kBN;
+    static constexpr int kPTileBytes = kPRowBytes * kBK;
+};
+
+struct GmBarriers {
+    uint64_t a_full[kNA], a_empty[kNA];
+    uint64_t p_full[kNP], p_empty[kNP];
+    uint64_t b_full[kNB], b_empty[kNB];
+    uint64_t t_full[2], t_empty[2];
+    uint64_t drain;
+    uint32_t tmem_base;
+    int abort;
+    int n_tiles;
+};
+
+struct TileInfo {
+    int g, row0, row_end, n0;
+};
+
+__device__ __forceinline__ bool gm_wait(uint64_t* bar, uint32_t parity, GmBarriers* sb, int* status, int id) {
+    if (*reinterpret_cast<volatile int*>(&sb->abort)) return false;
+    if (ptx::mbar_wait(ptx::smem_u32(bar), parity)) return true;
+    *reinterpret_cast<volatile int*>(&sb->abort) = 1;
+    if (status != nullptr) {
+        atomicCAS(status, kDevOk, kDevWaitExpired);
+        status[1] = id;
+    }
+    return false;
+}
+
+// tile index -> expert, first row, row bound, first column.  tile_prefix has G+1 entries.
+__device__ __forceinline__ TileInfo locate_tile(int t, const int* tile_prefix, const int* row_start, int G, int n_nt) {
+    int lo = 0, hi = G;  // largest g with tile_prefix[g] <= t
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tile_prefix[mid] <= t) lo = mid;
+        else hi = mid;
+    }
+    const int g = lo;
+    const int j = t - tile_prefix[g];
+    const int r0 = row_start[g], r1 = row_start[g + 1];
+    const int mt = (r1 - r0 + kBM - 1) / kBM;
+    // super-tiles of up to kSuperRows m-tiles x all n-tiles keep x rows and the expert's weights
+    // L2-resident while they are shared by concurrently running CTAs
+    const int per_super = kSuperRows * n_nt;
+    const int st = j / per_super;
+    const int base = st * kSuperRows;
+    const int h = min(kSuperRows, mt - base);
+    const int jj = j - st * per_super;
+    TileInfo ti;
+    ti.g = g;
+    ti.n0 = (jj / h) * kBN;
+    ti.row0 = r0 + (base + jj % h) * kBM;
+    ti.row_end = r1;
+    return ti;
+}
+
+// ---- dequant of one packed stage into the bf16 UMMA tile --------------------------------------
+// bf16 tile layout (MN-major, 128-byte swizzle): four blocks of 64 columns; inside a block row k
+// occupies 128 bytes at k*128 and its eight 16-byte chunks are XOR-swizzled with (k & 7).
+__device__ __forceinline__ uint32_t btile_offset(int k, int nchunk16) {  // nchunk16: 16-byte chunk 0..31
+    return (uint32_t)((nchunk16 >> 3) * (kBK * 128) + k * 128 + (((nchunk16 & 7) ^ (k & 7)) << 4));
+}
+
+template <int MODE>
+__device__ __forceinline__ void dequant_stage(const uint8_t* pt, uint8_t* bt, const GemmArgs& a, const TileInfo& ti,
+                                              int kt, int tid) {
+    using T = GmTraits<MODE>;
+    const int c16 = tid & 15;   // 16 output columns c16*16 .. c16*16+15
+    const int rbase = tid >> 4; // rows rbase + 16 j
+    float sf = 1.f;
+    if constexpr (MODE == B200MOE_CT_FP8) {
+        sf = __ldg(static_cast<const float*>(a.scale) +
+                   ((size_t)ti.g * (a.K >> 7) + ((kt * kBK) >> 7)) * (a.N >> 7) + ((ti.n0 + c16 * 16) >> 7));
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int k = rbase + 16 * j;
+        uint32_t o[8];
+        if constexpr (MODE == B200MOE_CT_INT8) {
+            const uint4 q = *reinterpret_cast<const uint4*>(pt + k * T::kPRowBytes + c16 * 16);
+            s8x4_to_bf16(q.x, o[0], o[1]);
+            s8x4_to_bf16(q.y, o[2], o[3]);
+            s8x4_to_bf16(q.z, o[4], o[5]);
+            s8x4_to_bf16(q.w, o[6], o[7]);
+        } else if constexpr (MODE == B200MOE_CT_FP8) {
+            const uint4 q = *reinterpret_cast<const uint4*>(pt + k * T::kPRowBytes + c16 * 16);
+            const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float f[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const uint32_t p = prmt(w4[i], 0u, 0x0444u | (b << 12));
+                    const uint32_t d = ((p >> 4) & 0x07F00000u) | (p & 0x80000000u);
+                    f[b] = (__uint_as_float(d) * 1.329227995784916e36f) * sf;  // exact * 2^120, then fp32 scale
+                }
+                o[2 * i] = pack_bf16x2(f[0], f[1]);
+                o[2 * i + 1] = pack_bf16x2(f[2], f[3]);
+            }
+        } else {  // FP4: 8 bytes = 16 codes, bf16 scale per 16 k rows per column
+            const uint2 q = *reinterpret_cast<const uint2*>(pt + k * T::kPRowBytes + c16 * 8);
+            const uint4* sp = reinterpret_cast<const uint4*>(
+                static_cast<const __nv_bfloat16*>(a.scale) +
+                ((size_t)ti.g * (a.K >> 4) + ((kt * kBK + k) >> 4)) * a.N + ti.n0 + c16 * 16);
+            const uint4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
+            uint32_t v[4];
+            e2m1x8_to_bf16(q.x, v);
+            o[0] = mul_bf16x2(v[0], s0.x); o[1] = mul_bf16x2(v[1], s0.y);
+            o[2] = mul_bf16x2(v[2], s0.z); o[3] = mul_bf16x2(v[3], s0.w);
+            e2m1x8_to_bf16(q.y, v);
+            o[4] = mul_bf16x2(v[0], s1.x); o[5] = mul_bf16x2(v[1], s1.y);
+            o[6] = mul_bf16x2(v[2], s1.z); o[7] = mul_bf16x2(v[3], s1.w);
+        }
+        *reinterpret_cast<uint4*>(bt + btile_offset(k, 2 * c16)) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(bt + btile_offset(k, 2 * c16 + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                    const GemmArgs a) {
+    using T = GmTraits<MODE>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* a_ring = base;
+    uint8_t* b_ring = a_ring + kNA * kATileBytes;
+    uint8_t* p_ring = b_ring + kNB * kBTileBytes;
+    GmBarriers* sb = reinterpret_cast<GmBarriers*>(p_ring + kNP * T::kPTileBytes);
+    int* row_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sb) + 256);
+    int* tile_prefix = row_start + (a.G + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_nt = a.N / kBN;
+    const int n_kt = a.K / kBK;
+
+    load_row_starts(a.group_list, a.G, a.M, a.gl_type, row_start, a.status);
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        tile_prefix[0] = 0;
+        for (int g = 0; g < a.G; ++g) {
+            acc += ((row_start[g + 1] - row_start[g] + kBM - 1) / kBM) * n_nt;
+            tile_prefix[g + 1] = acc;
+        }
+        sb->n_tiles = acc;
+        sb->abort = 0;
+        for (int i = 0; i < kNA; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->a_full[i]), 1); ptx::mbar_init(ptx::smem_u32(&sb->a_empty[i]), 1); }
+        for (int i = 0; i < kNP; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->p_full[i]), 1); ptx::mbar_init(ptx::smem_u32(&sb->p_empty[i]), kDqWarps); }
+        for (int i = 0; i < kNB; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->b_full[i]), kDqWarps); ptx::mbar_init(ptx::smem_u32(&sb->b_empty[i]), 1); }
+        for (int i = 0; i < 2; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->t_full[i]), 1); ptx::mbar_init(ptx::smem_u32(&sb->t_empty[i]), 4); }
+        ptx::mbar_init(ptx::smem_u32(&sb->drain), 1);
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_x);
+        ptx::prefetch_tensormap(&tmap_w);
+    }
+    if (warp == kWarpMma) {
+        ptx::tmem_alloc(ptx::smem_u32(&sb->tmem_base), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+
+    const int n_tiles = sb->n_tiles;
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&sb->tmem_base);
+
+    if (warp == kWarpA) {
+        // ------------------------------ x-tile producer ------------------------------
+        if (lane == 0) {
+            uint32_t ia = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
+                for (int kt = 0; kt < n_kt; ++kt, ++ia) {
+                    const uint32_t s = ia % kNA, ph = (ia / kNA) & 1;
+                    if (ia >= kNA && !gm_wait(&sb->a_empty[s], ph ^ 1, sb, a.status, 10 + (int)s)) { ok = false; break; }
+                    const uint32_t bar = ptx::smem_u32(&sb->a_full[s]);
+                    ptx::mbar_arrive_expect_tx(bar, kATileBytes);
+                    ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes), &tmap_x, bar, kt * kBK, ti.row0);
+                }
+            }
+            if (!ok)
+                for (uint32_t j = (ia > kNA ? ia - kNA : 0); j < ia; ++j)
+                    (void)ptx::mbar_wait(ptx::smem_u32(&sb->a_full[j % kNA]), (j / kNA) & 1);
+        }
+    } else if (warp == kWarpP) {
+        // ------------------------------ packed-weight producer ------------------------------
+        if (lane == 0) {
+            uint32_t ip = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
+                for (int kt = 0; kt < n_kt; ++kt, ++ip) {
+                    const uint32_t s = ip % kNP, ph = (ip / kNP) & 1;
+                    if (ip >= kNP && !gm_wait(&sb->p_empty[s], ph ^ 1, sb, a.status, 20 + (int)s)) { ok = false; break; }
+                    const uint32_t bar = ptx::smem_u32(&sb->p_full[s]);
+                    ptx::mbar_arrive_expect_tx(bar, T::kPTileBytes);
+                    ptx::tma_load_2d(ptx::smem_u32(p_ring + s * T::kPTileBytes), &tmap_w, bar,
+                                     T::kNibbles ? ti.n0 / 2 : ti.n0, ti.g * a.K + kt * kBK);
+                }
+            }
+            if (!ok)
+                for (uint32_t j = (ip > kNP ? ip - kNP : 0); j < ip; ++j)
+                    (void)ptx::mbar_wait(ptx::smem_u32(&sb->p_full[j % kNP]), (j / kNP) & 1);
+        }
+    } else if (warp == kWarpMma) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = ptx::umma_idesc_bf16(kBM, kBN, true);
+            uint32_t ia = 0, ib = 0, it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++it) {
+                const uint32_t ab = it & 1, pht = (it >> 1) & 1;
+                if (it >= 2 && !gm_wait(&sb->t_empty[ab], pht ^ 1, sb, a.status, 30 + (int)ab)) { ok = false; break; }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + ab * kBN;
+                for (int kt = 0; kt < n_kt; ++kt, ++ia, ++ib) {
+                    const uint32_t sa = ia % kNA, pha = (ia / kNA) & 1;
+                    const uint32_t sbb = ib % kNB, phb = (ib / kNB) & 1;
+                    if (!gm_wait(&sb->a_full[sa], pha, sb, a.status, 40 + (int)sa)) { ok = false; break; }
+                    if (!gm_wait(&sb->b_full[sbb], phb, sb, a.status, 50 + (int)sbb)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t a_addr = ptx::smem_u32(a_ring + sa * kATileBytes);
+                    const uint32_t b_addr = ptx::smem_u32(b_ring + sbb * kBTileBytes);
+#pragma unroll
+                    for (int k16 = 0; k16 < kBK / 16; ++k16) {
+                        // A: K-major, 8-row groups 1024 B apart, 32 B per 16 k inside the swizzle atom
+                        const uint64_t da = ptx::umma_desc_sw128(a_addr + k16 * 32, 0, 1024);
+                        // B: MN-major, 64-column blocks kBK*128 B apart (LBO), 8-k groups 1024 B apart (SBO)
+                        const uint64_t db = ptx::umma_desc_sw128(b_addr + k16 * 2048, kBK * 128, 1024);
+                        ptx::umma_bf16(d_tmem, da, db, idesc, (kt > 0 || k16 > 0) ? 1u : 0u);
+                    }
+                    ptx::umma_commit(ptx::smem_u32(&sb->a_empty[sa]));
+                    ptx::umma_commit(ptx::smem_u32(&sb->b_empty[sbb]));
+                }
+                if (ok) ptx::umma_commit(ptx::smem_u32(&sb->t_full[ab]));
+            }
+            // drain: every issued MMA must have completed before TMEM is released
+            ptx::umma_commit(ptx::smem_u32(&sb->drain));
+            (void)ptx::mbar_wait(ptx::smem_u32(&sb->drain), 0);
+        }
+        __syncwarp();
+    } else if (warp >= kWarpEpi0 && warp < kWarpEpi0 + 4) {
+        // ------------------------------ epilogue ------------------------------
+        const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
+        const bool per_channel = (MODE == B200MOE_CT_INT8);
+        const bool has_offset = per_channel && a.offset != nullptr;
+        uint32_t it = 0;
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++it) {
+            const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
+            const uint32_t ab = it & 1, pht = (it >> 1) & 1;
+            if (!__all_sync(0xffffffffu, gm_wait(&sb->t_full[ab], pht, sb, a.status, 60 + (int)ab))) break;
+            ptx::tc_fence_after();
+            const int row = ti.row0 + quarter * 32 + lane;
+            const bool row_ok = row < ti.row_end;
+            const float rs = (has_offset && row_ok) ? __ldg(a.rowsum + row) : 0.f;
+            __nv_bfloat16* yrow = a.y + (size_t)row * a.N + ti.n0;
+#pragma unroll 1
+            for (int c = 0; c < kBN / 32; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(tmem_base + ab * kBN + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
+                float sv = 1.f, sov = 0.f;
+                if (per_channel) {
+                    const size_t ci = (size_t)ti.g * a.N + ti.n0 + c * 32 + lane;
+                    sv = __bfloat162float(static_cast<const __nv_bfloat16*>(a.scale)[ci]);
+                    if (has_offset) sov = sv * __bfloat162float(a.offset[ci]);
+                }
+                ptx::tmem_ld_wait();
+                uint32_t o[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
+                    if (per_channel) {
+                        const float s0 = __shfl_sync(0xffffffffu, sv, 2 * j), s1 = __shfl_sync(0xffffffffu, sv, 2 * j + 1);
+                        const float so0 = __shfl_sync(0xffffffffu, sov, 2 * j), so1 = __shfl_sync(0xffffffffu, sov, 2 * j + 1);
+                        v0 = fmaf(so0, rs, s0 * v0);
+                        v1 = fmaf(so1, rs, s1 * v1);
+                    }
+                    o[j] = pack_bf16x2(v0, v1);
+                }
+                if (row_ok) {
+                    uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) dst[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->t_empty[ab]));
+        }
+    } else if (warp >= kWarpDq0) {
+        // ------------------------------ dequant ------------------------------
+        const int tid = threadIdx.x - kWarpDq0 * 32;
+        uint32_t ip = 0, ib = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
+            for (int kt = 0; kt < n_kt; ++kt, ++ip, ++ib) {
+                const uint32_t sp = ip % kNP, php = (ip / kNP) & 1;
+                const uint32_t sbb = ib % kNB, phb = (ib / kNB) & 1;
+                bool got = gm_wait(&sb->p_full[sp], php, sb, a.status, 70 + (int)sp);
+                if (got && ib >= kNB) got = gm_wait(&sb->b_empty[sbb], phb ^ 1, sb, a.status, 80 + (int)sbb);
+                if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+                dequant_stage<MODE>(p_ring + sp * T::kPTileBytes, b_ring + sbb * kBTileBytes, a, ti, kt, tid);
+                ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(ptx::smem_u32(&sb->b_full[sbb]));
+                    ptx::mbar_arrive(ptx::smem_u32(&sb->p_empty[sp]));
+                }
+            }
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == kWarpMma) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// Row sums of x in fp32 (the offset term of the int8 epilogue): one warp per row.
+__global__ void rowsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int M, int K) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= M) return;
+    const uint4* p = reinterpret_cast<const uint4*>(x + (size_t)row * K);
+    float s = 0.f;
+    for (int i = threadIdx.x & 31; i < K / 8; i += 32) {
+        const uint4 q = __ldg(p + i);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s += __uint_as_float(w[j] << 16) + __uint_as_float(w[j] & 0xFFFF0000u);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) out[row] = s;
+}
+
+template <int MODE>
+static size_t gm_smem_bytes(int G) {
+    using T = GmTraits<MODE>;
+    return 1024 + (size_t)kNA * kATileBytes + (size_t)kNB * kBTileBytes + (size_t)kNP * T::kPTileBytes + 256 +
+           sizeof(int) * 2 * (size_t)(G + 1);
+}
+
+template <int MODE>
+static int gm_launch(const void* x, const void* w, const GemmArgs& a, cudaStream_t stream) {
+    using T = GmTraits<MODE>;
+    CUtensorMap tx, tw;
+    int rc = make_tensor_map_2d(&tx, x, 2, (uint64_t)a.M, a.K, kBM, kBK, true);
+    if (rc != B200MOE_OK) return rc;
+    rc = make_tensor_map_2d(&tw, w, 1, (uint64_t)a.G * a.K, T::kNibbles ? a.N / 2 : a.N, kBK, T::kPRowBytes, false);
+    if (rc != B200MOE_OK) return rc;
+    const size_t smem = gm_smem_bytes<MODE>(a.G);
+    B200MOE_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)smem));
+    grouped_gemm_kernel<MODE><<<sm_count(), kGemmThreads, smem, stream>>>(tx, tw, a);
+    B200MOE_CUDA_TRY(cudaGetLastError());
+    return B200MOE_OK;
+}
+
+static size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" size_t b200moe_grouped_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t G, int compute_type,
+                                                       int weight_layout) {
+    size_t b = B200MOE_STATUS_BYTES;
+    if (compute_type == B200MOE_CT_INT8 || compute_type == B200MOE_CT_INT4) b += align256((size_t)M * sizeof(float));
+    if (compute_type == B200MOE_CT_FP4 && weight_layout == B200MOE_LAYOUT_ASCEND)
+        b += (size_t)G * (size_t)K * (size_t)(N / 2);
+    return b;
+}
+
+extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const void* scale, const void* offset,
+                                    const int64_t* group_list, void* y, int64_t M, int64_t K, int64_t N, int64_t G,
+                                    int compute_type, int group_list_type, int weight_layout, void* workspace,
+                                    size_t workspace_bytes, void* stream) {
+    if (compute_type < B200MOE_CT_FP8 || compute_type > B200MOE_CT_INT4) return B200MOE_ERR_COMPUTE_TYPE;
+    if (group_list_type != B200MOE_GROUP_LIST_CUMSUM && group_list_type != B200MOE_GROUP_LIST_COUNTS)
+        return B200MOE_ERR_ARGUMENT;
+    if (weight_layout != B200MOE_LAYOUT_CANONICAL && weight_layout != B200MOE_LAYOUT_ASCEND)
+        return B200MOE_ERR_ARGUMENT;
+    if (M < 0 || K <= 0 || N <= 0 || G <= 0 || G > kMaxExperts || M > 0x7FFFFFF0LL || K > 0x7FFFFFF0LL ||
+        N > 0x7FFFFFF0LL || G * K > 0x7FFFFFF0LL)
+        return B200MOE_ERR_SHAPE;
+    if ((K % kBK) != 0 || (N % kBN) != 0) return B200MOE_ERR_SHAPE;
+    if (compute_type == B200MOE_CT_FP8 && (K % 128) != 0) return B200MOE_ERR_SHAPE;
+    if (compute_type == B200MOE_CT_INT4) return B200MOE_ERR_UNSUPPORTED;
+    if (M == 0) return B200MOE_OK;
+    if (!x || !weight || !scale || !group_list || !y) return B200MOE_ERR_NULL_POINTER;
+    if (!aligned16(x) || !aligned16(weight) || !aligned16(scale) || !aligned16(y) || (offset && !aligned16(offset)))
+        return B200MOE_ERR_ALIGNMENT;
+    const size_t need = b200moe_grouped_gemm_workspace_bytes(M, K, N, G, compute_type, weight_layout);
+    if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return B200MOE_ERR_WORKSPACE;
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    B200MOE_CUDA_TRY(cudaMemsetAsync(workspace, 0, 16, s));
+    uint8_t* ws = static_cast<uint8_t*>(workspace) + B200MOE_STATUS_BYTES;
+    GemmArgs a;
+    a.scale = scale;
+    a.offset = nullptr;
+    a.rowsum = nullptr;
+    a.group_list = group_list;
+    a.y = static_cast<__nv_bfloat16*>(y);
+    a.M = (int)M; a.K = (int)K; a.N = (int)N; a.G = (int)G;
+    a.gl_type = group_list_type;
+    a.status = static_cast<int*>(workspace);
+
+    if (compute_type == B200MOE_CT_INT8) {
+        float* rowsum = reinterpret_cast<float*>(ws);
+        ws += align256((size_t)M * sizeof(float));
+        if (offset != nullptr) {
+            rowsum_kernel<<<(unsigned)((M + 7) / 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rowsum, (int)M,
+                                                                   (int)K);
+            B200MOE_CUDA_TRY(cudaGetLastError());
+            a.offset = static_cast<const __nv_bfloat16*>(offset);
+            a.rowsum = rowsum;
+        }
+        return gm_launch<B200MOE_CT_INT8>(x, weight, a, s);
+    }
+    if (compute_type == B200MOE_CT_FP8) return gm_launch<B200MOE_CT_FP8>(x, weight, a, s);
+    const void* w = weight;
+    if (weight_layout == B200MOE_LAYOUT_ASCEND) {
+        int rc = b200moe_fp4_layout(weight, ws, G, K, N, 0, stream);
+        if (rc != B200MOE_OK) return rc;
+        w = ws;
+    }
+    return gm_launch<B200MOE_CT_FP4>(x, w, a, s);
+}

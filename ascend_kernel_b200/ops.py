@@ -1,0 +1,179 @@
+"""Python mirror of the reference's operator interface over the C ABI (torch is used only for
+device memory and the current stream).
+
+``grouped_gemm`` / ``grouped_soft_gemv`` keep the keyword names of the reference's pybind module
+(pybind.cpp:14-19 of the reference); outputs are caller-allocated and written in place, launches
+are asynchronous on torch's current stream.  Trailing keywords (defaulted, so existing calls are
+unchanged) select per-expert counts instead of cumulative sums and the canonical FP4 layout.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _abi
+from ._abi import CT, LAYOUT
+
+_lib = _abi.lib
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(**tensors):
+    for name, t in tensors.items():
+        if t is None:
+            continue
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor (there is no CPU path)")
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+
+
+def _compute_type(computeType: str) -> int:
+    if computeType not in CT:
+        # the reference reports an unknown computeType this way (grouped_gemm.cpp:10-16,129-133)
+        print(f'Invalid compute type: {computeType}. Supported: "fp4", "fp8", "int8", "int4"')
+        raise RuntimeError("Host tiling failed!")
+    return CT[computeType]
+
+
+def _check_common(x, weight, group_list, output, ct):
+    if x.dtype != torch.bfloat16 or output.dtype != torch.bfloat16:
+        raise RuntimeError("x and output must be bfloat16")
+    if group_list.dtype != torch.int64:
+        raise RuntimeError("group_list must be int64")
+    if x.dim() != 2 or weight.dim() != 3 or output.dim() != 2:
+        raise RuntimeError("expected x [M,K], weight [G,K,N(/2)], output [M,N]")
+    if weight.element_size() != 1:
+        raise RuntimeError("weight must be a 1-byte container (uint8 / int8)")
+    M, K = x.shape
+    G, Kw, Nw = weight.shape
+    N = Nw * 2 if ct in (CT["fp4"], CT["int4"]) else Nw
+    if Kw != K or tuple(output.shape) != (M, N) or group_list.numel() != G:
+        raise RuntimeError(f"shape mismatch: x {tuple(x.shape)}, weight {tuple(weight.shape)}, "
+                           f"output {tuple(output.shape)}, group_list {group_list.numel()}")
+    return M, K, N, G
+
+
+def _check_scale(scale, ct, G, K, N, what):
+    want = {CT["fp8"]: ((G, K // 128, N // 128), torch.float32), CT["fp4"]: ((G, K // 16, N), torch.bfloat16),
+            CT["int8"]: ((G, N), torch.bfloat16), CT["int4"]: ((G, K // 128, N), torch.bfloat16)}[ct]
+    if tuple(scale.shape) != want[0] or scale.dtype != want[1]:
+        raise RuntimeError(f"{what} must be {want[1]} of shape {want[0]}, got {scale.dtype} {tuple(scale.shape)}")
+
+
+def _run(fn, ws_fn, what, x, weight, scale, offset, group_list, output, ct, group_list_type, layout, M, K, N, G):
+    need = ws_fn(M, K, N, G, ct, layout)
+    ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = fn(_ptr(x), _ptr(weight), _ptr(scale), _ptr(offset), _ptr(group_list), _ptr(output), M, K, N, G, ct,
+                group_list_type, layout, _ptr(ws), need, _stream())
+    _abi.check(rc, what)
+    return ws
+
+
+def grouped_gemm(x, weight, antiquantScaleOptional, antiquantOffsetOptional, groupListOptional, computeType,
+                 output, group_list_type: int = 0, weight_layout: str = "ascend", return_workspace: bool = False):
+    """output[rows of expert g] = bf16(x[rows of expert g] @ dequant(weight[g])).  Returns None
+    (or the workspace tensor holding the device status words when ``return_workspace``)."""
+    ct = _compute_type(computeType)
+    _need_cuda(x=x, weight=weight, scale=antiquantScaleOptional, offset=antiquantOffsetOptional,
+               group_list=groupListOptional, output=output)
+    M, K, N, G = _check_common(x, weight, groupListOptional, output, ct)
+    _check_scale(antiquantScaleOptional, ct, G, K, N, "antiquantScaleOptional")
+    offset = antiquantOffsetOptional if ct in (CT["int8"], CT["int4"]) else None  # ignored for fp8/fp4
+    if offset is not None:
+        _check_scale(offset, ct, G, K, N, "antiquantOffsetOptional")
+    ws = _run(_lib.b200moe_grouped_gemm, _lib.b200moe_grouped_gemm_workspace_bytes, "grouped_gemm", x, weight,
+              antiquantScaleOptional, offset, groupListOptional, output, ct, group_list_type,
+              LAYOUT[weight_layout], M, K, N, G)
+    return ws if return_workspace else None
+
+
+def grouped_soft_gemv(x, weight, scale, groupList, computeType, output, group_list_type: int = 0,
+                      weight_layout: str = "ascend", offset=None, return_workspace: bool = False):
+    ct = _compute_type(computeType)
+    _need_cuda(x=x, weight=weight, scale=scale, offset=offset, group_list=groupList, output=output)
+    M, K, N, G = _check_common(x, weight, groupList, output, ct)
+    _check_scale(scale, ct, G, K, N, "scale")
+    if offset is not None:
+        if ct not in (CT["int8"], CT["int4"]):
+            raise RuntimeError("offset is only defined for int8 / int4")
+        _check_scale(offset, ct, G, K, N, "offset")
+    ws = _run(_lib.b200moe_grouped_gemv, _lib.b200moe_grouped_gemv_workspace_bytes, "grouped_soft_gemv", x, weight,
+              scale, offset, groupList, output, ct, group_list_type, LAYOUT[weight_layout], M, K, N, G)
+    return ws if return_workspace else None
+
+
+def fp4_dequant(codes, scale, output):
+    """codes: uint8/int8 [..., L/2]; scale: uint8 e8m0 [..., L/32] or None; output bf16 [..., L]."""
+    _need_cuda(codes=codes, scale=scale, output=output)
+    n = codes.numel() * 2
+    if output.dtype != torch.bfloat16 or output.numel() != n:
+        raise RuntimeError("output must be bfloat16 with twice as many elements as codes has bytes")
+    if scale is not None and (scale.element_size() != 1 or scale.numel() * 32 != n):
+        raise RuntimeError("scale must hold one e8m0 byte per 32 elements")
+    with torch.cuda.device(codes.device):
+        rc = _lib.b200moe_fp4_dequant(_ptr(codes), _ptr(scale), _ptr(output), n,
+                                      _abi.FP4_SCALE_NONE if scale is None else _abi.FP4_SCALE_E8M0_PER32, _stream())
+    _abi.check(rc, "fp4_dequant")
+
+
+def fp4_layout(src, to_ascend: bool):
+    """[G,K,N/2] packed FP4 weights between the canonical and the stored ("ascend") order."""
+    _need_cuda(src=src)
+    G, K, C = src.shape
+    dst = torch.empty_like(src)
+    with torch.cuda.device(src.device):
+        rc = _lib.b200moe_fp4_layout(_ptr(src), _ptr(dst), G, K, 2 * C, int(bool(to_ascend)), _stream())
+    _abi.check(rc, "fp4_layout")
+    return dst
+
+
+def silu_mul(h, out=None):
+    _need_cuda(h=h, out=out)
+    rows, two_i = h.shape
+    if out is None:
+        out = torch.empty(rows, two_i // 2, dtype=torch.bfloat16, device=h.device)
+    with torch.cuda.device(h.device):
+        rc = _lib.b200moe_silu_mul(_ptr(h), _ptr(out), rows, two_i // 2, _stream())
+    _abi.check(rc, "silu_mul")
+    return out
+
+
+def gather_rows(src, index, out=None):
+    _need_cuda(src=src, index=index, out=out)
+    if index.dtype != torch.int32:
+        raise RuntimeError("index must be int32")
+    if out is None:
+        out = torch.empty(index.numel(), src.shape[1], dtype=src.dtype, device=src.device)
+    with torch.cuda.device(src.device):
+        rc = _lib.b200moe_gather_rows(_ptr(src), _ptr(index), _ptr(out), index.numel(), src.shape[1], _stream())
+    _abi.check(rc, "gather_rows")
+    return out
+
+
+def combine(y, slot, weight, out=None):
+    _need_cuda(y=y, slot=slot, weight=weight, out=out)
+    if slot.dtype != torch.int32 or weight.dtype != torch.float32:
+        raise RuntimeError("slot must be int32 and weight float32")
+    T, top_k = slot.shape
+    if out is None:
+        out = torch.empty(T, y.shape[1], dtype=torch.bfloat16, device=y.device)
+    with torch.cuda.device(y.device):
+        rc = _lib.b200moe_combine(_ptr(y), _ptr(slot), _ptr(weight), _ptr(out), T, top_k, y.shape[1], _stream())
+    _abi.check(rc, "combine")
+    return out
+
+
+def read_status(ws):
+    import ctypes
+
+    out = (ctypes.c_int32 * 2)()
+    _abi.check(_lib.b200moe_read_status(_ptr(ws), out, _stream()), "read_status")
+    return int(out[0]), int(out[1])

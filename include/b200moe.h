@@ -1,0 +1,128 @@
+/*
+ * b200moe.h -- C ABI of the B200 (sm_100a) MoE expert-GEMM hot path.
+ *
+ * Drop-in boundary for the three operators the chitu engine calls through the reference's
+ * `cinfer_ascendc` extension.  Every entry point takes plain device pointers and sizes, launches
+ * asynchronously on the given CUDA stream (a `cudaStream_t` passed as `void*`; NULL = default
+ * stream), never synchronises, never allocates device memory (the caller passes a workspace),
+ * and returns 0 on success or a B200MOE_ERR_* code when the arguments are rejected (nothing is
+ * launched in that case).  Outputs are caller-allocated and written in place; output rows owned
+ * by no expert are left untouched, exactly as the reference operators do.
+ *
+ * Reference interfaces replaced (paths inside the reference project):
+ *   b200moe_grouped_gemm       grouped_gemm/src/grouped_gemm.h:12-16 (GroupedGemm), which calls
+ *                              aclnnGroupedMatmulAntiquantGetWorkspaceSize + aclnnGroupedMatmulAntiquant
+ *                              (grouped_gemm/src/grouped_gemm.cpp:145-159); python name
+ *                              `grouped_gemm` in pybind.cpp:17-19
+ *   b200moe_grouped_gemm_workspace_bytes
+ *                              the workspace half of that two-phase call
+ *                              (grouped_gemm/op_host/grouped_matmul_antiquant_tiling.cpp:413-460)
+ *   b200moe_grouped_gemv       grouped_soft_gemv/src/grouped_soft_gemv.h:12-14 (GroupedSoftGemv),
+ *                              python name `grouped_soft_gemv` in pybind.cpp:14-16
+ *   b200moe_fp4_dequant        the dequant phase of the GEMM kernel
+ *                              (grouped_gemm/op_kernel/antiquant_impl.h:210-251) as a standalone op
+ *   b200moe_fp4_layout         weight pre-shuffle the reference tests apply on the host
+ *                              (grouped_gemm/test/python/test_group_gemm_fp4.py:129-142)
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ---------------------------------------------------------------------- */
+enum {
+    B200MOE_OK = 0,
+    B200MOE_ERR_COMPUTE_TYPE = 1, /* not one of the B200MOE_CT_* values                     */
+    B200MOE_ERR_NULL_POINTER = 2, /* a required pointer is NULL                              */
+    B200MOE_ERR_SHAPE = 3,        /* negative size, or K/N not a multiple the mode requires  */
+    B200MOE_ERR_ALIGNMENT = 4,    /* a pointer is not 16-byte aligned                        */
+    B200MOE_ERR_WORKSPACE = 5,    /* workspace missing or smaller than *_workspace_bytes()   */
+    B200MOE_ERR_ARGUMENT = 6,     /* invalid enum value (group_list_type, layout, ...)       */
+    B200MOE_ERR_CUDA = 7,         /* a CUDA runtime / driver call failed at launch           */
+    B200MOE_ERR_UNSUPPORTED = 8   /* valid request this build does not implement             */
+};
+
+/* ---- compute types (the reference's `computeType` string) ------------------------------- */
+enum {
+    B200MOE_CT_FP8 = 0,  /* "fp8": uint8 e4m3 codes [G,K,N], fp32 scale [G,K/128,N/128]      */
+    B200MOE_CT_FP4 = 1,  /* "fp4": e2m1 pairs [G,K,N/2] (low nibble = even n), bf16 scale
+                                   [G,K/16,N]                                                */
+    B200MOE_CT_INT8 = 2, /* "int8": int8 [G,K,N], bf16 scale/offset [G,N]: (W+offset)*scale  */
+    B200MOE_CT_INT4 = 3  /* "int4": two's-complement pairs [G,K,N/2], bf16 scale/offset
+                                   [G,K/128,N]                                               */
+};
+
+enum { B200MOE_GROUP_LIST_CUMSUM = 0, B200MOE_GROUP_LIST_COUNTS = 1 };
+enum { B200MOE_LAYOUT_CANONICAL = 0, B200MOE_LAYOUT_ASCEND = 1 }; /* fp4 weights only */
+enum { B200MOE_FP4_SCALE_NONE = 0, B200MOE_FP4_SCALE_E8M0_PER32 = 1 };
+
+/* Device-side status words live in the first 16 bytes of every workspace:
+ *   word 0: 0 = ok; 1 = group_list invalid (not monotone / exceeds M; rows were clamped);
+ *           2 = a bounded pipeline wait expired inside a kernel (results are incomplete)
+ *   word 1: detail (expert index or barrier id). */
+#define B200MOE_STATUS_BYTES 256
+
+/* Grouped GEMM for prefill-sized expert batches:
+ *   y[r0_g:r1_g, :] = bf16( x[r0_g:r1_g, :] @ dequant(weight[g]) ), fp32 accumulation.
+ * x: bf16 [M,K] row-major; y: bf16 [M,N] row-major; group_list: int64 [G] on the device,
+ * cumulative row boundaries (type 0, reference behaviour) or per-expert counts (type 1).
+ * fp8/fp4: dequantised weights are rounded to bf16 before the product (reference semantics),
+ * `offset` is accepted and ignored.  int8: exact integer weights on the tensor cores, scale and
+ * offset applied in the fp32 epilogue; offset may be NULL (= 0). */
+int b200moe_grouped_gemm(const void* x, const void* weight, const void* scale, const void* offset,
+                         const int64_t* group_list, void* y, int64_t M, int64_t K, int64_t N, int64_t G,
+                         int compute_type, int group_list_type, int weight_layout, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+size_t b200moe_grouped_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t G, int compute_type,
+                                            int weight_layout);
+
+/* Grouped GEMV for decode-sized expert batches (any number of rows per expert is accepted;
+ * it is bandwidth-optimal up to 4 rows per expert).  Dequantised weights stay fp32, x is
+ * widened to fp32, one final round to bf16.  `offset` only for int8/int4 (may be NULL). */
+int b200moe_grouped_gemv(const void* x, const void* weight, const void* scale, const void* offset,
+                         const int64_t* group_list, void* y, int64_t M, int64_t K, int64_t N, int64_t G,
+                         int compute_type, int group_list_type, int weight_layout, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+size_t b200moe_grouped_gemv_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t G, int compute_type,
+                                            int weight_layout);
+
+/* Standalone FP4(e2m1) -> BF16.  codes: n_elems/2 bytes, low nibble = even element; scale:
+ * one e8m0 byte per 32 consecutive elements (scale_kind 1) or NULL (scale_kind 0);
+ * out: n_elems bf16.  n_elems must be a multiple of 32.  Bit-exact. */
+int b200moe_fp4_dequant(const void* codes, const void* scale_e8m0, void* out_bf16, int64_t n_elems,
+                        int scale_kind, void* stream);
+
+/* FP4 weight layout conversion, [G,K,N/2] bytes: to_ascend != 0 canonical -> stored ("ascend")
+ * order, 0 the inverse.  src and dst must not overlap. */
+int b200moe_fp4_layout(const void* src, void* dst, int64_t G, int64_t K, int64_t N, int to_ascend, void* stream);
+
+/* Small kernels the MoE layer needs around the two GEMMs (no reference counterpart: the
+ * reference ships only the two operators; these belong to the benchmark's layer configuration). */
+/* out[r, i] = bf16( silu(h[r, i]) * h[r, I + i] ), h bf16 [rows, 2I], out bf16 [rows, I]. */
+int b200moe_silu_mul(const void* h, void* out, int64_t rows, int64_t inter, void* stream);
+/* dst[i, :] = src[index[i], :] for i < n_rows (bf16 rows of `width` elements, int32 index). */
+int b200moe_gather_rows(const void* src, const int32_t* index, void* dst, int64_t n_rows, int64_t width,
+                        void* stream);
+/* out[t, :] = bf16( sum_j weight[t, j] * y[slot[t, j], :] ), y bf16 [*, width], slot int32 [T, top_k],
+ * weight fp32 [T, top_k]. */
+int b200moe_combine(const void* y, const int32_t* slot, const float* weight, void* out, int64_t n_tokens,
+                    int64_t top_k, int64_t width, void* stream);
+
+/* Copies the two device status words of a workspace to the host (synchronises the stream). */
+int b200moe_read_status(const void* workspace, int32_t out[2], void* stream);
+
+const char* b200moe_strerror(int code);
+/* "major.minor" of this ABI; a binding can refuse to run against another major. */
+const char* b200moe_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

@@ -1,0 +1,106 @@
+"""Grouped soft GEMV through the C ABI against the CPU oracle and the reference-derived fixtures."""
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests.util import assert_close_to_golden, bf16, load
+
+pytestmark = pytest.mark.gpu
+SENTINEL = -777.0
+
+
+def run_gemv(x, w, scale, gl, ct, offset=None, gl_type=0, layout="ascend"):
+    import ascend_kernel_b200 as ak
+
+    N = w.shape[2] * (2 if ct in ("fp4", "int4") else 1)
+    out = torch.full((x.shape[0], N), SENTINEL, dtype=torch.bfloat16, device="cuda")
+    ws = ak.grouped_soft_gemv(x.cuda(), w.cuda(), scale.cuda(), gl.cuda(), ct, out, group_list_type=gl_type,
+                              weight_layout=layout, offset=None if offset is None else offset.cuda(),
+                              return_workspace=True)
+    torch.cuda.synchronize()
+    return out, ak.read_status(ws)
+
+
+def _int8_case(counts, K, N, seed, with_offset):
+    gen = torch.Generator().manual_seed(seed)
+    G = len(counts)
+    counts = torch.tensor(counts, dtype=torch.int64)
+    M = int(counts.sum())
+    x = torch.randn(M, K, generator=gen).to(torch.bfloat16)
+    w = torch.randint(-128, 128, (G, K, N), generator=gen, dtype=torch.int8)
+    scale = (torch.rand(G, N, generator=gen) * 0.009 + 0.001).to(torch.bfloat16)
+    offset = (torch.rand(G, N, generator=gen) * 8 - 4).to(torch.bfloat16) if with_offset else None
+    return x, w, scale, offset, counts
+
+
+@pytest.mark.parametrize("counts,K,N,with_offset", [
+    ([1, 1, 1, 1], 256, 256, False),
+    ([1, 0, 2, 4, 0, 3], 512, 512, True),
+    ([0, 0, 5, 9, 1], 192, 768, True),       # more than 4 rows per expert, K not a multiple of 128
+    ([2] * 40, 128, 256, False),             # more work items than resident CTAs per expert slab
+])
+def test_int8_matches_oracle(counts, K, N, with_offset):
+    x, w, scale, offset, cnt = _int8_case(counts, K, N, 7, with_offset)
+    gold = O.golden_f32(x, w, scale, offset, cnt, "int8", O.GROUP_LIST_COUNTS, gemv=True)
+    out, st = run_gemv(x, w, scale, cnt, "int8", offset, gl_type=1)
+    assert st == (0, 0)
+    assert_close_to_golden(out, gold)
+    # cumulative group_list gives the same result
+    out2, _ = run_gemv(x, w, scale, torch.cumsum(cnt, 0), "int8", offset, gl_type=0)
+    assert torch.equal(out.cpu().view(torch.int16), out2.cpu().view(torch.int16))
+
+
+def test_rows_past_last_boundary_untouched():
+    x, w, scale, offset, cnt = _int8_case([1, 2, 1], 128, 256, 9, True)
+    x = torch.cat([x, torch.randn(3, 128).to(torch.bfloat16)])  # 3 rows owned by nobody
+    out, st = run_gemv(x, w, scale, torch.cumsum(cnt, 0), "int8", offset)
+    assert st == (0, 0)
+    assert (out[4:].float() == SENTINEL).all() and (out[:4].float() != SENTINEL).any()
+
+
+def test_fp8_reference_fixture():
+    d = load("gemv_fp8.npz")
+    w, s = torch.from_numpy(d["weight"]), torch.from_numpy(d["scale"])
+    x, gl = bf16(d["x_bits"]), torch.from_numpy(d["group_list"])
+    out, st = run_gemv(x, w, s, gl, "fp8")
+    assert st == (0, 0)
+    want = bf16(d["y_bits"]).float()
+    # the reference's own bar for this op: allclose(rtol=0.02) (test_group_soft_gemv_fp8.py:80)
+    assert torch.allclose(out.cpu().float(), want, rtol=0.02, atol=1e-2)
+    gold = O.golden_f32(x, w, s, None, gl, "fp8", gemv=True)
+    assert_close_to_golden(out, gold, ulps=2.0)
+
+
+def test_fp8_all_codes_and_many_rows():
+    gen = torch.Generator().manual_seed(3)
+    G, K, N = 3, 256, 256
+    w = torch.arange(256, dtype=torch.uint8).repeat(G * K * N // 256).reshape(G, K, N)
+    w = w[:, torch.randperm(K, generator=gen)]
+    s = torch.randn(G, K // 128, N // 128, generator=gen)
+    cnt = torch.tensor([3, 0, 6], dtype=torch.int64)
+    x = torch.randn(9, K, generator=gen).to(torch.bfloat16)
+    gold = O.golden_f32(x, w, s, None, torch.cumsum(cnt, 0), "fp8", gemv=True)
+    out, st = run_gemv(x, w, s, torch.cumsum(cnt, 0), "fp8")
+    assert st == (0, 0)
+    assert_close_to_golden(out, gold, ulps=2.0)
+
+
+@pytest.mark.parametrize("prefix", ["ref_", "uni_"])
+@pytest.mark.parametrize("layout", ["ascend", "canonical"])
+def test_fp4_reference_fixture(prefix, layout):
+    d = load("gemv_fp4.npz")
+    w = torch.from_numpy(d[prefix + ("weight_ascend" if layout == "ascend" else "weight_canonical")])
+    s, x, gl = bf16(d[prefix + "scale_bits"]), bf16(d[prefix + "x_bits"]), torch.from_numpy(d[prefix + "group_list"])
+    out, st = run_gemv(x, w, s, gl, "fp4", layout=layout)
+    assert st == (0, 0)
+    # reference bar: allclose(atol=0.5) against the bf16-weight golden (test_group_soft_gemv_fp4.py:223)
+    assert torch.allclose(out.cpu().float(), bf16(d[prefix + "y_bits"]).float(), atol=0.5)
+    gold = O.golden_f32(x, w, s, None, gl, "fp4", weight_layout=layout, gemv=True)
+    assert_close_to_golden(out, gold, ulps=2.0)
+
+
+def test_bad_group_list_is_clamped_and_reported():
+    x, w, scale, offset, cnt = _int8_case([1, 2, 1], 128, 256, 9, False)
+    bad = torch.tensor([1, 0, 99], dtype=torch.int64)  # not monotone, then beyond M
+    out, st = run_gemv(x, w, scale, bad, "int8")
+    assert st[0] == 1

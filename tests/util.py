@@ -21,3 +21,28 @@ def bits(t: torch.Tensor) -> torch.Tensor:
 
 def same_bits(a: torch.Tensor, b: torch.Tensor) -> bool:
     return bool(torch.equal(bits(a), bits(b)))
+
+
+def ulp_bf16(t: torch.Tensor) -> torch.Tensor:
+    """Size of one bf16 unit in the last place at |t| (float32 tensor in, float32 out)."""
+    a = t.abs().float().clamp_min(2.0 ** -126)
+    return torch.exp2(torch.floor(torch.log2(a)) - 7)
+
+
+def assert_close_to_golden(out: torch.Tensor, golden_f32: torch.Tensor, rel_l2_tol=1e-3, max_abs_tol=2e-2,
+                           ulps=1.0):
+    """The comparison the benchmark configuration states: kernel bf16 output against the float32
+    golden rounded to bf16; rel-L2 <= 1e-3, and every element within max-abs 2e-2 or, where one
+    bf16 step at that magnitude is already larger than 2e-2, within `ulps` bf16 steps."""
+    from oracle import oracle as O
+
+    mask = ~torch.isnan(golden_f32[:, 0])
+    g = golden_f32[mask].to(torch.bfloat16).float()
+    o = out.cpu()[mask].float()
+    rl2 = O.rel_l2(o, g)
+    diff = (o - g).abs()
+    bound = torch.maximum(torch.full_like(g, max_abs_tol), ulps * ulp_bf16(g))
+    bad = int((diff > bound).sum())
+    assert rl2 <= rel_l2_tol, f"rel-L2 {rl2:.3e} > {rel_l2_tol}"
+    assert bad == 0, f"{bad} elements beyond max(2e-2, {ulps} ulp); max diff {float(diff.max()):.4f}"
+    return rl2, float(diff.max()), float((o != g).float().mean())
