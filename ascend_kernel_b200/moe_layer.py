@@ -1,0 +1,146 @@
+"""Expert-parallel MoE FFN layer built from the hot-path operators.
+
+One process per GPU; experts are sharded contiguously over the ranks (expert e lives on rank
+e // (E / world)).  Per step:
+
+  route (softmax -> top-k -> renormalise)            torch, tiny
+  sort the (token, k) pairs by expert, gather rows   b200moe_gather_rows
+  all-to-all of per-expert counts, then of rows      NCCL (torch.distributed), world > 1 only
+  regroup received rows expert-major                 b200moe_gather_rows, world > 1 only
+  grouped GEMM gate|up  [H -> 2I], int8 antiquant    b200moe_grouped_gemm  (tcgen05)
+  SiLU(gate) * up                                    b200moe_silu_mul
+  grouped GEMM down     [I -> H], int8 antiquant     b200moe_grouped_gemm
+  inverse regroup, all-to-all back                   world > 1 only
+  weighted sum over each token's k results           b200moe_combine
+
+Data from peers always lands in this GPU's own memory (the NCCL receive buffer) before a kernel
+reads it.  torch is used for device memory, streams, the router's few small tensor ops and the
+process group; every row-sized operation is one of the package's CUDA kernels.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+
+class CudaRowOps:
+    """The row-sized operations of the layer, on this package's CUDA kernels."""
+
+    gather_rows = staticmethod(ops.gather_rows)
+    combine = staticmethod(ops.combine)
+    silu_mul = staticmethod(ops.silu_mul)
+    grouped_gemm = staticmethod(ops.grouped_gemm)
+
+
+class MoELayer:
+    def __init__(self, w13, s13, o13, w2, s2, o2, n_experts: int, top_k: int, group=None, row_ops=CudaRowOps):
+        """w13 int8 [E_local, H, 2I] (gate columns first), w2 int8 [E_local, I, H]; per-channel bf16
+        scales/offsets [E_local, N].  ``group``: a torch.distributed process group or None.
+        ``row_ops`` exists so the dispatch / regroup / combine index logic can be exercised by CPU
+        ranks in the test-suite with stand-in row operations; the product always uses CudaRowOps."""
+        self.ops = row_ops
+        self.w13, self.s13, self.o13, self.w2, self.s2, self.o2 = w13, s13, o13, w2, s2, o2
+        self.n_experts, self.top_k = n_experts, top_k
+        self.group = group
+        if group is not None:
+            import torch.distributed as dist
+
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        else:
+            self.world, self.rank = 1, 0
+        self.e_local = w13.shape[0]
+        assert self.e_local * self.world == n_experts
+        self.hidden, self.inter = w13.shape[1], w2.shape[1]
+        self.device = w13.device
+        self.timing = None  # optional dict of CUDA event pairs filled by forward(record=True)
+
+    # ---- routing ---------------------------------------------------------------------------
+    def route(self, logits):
+        p = torch.softmax(logits.float(), dim=-1)
+        w, idx = torch.topk(p, self.top_k, dim=-1)
+        return (w / w.sum(dim=-1, keepdim=True)).contiguous(), idx
+
+    def _experts(self, rows, counts, record):
+        """rows [R, H] expert-major with per-local-expert counts -> [R, H]."""
+        R = rows.shape[0]
+        h = torch.empty(R, 2 * self.inter, dtype=torch.bfloat16, device=self.device)
+        y = torch.empty(R, self.hidden, dtype=torch.bfloat16, device=self.device)
+        if R == 0:
+            return y
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if record else None
+        self.timing = None
+        if ev:
+            ev[0].record()
+        self.ops.grouped_gemm(rows, self.w13, self.s13, self.o13, counts, "int8", h, group_list_type=1)
+        if ev:
+            ev[1].record()
+        act = self.ops.silu_mul(h)
+        if ev:
+            ev[2].record()
+        self.ops.grouped_gemm(act, self.w2, self.s2, self.o2, counts, "int8", y, group_list_type=1)
+        if ev:
+            ev[3].record()
+            self.timing = ev
+        return y
+
+    # ---- one step --------------------------------------------------------------------------
+    def forward(self, x, logits, record: bool = False):
+        """x bf16 [T, H], logits bf16 [T, E] on this rank's device -> bf16 [T, H]."""
+        T = x.shape[0]
+        wts, idx = self.route(logits)
+        flat = idx.reshape(-1)
+        order = torch.argsort(flat, stable=True)                 # pair indices sorted by expert
+        token_of = (order // self.top_k).to(torch.int32)
+        slot = torch.empty_like(order)
+        slot[order] = torch.arange(order.numel(), device=self.device)
+        slot = slot.reshape(T, self.top_k).to(torch.int32)       # position of pair (t, j) in sorted order
+        counts = torch.bincount(flat, minlength=self.n_experts)  # int64 [E]
+        send = self.ops.gather_rows(x, token_of)                      # [T*k, H] sorted by expert
+
+        if self.world == 1:
+            y = self._experts(send, counts, record)
+            return self.ops.combine(y, slot, wts)
+
+        import torch.distributed as dist
+
+        # per (destination rank, local expert) counts out, per (source rank, local expert) counts in
+        send_counts = counts.reshape(self.world, self.e_local)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        # the variable all-to-all needs its split sizes on the host
+        both = torch.stack([send_counts.sum(1), recv_counts.sum(1)]).cpu()
+        in_split, out_split = both[0].tolist(), both[1].tolist()
+        n_recv = int(sum(out_split))
+        recv = torch.empty(n_recv, self.hidden, dtype=torch.bfloat16, device=self.device)
+        dist.all_to_all_single(recv, send, out_split, in_split, group=self.group)
+
+        # received order is (source rank, expert); the grouped GEMM wants expert-major
+        local_counts = recv_counts.sum(0)
+        blk = recv_counts.reshape(-1)                                          # block sizes, source-major
+        src_start = torch.cumsum(blk, 0) - blk                                 # where each block sits now
+        em = recv_counts.t().contiguous().reshape(-1)                          # block sizes, expert-major
+        em_start = (torch.cumsum(em, 0) - em).reshape(self.e_local, self.world).t().reshape(-1)
+        # for every received row: its position in expert-major order
+        pos = torch.repeat_interleave(em_start - src_start, blk, output_size=n_recv) + torch.arange(
+            n_recv, device=self.device)
+        inv = torch.empty_like(pos)
+        inv[pos] = torch.arange(n_recv, device=self.device)
+        rows = self.ops.gather_rows(recv, inv.to(torch.int32))                      # expert-major
+        y = self._experts(rows, local_counts, record)
+        back = self.ops.gather_rows(y, pos.to(torch.int32))                         # source-major again
+        ret = torch.empty(send.shape[0], self.hidden, dtype=torch.bfloat16, device=self.device)
+        dist.all_to_all_single(ret, back, in_split, out_split, group=self.group)
+        return self.ops.combine(ret, slot, wts)
+
+    def forward_host(self, x_host, logits_host, out_host=None):
+        """End-to-end call with host buffers: pinned host -> device copies of this step's inputs,
+        the layer, and the device -> host read of the result."""
+        x = x_host.to(self.device, non_blocking=True)
+        lg = logits_host.to(self.device, non_blocking=True)
+        out = self.forward(x, lg)
+        if out_host is None:
+            out_host = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return out_host

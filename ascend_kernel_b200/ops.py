@@ -15,6 +15,14 @@ from ._abi import CT, LAYOUT
 
 _lib = _abi.lib
 
+# number of this package's kernels launched so far (the benchmark reads and resets it)
+LAUNCHES = 0
+
+
+def _count(n):
+    global LAUNCHES
+    LAUNCHES += n
+
 
 def _ptr(t):
     return None if t is None else t.data_ptr()
@@ -92,6 +100,8 @@ def grouped_gemm(x, weight, antiquantScaleOptional, antiquantOffsetOptional, gro
     ws = _run(_lib.b200moe_grouped_gemm, _lib.b200moe_grouped_gemm_workspace_bytes, "grouped_gemm", x, weight,
               antiquantScaleOptional, offset, groupListOptional, output, ct, group_list_type,
               LAYOUT[weight_layout], M, K, N, G)
+    if M > 0:  # GEMM + row sums for the offset term + layout conversion of pre-shuffled fp4 weights
+        _count(1 + (offset is not None) + (ct == CT["fp4"] and weight_layout == "ascend"))
     return ws if return_workspace else None
 
 
@@ -107,6 +117,8 @@ def grouped_soft_gemv(x, weight, scale, groupList, computeType, output, group_li
         _check_scale(offset, ct, G, K, N, "offset")
     ws = _run(_lib.b200moe_grouped_gemv, _lib.b200moe_grouped_gemv_workspace_bytes, "grouped_soft_gemv", x, weight,
               scale, offset, groupList, output, ct, group_list_type, LAYOUT[weight_layout], M, K, N, G)
+    if M > 0:
+        _count(1 + (ct == CT["fp4"] and weight_layout == "ascend"))
     return ws if return_workspace else None
 
 
@@ -122,6 +134,7 @@ def fp4_dequant(codes, scale, output):
         rc = _lib.b200moe_fp4_dequant(_ptr(codes), _ptr(scale), _ptr(output), n,
                                       _abi.FP4_SCALE_NONE if scale is None else _abi.FP4_SCALE_E8M0_PER32, _stream())
     _abi.check(rc, "fp4_dequant")
+    _count(1)
 
 
 def fp4_layout(src, to_ascend: bool):
@@ -132,6 +145,7 @@ def fp4_layout(src, to_ascend: bool):
     with torch.cuda.device(src.device):
         rc = _lib.b200moe_fp4_layout(_ptr(src), _ptr(dst), G, K, 2 * C, int(bool(to_ascend)), _stream())
     _abi.check(rc, "fp4_layout")
+    _count(1)
     return dst
 
 
@@ -143,6 +157,7 @@ def silu_mul(h, out=None):
     with torch.cuda.device(h.device):
         rc = _lib.b200moe_silu_mul(_ptr(h), _ptr(out), rows, two_i // 2, _stream())
     _abi.check(rc, "silu_mul")
+    _count(1)
     return out
 
 
@@ -155,6 +170,7 @@ def gather_rows(src, index, out=None):
     with torch.cuda.device(src.device):
         rc = _lib.b200moe_gather_rows(_ptr(src), _ptr(index), _ptr(out), index.numel(), src.shape[1], _stream())
     _abi.check(rc, "gather_rows")
+    _count(1)
     return out
 
 
@@ -168,6 +184,7 @@ def combine(y, slot, weight, out=None):
     with torch.cuda.device(y.device):
         rc = _lib.b200moe_combine(_ptr(y), _ptr(slot), _ptr(weight), _ptr(out), T, top_k, y.shape[1], _stream())
     _abi.check(rc, "combine")
+    _count(1)
     return out
 
 

@@ -1,0 +1,414 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE expert-GEMM hot path on B200.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...        # the CPU golden path on the host cores
+
+One step = one pass of the expert-parallel MoE FFN layer (benchmark configuration 4: 4096 tokens,
+hidden 7168, 256 experts, intermediate 2048, top-8, int8 antiquant weights with per-channel
+scale/offset) over a batch of seeded synthetic tokens.  The global batch is fixed (strong
+scaling): each of the N ranks holds 4096/N tokens and 256/N experts.
+
+Rank 0 prints ONE JSON line.  `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is
+the same metric through the public host-buffer call (pinned host -> device copies of the step's
+inputs and the device -> host read of the result inside the timed region); `roofline` covers the
+dominant kernel of the step (the tcgen05 grouped GEMM, both launches); `kernels` (N=1 only) holds
+the three hot-path kernels at their own benchmark configurations (prefill grouped GEMM, decode
+grouped GEMV, FP4 dequant) with their roofline fractions of the measured peaks; `cpu_baseline` is
+the CPU oracle (torch-CPU float32 golden path) timed on this box's host cores on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CFG = dict(n_tokens=4096, hidden=7168, n_experts=256, inter=2048, top_k=8, seed=4)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks during the timed region
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc = index, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            return
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [v.strip() for v in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if sm:
+            self.result = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                           "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU golden path (oracle) on a bounded sample -- the cpu_baseline leg and the reference arm
+# ------------------------------------------------------------------------------------------------
+def cpu_sample_inputs(every: int):
+    """Routing of the full configuration; weights only for every `every`-th expert by load rank."""
+    import torch
+
+    from ascend_kernel_b200 import inputs
+    from oracle import oracle as O
+
+    c = inputs.config4("cpu", expert_lo=0, expert_hi=0, **CFG)
+    wts, idx = O.route_topk(c["logits"], CFG["top_k"])
+    counts = torch.bincount(idx.reshape(-1), minlength=CFG["n_experts"])
+    by_load = torch.argsort(counts, descending=True)
+    chosen = by_load[every // 2::every].tolist()
+    weights = {e: inputs.config4("cpu", n_tokens=1, hidden=CFG["hidden"], n_experts=CFG["n_experts"],
+                                 inter=CFG["inter"], top_k=CFG["top_k"], seed=CFG["seed"], expert_lo=e,
+                                 expert_hi=e + 1) for e in chosen}
+    return c, idx, counts, chosen, weights
+
+
+def cpu_moe_sample(every: int, prepared=None):
+    """Times the CPU golden path over the sampled experts' routed rows (weight generation is
+    outside the timed region).  Returns (tokens_per_s, seconds, rows, description)."""
+    import torch
+
+    c, idx, counts, chosen, weights = prepared if prepared is not None else cpu_sample_inputs(every)
+    rows_total, t_total = 0, 0.0
+    I = CFG["inter"]
+    for e in chosen:
+        tok = (idx == e).nonzero(as_tuple=True)[0]
+        if tok.numel() == 0:
+            continue
+        w = weights[e]
+        xr = c["x"][tok]
+        t0 = time.perf_counter()
+        wd1 = (w["w13"][0].float() + w["o13"][0].float()) * w["s13"][0].float()
+        h = (xr.float() @ wd1).to(torch.bfloat16).float()
+        act = (torch.nn.functional.silu(h[:, :I]) * h[:, I:]).to(torch.bfloat16).float()
+        wd2 = (w["w2"][0].float() + w["o2"][0].float()) * w["s2"][0].float()
+        _ = (act @ wd2).to(torch.bfloat16)
+        t_total += time.perf_counter() - t0
+        rows_total += int(tok.numel())
+    tok_s = (rows_total / CFG["top_k"]) / t_total if t_total > 0 else 0.0
+    desc = (f"{len(chosen)} of {CFG['n_experts']} experts (every {every}th by load rank) with all their routed rows "
+            f"({rows_total} of {CFG['n_tokens'] * CFG['top_k']} rows), float32 torch-CPU dequant + matmul; "
+            f"tokens/s = rows/top_k/time")
+    return tok_s, t_total, rows_total, desc
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+
+    threads = torch.get_num_threads()
+    every = 32
+    prepared = cpu_sample_inputs(every)
+    for _ in range(args.warmup):
+        cpu_moe_sample(every, prepared)
+    vals, secs = [], 0.0
+    for _ in range(args.steps):
+        v, t, rows, desc = cpu_moe_sample(every, prepared)
+        vals.append(v)
+        secs += t
+    value = statistics.mean(vals) if vals else 0.0
+    line = {
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * secs / max(1, args.steps), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "the reference's device code targets Ascend NPUs and cannot run here; this arm times the CPU "
+                "restatement of its golden path (oracle port) on the host cores",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": "moe_ffn_layer_int8_antiquant (benchmark configuration 4)", **CFG,
+            "experts_per_gpu": CFG["n_experts"] // n_gpus, "tokens_per_gpu": CFG["n_tokens"] // n_gpus,
+            "parallelism": f"ep{n_gpus}",
+            "l2": "no flush: per-GPU working set (expert weights) is far larger than the 126 MB L2"}
+
+
+# ------------------------------------------------------------------------------------------------
+# per-kernel lines (N = 1)
+# ------------------------------------------------------------------------------------------------
+def time_launches(fn, n_warm, n_iter):
+    import torch
+
+    for _ in range(n_warm):
+        fn()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_iter)]
+    for a, b in evs:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    return statistics.median(a.elapsed_time(b) for a, b in evs)
+
+
+def kernel_lines(peaks, quick=False):
+    import torch
+
+    import ascend_kernel_b200 as ak
+    from ascend_kernel_b200 import inputs
+
+    dev = "cuda"
+    out = {}
+    # ---- prefill grouped GEMM (configuration 3, variant A) ----
+    c = inputs.config3(dev) if not quick else inputs.config3(dev, n_rows=8192, n_experts=32)
+    M, K = c["x"].shape
+    G, _, N = c["weight"].shape
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    ms = time_launches(lambda: ak.grouped_gemm(c["x"], c["weight"], c["scale"], c["offset"], c["counts"], "int8", y,
+                                               group_list_type=1), 3, 10)
+    flops = 2.0 * M * K * N
+    out["grouped_gemm_prefill_int8"] = {
+        "ms": ms, "tflops": flops / ms / 1e9, "frac_of_measured_sustained": flops / ms / 1e9 / peaks["bf16_tflops_sustained"],
+        "frac_of_measured_burst": flops / ms / 1e9 / peaks["bf16_tflops"], "frac_of_spec_2250": flops / ms / 1e9 / 2250.0,
+        "shape": {"M": M, "K": K, "N": N, "G": G, "active_experts": int((c["counts"] > 0).sum())}}
+    # ---- decode grouped GEMV (configuration 1): reuse the weight tensor ----
+    counts = inputs.routed_counts(32, G, 8, torch.Generator().manual_seed(1)).to(dev)
+    Mv = int(counts.sum())
+    xv = c["x"][:Mv].contiguous()
+    yv = torch.empty(Mv, N, dtype=torch.bfloat16, device=dev)
+    n_act = int((counts > 0).sum())
+    ms = time_launches(lambda: ak.grouped_soft_gemv(xv, c["weight"], c["scale"], counts, "int8", yv,
+                                                    group_list_type=1), 3, 10)
+    by = n_act * K * N + 2.0 * Mv * K + 2.0 * Mv * N + n_act * N * 2
+    out["grouped_gemv_decode_int8_pass1"] = {"ms": ms, "gbs": by / ms / 1e6, "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
+                                             "frac_of_spec_8000": by / ms / 1e6 / 8000.0,
+                                             "shape": {"M": Mv, "K": K, "N": N, "G": G, "active_experts": n_act}}
+    del c, y, xv, yv
+    torch.cuda.empty_cache()
+    if not quick:
+        gen = torch.Generator(device=dev).manual_seed(11)
+        K2, N2 = 2048, 7168
+        w2 = inputs.int8_weights(G, K2, N2, gen, dev)
+        s2 = (torch.rand(G, N2, generator=gen, device=dev) * 0.009 + 0.001).to(torch.bfloat16)
+        x2 = torch.randn(Mv, K2, generator=gen, device=dev).to(torch.bfloat16)
+        y2 = torch.empty(Mv, N2, dtype=torch.bfloat16, device=dev)
+        ms = time_launches(lambda: ak.grouped_soft_gemv(x2, w2, s2, counts, "int8", y2, group_list_type=1), 3, 10)
+        by = n_act * K2 * N2 + 2.0 * Mv * K2 + 2.0 * Mv * N2 + n_act * N2 * 2
+        out["grouped_gemv_decode_int8_pass2"] = {"ms": ms, "gbs": by / ms / 1e6, "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
+                                                 "frac_of_spec_8000": by / ms / 1e6 / 8000.0,
+                                                 "shape": {"M": Mv, "K": K2, "N": N2, "G": G, "active_experts": n_act}}
+        del w2, s2, x2, y2
+        torch.cuda.empty_cache()
+    # ---- FP4 dequant (configuration 2) ----
+    d = inputs.config2(dev) if not quick else inputs.config2(dev, shape=(32, 2048, 7168))
+    n = d["codes"].numel() * 2
+    o = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    ms = time_launches(lambda: ak.fp4_dequant(d["codes"], d["scale"], o), 3, 10)
+    by = n * (0.5 + 1.0 / 32 + 2.0)
+    out["fp4_dequant_e8m0"] = {"ms": ms, "gbs": by / ms / 1e6, "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
+                               "frac_of_spec_8000": by / ms / 1e6 / 8000.0, "elements": n}
+    del d, o
+    torch.cuda.empty_cache()
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+
+    import ascend_kernel_b200 as ak  # noqa: F401  (fails loudly if the CUDA library is missing)
+    from ascend_kernel_b200 import inputs, ops
+    from ascend_kernel_b200.moe_layer import MoELayer
+
+    peaks, peak_kind = load_peaks()
+    E, T = CFG["n_experts"], CFG["n_tokens"]
+    assert E % world == 0 and T % world == 0
+    e_local, t_local = E // world, T // world
+    c = inputs.config4(dev, expert_lo=rank * e_local, expert_hi=(rank + 1) * e_local, **CFG)
+    layer = MoELayer(c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], E, CFG["top_k"], group)
+    x_host = c["x"][rank * t_local:(rank + 1) * t_local].contiguous().pin_memory()
+    lg_host = c["logits"][rank * t_local:(rank + 1) * t_local].contiguous().pin_memory()
+    x, lg = x_host.to(dev), lg_host.to(dev)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier(group=group)
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        import torch.distributed as dist
+
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        return float(t.item())
+
+    # ---- device-resident timing ----
+    for _ in range(args.warmup):
+        layer.forward(x, lg)
+    barrier()
+    ops.LAUNCHES = 0
+    gemm_ms, gemm_events = 0.0, []
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(args.steps):
+            layer.forward(x, lg, record=True)
+            if layer.timing is not None:
+                gemm_events.append(layer.timing)
+        ev1.record()
+        barrier()
+    launches = ops.LAUNCHES / max(1, args.steps)
+    total_ms = max_over_ranks(ev0.elapsed_time(ev1))
+    for ev in gemm_events:
+        gemm_ms += ev[0].elapsed_time(ev[1]) + ev[2].elapsed_time(ev[3])
+    ms_per_step = total_ms / args.steps
+    value = T / (ms_per_step / 1e3)
+
+    # ---- end to end through the host-buffer call ----
+    out_host = torch.empty(t_local, CFG["hidden"], dtype=torch.bfloat16).pin_memory()
+    for _ in range(min(3, args.warmup)):
+        layer.forward_host(x_host, lg_host, out_host)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        layer.forward_host(x_host, lg_host, out_host)
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    h2d = (x_host.numel() * 2 + lg_host.numel() * 2) * world
+    d2h = out_host.numel() * 2 * world
+
+    # ---- roofline of the dominant kernel (both grouped-GEMM launches of a step, this rank) ----
+    rows_local = T * CFG["top_k"] / world  # expectation; exact rows differ per rank by routing
+    flops_step = 2.0 * rows_local * (CFG["hidden"] * 2 * CFG["inter"] + CFG["inter"] * CFG["hidden"])
+    gemm_ms_step = gemm_ms / max(1, len(gemm_events))
+    achieved = flops_step / gemm_ms_step / 1e9 if gemm_ms_step > 0 else 0.0
+    roofline = {"bound": "tensor", "kernel": "grouped_gemm_kernel<int8> (2 launches per step, rank 0)",
+                "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["bf16_tflops_sustained"], "peak_kind": f"{peak_kind} (sustained cuBLAS bf16)",
+                "traffic": None, "ms_per_step_in_kernel": gemm_ms_step}
+
+    line = {
+        "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16 x int8 -> fp32 accumulate", "data": "synthetic",
+        "config": workload_config(world),
+        "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms},
+        "gpu_launches": launches * args.steps, "gpu_launches_per_step": launches,
+        "roofline": roofline, "clocks": clk.result,
+    }
+    if world == 1 and rank == 0:
+        del layer, c
+        torch.cuda.empty_cache()
+        if not args.no_kernels:
+            line["kernels"] = kernel_lines(peaks, quick=args.quick)
+            line["kernels"]["peaks"] = {**peaks, "kind": peak_kind}
+        if not args.no_cpu:
+            tok_s, secs, rows, desc = cpu_moe_sample(16)
+            line["cpu_baseline"] = {"value": tok_s, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                                    "sample": desc, "seconds": secs}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel lines (N=1)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--quick", action="store_true", help="small shapes for the per-kernel lines (profiling)")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

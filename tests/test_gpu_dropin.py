@@ -1,0 +1,94 @@
+"""The compiled `cinfer_ascendc` module called the way the reference's own tests call it
+(keyword arguments in their order, output written in place, no return value), on the
+reference-derived fixtures."""
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests.util import assert_close_to_golden, bf16, load
+
+pytestmark = pytest.mark.gpu
+
+
+def _module():
+    from ascend_kernel_b200 import cinfer_ascendc
+
+    return cinfer_ascendc
+
+
+def test_grouped_gemm_fp8_call_shape_of_reference_test():
+    m = _module()
+    d = load("gemm_fp8.npz")
+    w1w3 = torch.from_numpy(d["weight"]).cuda()
+    scale = torch.from_numpy(d["scale"]).cuda()
+    x = bf16(d["x_bits"]).cuda()
+    expert_tokens = torch.from_numpy(d["group_list"]).cuda()
+    scale_off = torch.zeros_like(scale)
+    output = torch.zeros([x.shape[0], w1w3.shape[2]], device="cuda", dtype=torch.bfloat16)
+    ret = m.grouped_gemm(x, w1w3, output=output, antiquantOffsetOptional=scale_off, antiquantScaleOptional=scale,
+                         groupListOptional=expert_tokens, computeType="fp8")
+    torch.cuda.synchronize()
+    assert ret is None
+    assert torch.allclose(output.cpu().float(), bf16(d["y_bits"]).float(), atol=0.02, rtol=1e-2)
+    gold = O.golden_f32(x.cpu(), w1w3.cpu(), scale.cpu(), None, expert_tokens.cpu(), "fp8")
+    assert_close_to_golden(output, gold)
+
+
+def test_grouped_gemm_fp4_ascend_layout():
+    m = _module()
+    d = load("gemm_fp4.npz")
+    w = torch.from_numpy(d["ref_weight_ascend"]).cuda()
+    new_scale = bf16(d["ref_scale_bits"]).cuda()
+    x = bf16(d["ref_x_bits"]).cuda()
+    gl = torch.from_numpy(d["ref_group_list"]).cuda()
+    output = torch.zeros([x.shape[0], w.shape[-1] * 2], dtype=x.dtype, device=x.device)
+    m.grouped_gemm(x, w, output=output, antiquantOffsetOptional=torch.zeros_like(new_scale),
+                   antiquantScaleOptional=new_scale, groupListOptional=gl, computeType="fp4")
+    torch.cuda.synchronize()
+    assert torch.allclose(output.cpu().float(), bf16(d["ref_y_bits"]).float(), atol=0.15)
+
+
+def test_grouped_soft_gemv_fp8_and_fp4():
+    m = _module()
+    d = load("gemv_fp8.npz")
+    w, s = torch.from_numpy(d["weight"]).cuda(), torch.from_numpy(d["scale"]).cuda()
+    x, gl = bf16(d["x_bits"]).cuda(), torch.from_numpy(d["group_list"]).cuda()
+    output = torch.zeros([x.shape[0], w.shape[2]], device="cuda", dtype=torch.bfloat16)
+    m.grouped_soft_gemv(x, w, output=output, scale=s, groupList=gl, computeType="fp8")
+    torch.cuda.synchronize()
+    assert torch.allclose(output.cpu().float(), bf16(d["y_bits"]).float(), rtol=0.02, atol=1e-2)
+    d = load("gemv_fp4.npz")
+    w, s = torch.from_numpy(d["ref_weight_ascend"]).cuda(), bf16(d["ref_scale_bits"]).cuda()
+    x, gl = bf16(d["ref_x_bits"]).cuda(), torch.from_numpy(d["ref_group_list"]).cuda()
+    output = torch.zeros([x.shape[0], w.shape[-1] * 2], dtype=x.dtype, device=x.device)
+    m.grouped_soft_gemv(x, w, output=output, scale=s, groupList=gl, computeType="fp4")
+    torch.cuda.synchronize()
+    assert torch.allclose(output.cpu().float(), bf16(d["ref_y_bits"]).float(), atol=0.5)
+
+
+def test_int8_counts_mode_and_errors():
+    m = _module()
+    from ascend_kernel_b200 import inputs
+
+    c = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inputs.config0().items()}
+    out = torch.zeros(c["x"].shape[0], c["weight"].shape[2], dtype=torch.bfloat16, device="cuda")
+    m.grouped_gemm(c["x"], c["weight"], c["scale"], c["offset"], c["counts"], "int8", out, group_list_type=1)
+    torch.cuda.synchronize()
+    gold = O.golden_f32(c["x"].cpu(), c["weight"].cpu(), c["scale"].cpu(), c["offset"].cpu(), c["counts"].cpu(),
+                        "int8", O.GROUP_LIST_COUNTS)
+    assert_close_to_golden(out, gold)
+    with pytest.raises(RuntimeError, match="Host tiling failed"):
+        m.grouped_gemm(c["x"], c["weight"], c["scale"], c["offset"], c["counts"], "fp16", out)
+    with pytest.raises(RuntimeError):
+        m.grouped_gemm(c["x"].cpu(), c["weight"], c["scale"], c["offset"], c["counts"], "int8", out)
+
+
+def test_fp4_dequant_entry():
+    m = _module()
+    gen = torch.Generator().manual_seed(2)
+    codes = torch.randint(0, 256, (8, 64), generator=gen, dtype=torch.uint8)
+    sc = torch.randint(119, 128, (8, 4), generator=gen, dtype=torch.uint8)
+    out = torch.empty(8, 128, dtype=torch.bfloat16, device="cuda")
+    m.fp4_dequant(codes.cuda(), sc.cuda(), out)
+    torch.cuda.synchronize()
+    assert torch.equal(out.cpu().view(torch.int16), O.fp4_dequant_e8m0(codes, sc).view(torch.int16))
