@@ -8,26 +8,38 @@
 // experts' tile counts kept in shared memory, binary search per tile), so there is no host
 // synchronisation and no schedule in global memory.
 //
-// Warp roles (16 warps):
+// Warp roles (24 warps):
 //   warp 0      TMA producer of x tiles      (128 rows x 64 k, bf16, 128-byte swizzle, K-major A)
-//   warp 1      TMA producer of packed weight tiles (64 k x 256 n bytes / nibbles, as stored)
 //   warp 2      TMEM allocation + tcgen05.mma issue (one elected lane), UMMA 128x256x16
 //   warps 4-7   epilogue: tcgen05.ld of the accumulator, scale/offset in fp32, bf16 stores
-//   warps 8-15  dequant: packed tile -> bf16 tile in the UMMA MN-major 128-byte-swizzle layout
-// Rings: 4 x-tile stages, 3 packed stages, 3 bf16 weight stages, 2 accumulators of 256 TMEM columns
-// (the epilogue of tile i overlaps the main loop of tile i+1).  Weights never make a round trip
-// through global memory.  Every wait is bounded; on expiry the kernel records an error status,
-// all roles wind down, copies in flight are given time to land and TMEM is released.
+//   warps 8-23  dequant, two groups of 8 warps taking alternate k-stages: packed weights global ->
+//               registers (128-bit coalesced loads, prefetched two of the group's stages ahead) ->
+//               bf16 tile in the UMMA MN-major 128-byte-swizzle layout
+// Rings: 5 x-tile stages, 4 bf16 weight stages, 2 accumulators of 256 TMEM columns (the epilogue
+// of tile i overlaps the main loop of tile i+1).  Shared-memory bandwidth bounds this kernel (the
+// tensor core alone reads 48 KB per 64-k stage), so packed weights go through registers, not
+// through a shared-memory staging ring, and the bf16 tile is written without bank conflicts.
+// Weights never make a round trip through global memory.  Every wait is bounded; on expiry the
+// kernel records an error status, all roles wind down, copies in flight are given time to land
+// and TMEM is released.
 #include "common.cuh"
 #include "ptx.cuh"
 
 namespace b200moe {
 
 constexpr int kBM = 128, kBN = 256, kBK = 64;
-constexpr int kNA = 4, kNP = 3, kNB = 3;
-constexpr int kGemmThreads = 512;
-constexpr int kWarpA = 0, kWarpP = 1, kWarpMma = 2, kWarpEpi0 = 4, kWarpDq0 = 8;
-constexpr int kDqWarps = 8;
+constexpr int kNA = 5, kNB = 4;
+constexpr int kPrefetch = 2;  // packed stages held in registers ahead of the one being converted
+constexpr int kL2Ahead = 8;   // stages by which the L2 prefetch of packed weights leads the x-tile loads
+constexpr int kGemmThreads = 768;
+constexpr int kWarpA = 0, kWarpMma = 2, kWarpEpi0 = 4, kWarpDq0 = 8;
+// The dequant warps form kDqGroups groups; group i converts the k-stages i, i + kDqGroups, ...
+// so a warp pays the barrier handshake once per kDqGroups stages and the groups overlap each
+// other's waits.
+constexpr int kDqGroups = 2;
+constexpr int kDqGroupWarps = 8;
+constexpr int kDqRowStep = 2 * kDqGroupWarps;  // a warp owns two rows; the group covers this many per pass
+constexpr int kDqRows = kBK / kDqRowStep;      // k rows converted by a thread per stage
 constexpr int kSuperRows = 16;  // m-tiles per L2 super-tile
 constexpr int kATileBytes = kBM * kBK * 2;
 constexpr int kBTileBytes = kBK * kBN * 2;
@@ -52,7 +64,6 @@ struct GmTraits {
 
 struct GmBarriers {
     uint64_t a_full[kNA], a_empty[kNA];
-    uint64_t p_full[kNP], p_empty[kNP];
     uint64_t b_full[kNB], b_empty[kNB];
     uint64_t t_full[2], t_empty[2];
     uint64_t drain;
@@ -65,15 +76,31 @@ struct TileInfo {
     int g, row0, row_end, n0;
 };
 
-__device__ __forceinline__ bool gm_wait(uint64_t* bar, uint32_t parity, GmBarriers* sb, int* status, int id) {
-    if (*reinterpret_cast<volatile int*>(&sb->abort)) return false;
-    if (ptx::mbar_wait(ptx::smem_u32(bar), parity)) return true;
-    *reinterpret_cast<volatile int*>(&sb->abort) = 1;
-    if (status != nullptr) {
-        atomicCAS(status, kDevOk, kDevWaitExpired);
-        status[1] = id;
+// Bounded wait on a pipeline barrier.  The fast path is a single try_wait; the slow path polls,
+// notices an abort raised by another role and gives up after ptx::kWaitLimitNs.
+__device__ __noinline__ bool gm_wait_slow(uint32_t bar, uint32_t parity, GmBarriers* sb, int* status, int id) {
+    volatile int* abort = &sb->abort;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    while (!ptx::mbar_try_wait(bar, parity)) {
+        if ((++spins & 0xFF) == 0) {
+            if (*abort) return false;
+            if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
+                *abort = 1;
+                if (status != nullptr) {
+                    atomicCAS(status, kDevOk, kDevWaitExpired);
+                    status[1] = id;
+                }
+                return false;
+            }
+        }
     }
-    return false;
+    return true;
+}
+__device__ __forceinline__ bool gm_wait(uint64_t* bar, uint32_t parity, GmBarriers* sb, int* status, int id) {
+    const uint32_t b = ptx::smem_u32(bar);
+    if (ptx::mbar_try_wait(b, parity)) return true;
+    return gm_wait_slow(b, parity, sb, status, id);
 }
 
 // tile index -> expert, first row, row bound, first column.  tile_prefix has G+1 entries.
@@ -110,29 +137,69 @@ __device__ __forceinline__ uint32_t btile_offset(int k, int nchunk16) {  // nchu
     return (uint32_t)((nchunk16 >> 3) * (kBK * 128) + k * 128 + (((nchunk16 & 7) ^ (k & 7)) << 4));
 }
 
+// Thread -> (row, 16-column chunk) assignment of the dequant warps.  A warp owns two consecutive
+// k rows (an even one and the next).  Each quarter-warp holds four lanes on the even row in
+// 64-column block p and four lanes on the odd row in block p^1: the 128-bit stores of a quarter
+// then hit eight different 16-byte bank groups (the swizzle term k&7 differs in its low bit
+// between the two rows), and the packed loads of a warp still cover both rows contiguously.
+struct DqLane {
+    int row;  // 0 .. kDqRowStep-1: the thread converts k = row + kDqRowStep * j, j < kDqRows, of its stages
+    int c16;  // 16-column chunk 0..15
+};
+__device__ __forceinline__ DqLane dq_lane(int tid) {
+    const int w = tid >> 5, l = tid & 31;
+    const int p = l >> 3, q = l & 7, odd = q >> 2;
+    DqLane d;
+    d.row = 2 * w + odd;
+    d.c16 = 4 * (p ^ odd) + (q & 3);
+    return d;
+}
+
+// Packed weights of one stage held by a thread: kDqRows rows x 16 columns.
 template <int MODE>
-__device__ __forceinline__ void dequant_stage(const uint8_t* pt, uint8_t* bt, const GemmArgs& a, const TileInfo& ti,
-                                              int kt, int tid) {
+struct PackedRegs {
+    uint4 q[kDqRows];  // fp4 / int4 use only .x/.y of each
+};
+
+template <int MODE>
+__device__ __forceinline__ void load_packed(PackedRegs<MODE>& r, const uint8_t* __restrict__ w, const GemmArgs& a,
+                                            const TileInfo& ti, int kt, const DqLane& d) {
     using T = GmTraits<MODE>;
-    const int c16 = tid & 15;   // 16 output columns c16*16 .. c16*16+15
-    const int rbase = tid >> 4; // rows rbase + 16 j
+    const size_t row_bytes = T::kNibbles ? (size_t)a.N / 2 : (size_t)a.N;
+    const uint8_t* base = w + ((size_t)ti.g * a.K + (size_t)kt * kBK + d.row) * row_bytes +
+                          (T::kNibbles ? (ti.n0 >> 1) + d.c16 * 8 : ti.n0 + d.c16 * 16);
+#pragma unroll
+    for (int j = 0; j < kDqRows; ++j) {
+        const uint8_t* p = base + (size_t)(kDqRowStep * j) * row_bytes;
+        if constexpr (T::kNibbles) {
+            const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+            r.q[j] = make_uint4(v.x, v.y, 0u, 0u);
+        } else {
+            r.q[j] = __ldg(reinterpret_cast<const uint4*>(p));
+        }
+    }
+}
+
+template <int MODE>
+__device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint8_t* bt, const GemmArgs& a,
+                                              const TileInfo& ti, int kt, const DqLane& d) {
+    const int c16 = d.c16;
     float sf = 1.f;
     if constexpr (MODE == B200MOE_CT_FP8) {
         sf = __ldg(static_cast<const float*>(a.scale) +
                    ((size_t)ti.g * (a.K >> 7) + ((kt * kBK) >> 7)) * (a.N >> 7) + ((ti.n0 + c16 * 16) >> 7));
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int k = rbase + 16 * j;
+    for (int j = 0; j < kDqRows; ++j) {
+        const int k = d.row + kDqRowStep * j;
+        const uint4 q = r.q[j];
         uint32_t o[8];
         if constexpr (MODE == B200MOE_CT_INT8) {
-            const uint4 q = *reinterpret_cast<const uint4*>(pt + k * T::kPRowBytes + c16 * 16);
             s8x4_to_bf16(q.x, o[0], o[1]);
             s8x4_to_bf16(q.y, o[2], o[3]);
             s8x4_to_bf16(q.z, o[4], o[5]);
             s8x4_to_bf16(q.w, o[6], o[7]);
         } else if constexpr (MODE == B200MOE_CT_FP8) {
-            const uint4 q = *reinterpret_cast<const uint4*>(pt + k * T::kPRowBytes + c16 * 16);
             const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -140,14 +207,13 @@ __device__ __forceinline__ void dequant_stage(const uint8_t* pt, uint8_t* bt, co
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
                     const uint32_t p = prmt(w4[i], 0u, 0x0444u | (b << 12));
-                    const uint32_t d = ((p >> 4) & 0x07F00000u) | (p & 0x80000000u);
-                    f[b] = (__uint_as_float(d) * 1.329227995784916e36f) * sf;  // exact * 2^120, then fp32 scale
+                    const uint32_t dd = ((p >> 4) & 0x07F00000u) | (p & 0x80000000u);
+                    f[b] = (__uint_as_float(dd) * 1.329227995784916e36f) * sf;  // exact * 2^120, then fp32 scale
                 }
                 o[2 * i] = pack_bf16x2(f[0], f[1]);
                 o[2 * i + 1] = pack_bf16x2(f[2], f[3]);
             }
         } else {  // FP4: 8 bytes = 16 codes, bf16 scale per 16 k rows per column
-            const uint2 q = *reinterpret_cast<const uint2*>(pt + k * T::kPRowBytes + c16 * 8);
             const uint4* sp = reinterpret_cast<const uint4*>(
                 static_cast<const __nv_bfloat16*>(a.scale) +
                 ((size_t)ti.g * (a.K >> 4) + ((kt * kBK + k) >> 4)) * a.N + ti.n0 + c16 * 16);
@@ -165,17 +231,39 @@ __device__ __forceinline__ void dequant_stage(const uint8_t* pt, uint8_t* bt, co
     }
 }
 
+// Walks the (tile, k-stage) sequence of this CTA; the dequant warps run two of these, one for
+// the stage being converted and one kPrefetch stages ahead for the loads.
+struct StageIter {
+    int t, kt;
+    TileInfo ti;
+    bool valid;
+};
+__device__ __forceinline__ void iter_start(StageIter& it, int n_tiles, const int* tile_prefix, const int* row_start,
+                                           int G, int n_nt) {
+    it.t = blockIdx.x;
+    it.kt = 0;
+    it.valid = it.t < n_tiles;
+    if (it.valid) it.ti = locate_tile(it.t, tile_prefix, row_start, G, n_nt);
+}
+__device__ __forceinline__ void iter_next(StageIter& it, int n_kt, int n_tiles, const int* tile_prefix,
+                                          const int* row_start, int G, int n_nt) {
+    if (++it.kt < n_kt) return;
+    it.kt = 0;
+    it.t += gridDim.x;
+    it.valid = it.t < n_tiles;
+    if (it.valid) it.ti = locate_tile(it.t, tile_prefix, row_start, G, n_nt);
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                    const GemmArgs a) {
+                    const uint8_t* __restrict__ weight, const GemmArgs a) {
     using T = GmTraits<MODE>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* a_ring = base;
     uint8_t* b_ring = a_ring + kNA * kATileBytes;
-    uint8_t* p_ring = b_ring + kNB * kBTileBytes;
-    GmBarriers* sb = reinterpret_cast<GmBarriers*>(p_ring + kNP * T::kPTileBytes);
+    GmBarriers* sb = reinterpret_cast<GmBarriers*>(b_ring + kNB * kBTileBytes);
     int* row_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sb) + 256);
     int* tile_prefix = row_start + (a.G + 1);
 
@@ -194,8 +282,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         sb->n_tiles = acc;
         sb->abort = 0;
         for (int i = 0; i < kNA; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->a_full[i]), 1); ptx::mbar_init(ptx::smem_u32(&sb->a_empty[i]), 1); }
-        for (int i = 0; i < kNP; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->p_full[i]), 1); ptx::mbar_init(ptx::smem_u32(&sb->p_empty[i]), kDqWarps); }
-        for (int i = 0; i < kNB; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->b_full[i]), kDqWarps); ptx::mbar_init(ptx::smem_u32(&sb->b_empty[i]), 1); }
+        for (int i = 0; i < kNB; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->b_full[i]), kDqGroupWarps); ptx::mbar_init(ptx::smem_u32(&sb->b_empty[i]), 1); }
         for (int i = 0; i < 2; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->t_full[i]), 1); ptx::mbar_init(ptx::smem_u32(&sb->t_empty[i]), 4); }
         ptx::mbar_init(ptx::smem_u32(&sb->drain), 1);
         ptx::fence_mbar_init();
@@ -215,9 +302,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
     if (warp == kWarpA) {
         // ------------------------------ x-tile producer ------------------------------
+        // Also pulls the packed weight tile of the stage kL2Ahead further on into L2 (a TMA
+        // prefetch has no shared-memory destination), so the dequant warps' register loads, which
+        // can only run a stage or two ahead, find their data in L2 instead of waiting on HBM.
         if (lane == 0) {
             uint32_t ia = 0;
             bool ok = true;
+            StageIter far;
+            iter_start(far, n_tiles, tile_prefix, row_start, a.G, n_nt);
+            for (int i = 0; i < kL2Ahead && far.valid; ++i) {
+                ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0, far.ti.g * a.K + far.kt * kBK);
+                iter_next(far, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
+            }
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
                 for (int kt = 0; kt < n_kt; ++kt, ++ia) {
@@ -226,61 +322,51 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     const uint32_t bar = ptx::smem_u32(&sb->a_full[s]);
                     ptx::mbar_arrive_expect_tx(bar, kATileBytes);
                     ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes), &tmap_x, bar, kt * kBK, ti.row0);
+                    if (far.valid) {
+                        ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0,
+                                                far.ti.g * a.K + far.kt * kBK);
+                        iter_next(far, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
+                    }
                 }
             }
             if (!ok)
                 for (uint32_t j = (ia > kNA ? ia - kNA : 0); j < ia; ++j)
                     (void)ptx::mbar_wait(ptx::smem_u32(&sb->a_full[j % kNA]), (j / kNA) & 1);
         }
-    } else if (warp == kWarpP) {
-        // ------------------------------ packed-weight producer ------------------------------
-        if (lane == 0) {
-            uint32_t ip = 0;
-            bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-                const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
-                for (int kt = 0; kt < n_kt; ++kt, ++ip) {
-                    const uint32_t s = ip % kNP, ph = (ip / kNP) & 1;
-                    if (ip >= kNP && !gm_wait(&sb->p_empty[s], ph ^ 1, sb, a.status, 20 + (int)s)) { ok = false; break; }
-                    const uint32_t bar = ptx::smem_u32(&sb->p_full[s]);
-                    ptx::mbar_arrive_expect_tx(bar, T::kPTileBytes);
-                    ptx::tma_load_2d(ptx::smem_u32(p_ring + s * T::kPTileBytes), &tmap_w, bar,
-                                     T::kNibbles ? ti.n0 / 2 : ti.n0, ti.g * a.K + kt * kBK);
-                }
-            }
-            if (!ok)
-                for (uint32_t j = (ip > kNP ? ip - kNP : 0); j < ip; ++j)
-                    (void)ptx::mbar_wait(ptx::smem_u32(&sb->p_full[j % kNP]), (j / kNP) & 1);
-        }
     } else if (warp == kWarpMma) {
         // ------------------------------ MMA issuer ------------------------------
+        // One thread feeds the tensor core; its per-stage instruction count bounds the MMA rate, so
+        // ring positions and parities are carried incrementally and the shared-memory descriptors
+        // are a 64-bit base plus a small stage / k offset.
         if (lane == 0) {
             const uint32_t idesc = ptx::umma_idesc_bf16(kBM, kBN, true);
-            uint32_t ia = 0, ib = 0, it = 0;
+            // A: K-major, 8-row groups 1024 B apart, 32 B per 16 k inside the swizzle atom
+            const uint64_t da0 = ptx::umma_desc_sw128(ptx::smem_u32(a_ring), 0, 1024);
+            // B: MN-major, 64-column blocks kBK*128 B apart (LBO), 8-k groups 1024 B apart (SBO)
+            const uint64_t db0 = ptx::umma_desc_sw128(ptx::smem_u32(b_ring), kBK * 128, 1024);
+            uint32_t sa = 0, pha = 0, sbb = 0, phb = 0, it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++it) {
                 const uint32_t ab = it & 1, pht = (it >> 1) & 1;
                 if (it >= 2 && !gm_wait(&sb->t_empty[ab], pht ^ 1, sb, a.status, 30 + (int)ab)) { ok = false; break; }
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + ab * kBN;
-                for (int kt = 0; kt < n_kt; ++kt, ++ia, ++ib) {
-                    const uint32_t sa = ia % kNA, pha = (ia / kNA) & 1;
-                    const uint32_t sbb = ib % kNB, phb = (ib / kNB) & 1;
+                uint32_t accumulate = 0;
+                for (int kt = 0; kt < n_kt; ++kt) {
                     if (!gm_wait(&sb->a_full[sa], pha, sb, a.status, 40 + (int)sa)) { ok = false; break; }
                     if (!gm_wait(&sb->b_full[sbb], phb, sb, a.status, 50 + (int)sbb)) { ok = false; break; }
                     ptx::tc_fence_after();
-                    const uint32_t a_addr = ptx::smem_u32(a_ring + sa * kATileBytes);
-                    const uint32_t b_addr = ptx::smem_u32(b_ring + sbb * kBTileBytes);
+                    const uint64_t da = da0 + (uint64_t)(sa * (kATileBytes >> 4));
+                    const uint64_t db = db0 + (uint64_t)(sbb * (kBTileBytes >> 4));
 #pragma unroll
                     for (int k16 = 0; k16 < kBK / 16; ++k16) {
-                        // A: K-major, 8-row groups 1024 B apart, 32 B per 16 k inside the swizzle atom
-                        const uint64_t da = ptx::umma_desc_sw128(a_addr + k16 * 32, 0, 1024);
-                        // B: MN-major, 64-column blocks kBK*128 B apart (LBO), 8-k groups 1024 B apart (SBO)
-                        const uint64_t db = ptx::umma_desc_sw128(b_addr + k16 * 2048, kBK * 128, 1024);
-                        ptx::umma_bf16(d_tmem, da, db, idesc, (kt > 0 || k16 > 0) ? 1u : 0u);
+                        ptx::umma_bf16(d_tmem, da + (uint64_t)(k16 * 2), db + (uint64_t)(k16 * 128), idesc, accumulate);
+                        accumulate = 1;
                     }
                     ptx::umma_commit(ptx::smem_u32(&sb->a_empty[sa]));
                     ptx::umma_commit(ptx::smem_u32(&sb->b_empty[sbb]));
+                    if (++sa == kNA) { sa = 0; pha ^= 1; }
+                    if (++sbb == kNB) { sbb = 0; phb ^= 1; }
                 }
                 if (ok) ptx::umma_commit(ptx::smem_u32(&sb->t_full[ab]));
             }
@@ -339,24 +425,44 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
     } else if (warp >= kWarpDq0) {
         // ------------------------------ dequant ------------------------------
-        const int tid = threadIdx.x - kWarpDq0 * 32;
-        uint32_t ip = 0, ib = 0;
+        const int dq_tid = threadIdx.x - kWarpDq0 * 32;
+        const int grp = dq_tid / (kDqGroupWarps * 32);
+        const DqLane d = dq_lane(dq_tid % (kDqGroupWarps * 32));
+        StageIter cur, pf;
+        iter_start(cur, n_tiles, tile_prefix, row_start, a.G, n_nt);
+        for (int i = 0; i < grp && cur.valid; ++i) iter_next(cur, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
+        pf = cur;
+        PackedRegs<MODE> regs[kPrefetch];
+#pragma unroll
+        for (int u = 0; u < kPrefetch; ++u) {
+            if (pf.valid) {
+                load_packed<MODE>(regs[u], weight, a, pf.ti, pf.kt, d);
+#pragma unroll
+                for (int i = 0; i < kDqGroups; ++i)
+                    if (pf.valid) iter_next(pf, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
+            }
+        }
+        uint32_t ib = grp;
         bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-            const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
-            for (int kt = 0; kt < n_kt; ++kt, ++ip, ++ib) {
-                const uint32_t sp = ip % kNP, php = (ip / kNP) & 1;
+        while (cur.valid && ok) {
+#pragma unroll
+            for (int u = 0; u < kPrefetch; ++u) {
+                if (!cur.valid) break;
                 const uint32_t sbb = ib % kNB, phb = (ib / kNB) & 1;
-                bool got = gm_wait(&sb->p_full[sp], php, sb, a.status, 70 + (int)sp);
-                if (got && ib >= kNB) got = gm_wait(&sb->b_empty[sbb], phb ^ 1, sb, a.status, 80 + (int)sbb);
+                bool got = true;
+                if (ib >= kNB) got = gm_wait(&sb->b_empty[sbb], phb ^ 1, sb, a.status, 80 + (int)sbb);
                 if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-                dequant_stage<MODE>(p_ring + sp * T::kPTileBytes, b_ring + sbb * kBTileBytes, a, ti, kt, tid);
+                convert_stage<MODE>(regs[u], b_ring + sbb * kBTileBytes, a, cur.ti, cur.kt, d);
                 ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
                 __syncwarp();
-                if (lane == 0) {
-                    ptx::mbar_arrive(ptx::smem_u32(&sb->b_full[sbb]));
-                    ptx::mbar_arrive(ptx::smem_u32(&sb->p_empty[sp]));
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->b_full[sbb]));
+                if (pf.valid) load_packed<MODE>(regs[u], weight, a, pf.ti, pf.kt, d);
+#pragma unroll
+                for (int i = 0; i < kDqGroups; ++i) {
+                    if (pf.valid) iter_next(pf, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
+                    if (cur.valid) iter_next(cur, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
                 }
+                ib += kDqGroups;
             }
         }
     }
@@ -386,11 +492,8 @@ __global__ void rowsum_kernel(const __nv_bfloat16* __restrict__ x, float* __rest
     if ((threadIdx.x & 31) == 0) out[row] = s;
 }
 
-template <int MODE>
 static size_t gm_smem_bytes(int G) {
-    using T = GmTraits<MODE>;
-    return 1024 + (size_t)kNA * kATileBytes + (size_t)kNB * kBTileBytes + (size_t)kNP * T::kPTileBytes + 256 +
-           sizeof(int) * 2 * (size_t)(G + 1);
+    return 1024 + (size_t)kNA * kATileBytes + (size_t)kNB * kBTileBytes + 256 + sizeof(int) * 2 * (size_t)(G + 1);
 }
 
 template <int MODE>
@@ -401,10 +504,10 @@ static int gm_launch(const void* x, const void* w, const GemmArgs& a, cudaStream
     if (rc != B200MOE_OK) return rc;
     rc = make_tensor_map_2d(&tw, w, 1, (uint64_t)a.G * a.K, T::kNibbles ? a.N / 2 : a.N, kBK, T::kPRowBytes, false);
     if (rc != B200MOE_OK) return rc;
-    const size_t smem = gm_smem_bytes<MODE>(a.G);
+    const size_t smem = gm_smem_bytes(a.G);
     B200MOE_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem));
-    grouped_gemm_kernel<MODE><<<sm_count(), kGemmThreads, smem, stream>>>(tx, tw, a);
+    grouped_gemm_kernel<MODE><<<sm_count(), kGemmThreads, smem, stream>>>(tx, tw, static_cast<const uint8_t*>(w), a);
     B200MOE_CUDA_TRY(cudaGetLastError());
     return B200MOE_OK;
 }

@@ -86,6 +86,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
         : "memory");
 }
 
+// 2-D tile prefetch global -> L2 (no shared-memory destination, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(m)),
+                 "r"(x), "r"(y)
+                 : "memory");
+}
+
 // ---- tcgen05 / TMEM ------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
@@ -148,6 +155,8 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t
 }
 
 // Instruction descriptor, kind::f16: D fp32, A and B bf16, A K-major, B major as given.
+// (Both operands must carry the same 16-bit format: a bf16 A with an fp16 B is rejected by the
+// hardware as an illegal instruction.)
 __device__ __forceinline__ uint32_t umma_idesc_bf16(int m, int n, bool b_mn_major) {
     uint32_t d = 0;
     d |= 1u << 4;                      // D format: f32

@@ -62,7 +62,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
         return self
@@ -204,7 +204,7 @@ def time_launches(fn, n_warm, n_iter):
     return statistics.median(a.elapsed_time(b) for a, b in evs)
 
 
-def kernel_lines(peaks, quick=False):
+def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
     import torch
 
     import ascend_kernel_b200 as ak
@@ -217,10 +217,11 @@ def kernel_lines(peaks, quick=False):
     M, K = c["x"].shape
     G, _, N = c["weight"].shape
     y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-    ms = time_launches(lambda: ak.grouped_gemm(c["x"], c["weight"], c["scale"], c["offset"], c["counts"], "int8", y,
+    if "gemm" in which:
+      ms = time_launches(lambda: ak.grouped_gemm(c["x"], c["weight"], c["scale"], c["offset"], c["counts"], "int8", y,
                                                group_list_type=1), 3, 10)
-    flops = 2.0 * M * K * N
-    out["grouped_gemm_prefill_int8"] = {
+      flops = 2.0 * M * K * N
+      out["grouped_gemm_prefill_int8"] = {
         "ms": ms, "tflops": flops / ms / 1e9, "frac_of_measured_sustained": flops / ms / 1e9 / peaks["bf16_tflops_sustained"],
         "frac_of_measured_burst": flops / ms / 1e9 / peaks["bf16_tflops"], "frac_of_spec_2250": flops / ms / 1e9 / 2250.0,
         "shape": {"M": M, "K": K, "N": N, "G": G, "active_experts": int((c["counts"] > 0).sum())}}
@@ -230,15 +231,16 @@ def kernel_lines(peaks, quick=False):
     xv = c["x"][:Mv].contiguous()
     yv = torch.empty(Mv, N, dtype=torch.bfloat16, device=dev)
     n_act = int((counts > 0).sum())
-    ms = time_launches(lambda: ak.grouped_soft_gemv(xv, c["weight"], c["scale"], counts, "int8", yv,
+    if "gemv" in which:
+      ms = time_launches(lambda: ak.grouped_soft_gemv(xv, c["weight"], c["scale"], counts, "int8", yv,
                                                     group_list_type=1), 3, 10)
-    by = n_act * K * N + 2.0 * Mv * K + 2.0 * Mv * N + n_act * N * 2
-    out["grouped_gemv_decode_int8_pass1"] = {"ms": ms, "gbs": by / ms / 1e6, "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
+      by = n_act * K * N + 2.0 * Mv * K + 2.0 * Mv * N + n_act * N * 2
+      out["grouped_gemv_decode_int8_pass1"] = {"ms": ms, "gbs": by / ms / 1e6, "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
                                              "frac_of_spec_8000": by / ms / 1e6 / 8000.0,
                                              "shape": {"M": Mv, "K": K, "N": N, "G": G, "active_experts": n_act}}
     del c, y, xv, yv
     torch.cuda.empty_cache()
-    if not quick:
+    if not quick and "gemv" in which:
         gen = torch.Generator(device=dev).manual_seed(11)
         K2, N2 = 2048, 7168
         w2 = inputs.int8_weights(G, K2, N2, gen, dev)
@@ -252,6 +254,8 @@ def kernel_lines(peaks, quick=False):
                                                  "shape": {"M": Mv, "K": K2, "N": N2, "G": G, "active_experts": n_act}}
         del w2, s2, x2, y2
         torch.cuda.empty_cache()
+    if "dequant" not in which:
+        return out
     # ---- FP4 dequant (configuration 2) ----
     d = inputs.config2(dev) if not quick else inputs.config2(dev, shape=(32, 2048, 7168))
     n = d["codes"].numel() * 2
@@ -395,9 +399,11 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="moe", choices=["moe", "gemm", "gemv", "dequant"],
+                    help="moe: the benchmark line; others: one kernel alone (for profiling)")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel lines (N=1)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--quick", action="store_true", help="small shapes for the per-kernel lines (profiling)")
@@ -406,6 +412,16 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "moe":
+        # one hot-path kernel alone at its own benchmark configuration (--quick: a small case of
+        # the same kernel, sized for profiler captures)
+        import torch
+
+        torch.cuda.set_device(0)
+        peaks, kind = load_peaks()
+        line = {"workload": args.workload, "quick": args.quick, "peaks": {**peaks, "kind": kind},
+                "kernels": kernel_lines(peaks, quick=args.quick, which=(args.workload,))}
+        print(json.dumps(line), flush=True)
     else:
         run_ours(args)
 
