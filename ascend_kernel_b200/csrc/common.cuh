@@ -110,6 +110,22 @@ __device__ __forceinline__ void s8x4_to_bf16(uint32_t w, uint32_t& o01, uint32_t
     o23 = add_bf16x2(fma_bf16x2(hi23, k16, kneg), lo23);
 }
 
+// Four signed int8 (one 32-bit word) -> four bf16, exact, in seven instructions.
+// byte = low7 - 128*sign: (w & 0x7F) | 0x4300 is the bf16 128+low7 and (w & 0x80) | 0x4300 is the
+// bf16 128 or 256, so one bf16x2 subtraction per two bytes yields the value.  The masks pick
+// bytes 0 and 2 of the word (and 1 and 3 after a shift): `o02` holds elements (0, 2), `o13`
+// elements (1, 3).
+__device__ __forceinline__ void s8x4_to_bf16_even_odd(uint32_t w, uint32_t& o02, uint32_t& o13) {
+    uint32_t lo, sg;
+    asm("lop3.b32 %0, %1, 0x007F007F, 0x43004300, 0xEA;" : "=r"(lo) : "r"(w));  // (w & m) | c
+    asm("lop3.b32 %0, %1, 0x00800080, 0x43004300, 0xEA;" : "=r"(sg) : "r"(w));
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(o02) : "r"(lo), "r"(sg));
+    const uint32_t v = w >> 8;
+    asm("lop3.b32 %0, %1, 0x007F007F, 0x43004300, 0xEA;" : "=r"(lo) : "r"(v));
+    asm("lop3.b32 %0, %1, 0x00800080, 0x43004300, 0xEA;" : "=r"(sg) : "r"(v));
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(o13) : "r"(lo), "r"(sg));
+}
+
 // Row boundaries of every expert from the device-side group_list, clamped into [0, M] and made
 // monotone so no later index can leave the tensors; a violation is reported in the status words.
 // Executed by a whole CTA; row_start has G+1 entries in shared memory.  G <= kMaxExperts.

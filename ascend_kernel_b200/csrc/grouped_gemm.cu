@@ -3,20 +3,23 @@
 //
 //   y[rows of expert g] = bf16( x[rows of expert g] @ dequant(W[g]) ),  fp32 accumulation in TMEM.
 //
-// One CTA per SM walks a static round-robin over output tiles of 128 rows x 256 columns.  The
+// One CTA per SM walks a static round-robin over output tiles of up to 256 rows x 256 columns:
+// two UMMA 128x256x16 instructions (rows 0-127 and 128-255 of the tile, one TMEM accumulator of
+// 256 columns each) share every dequantised weight stage, so the CUDA-core dequant work per
+// tensor-core flop is half that of a 128-row tile; tiles with at most 128 rows issue one.  The
 // tile list is derived inside the kernel from the device-side group_list (prefix sum over the
 // experts' tile counts kept in shared memory, binary search per tile), so there is no host
 // synchronisation and no schedule in global memory.
 //
-// Warp roles (24 warps):
-//   warp 0      TMA producer of x tiles      (128 rows x 64 k, bf16, 128-byte swizzle, K-major A)
-//   warp 2      TMEM allocation + tcgen05.mma issue (one elected lane), UMMA 128x256x16
-//   warps 4-7   epilogue: tcgen05.ld of the accumulator, scale/offset in fp32, bf16 stores
-//   warps 8-23  dequant, two groups of 8 warps taking alternate k-stages: packed weights global ->
+// Warp roles (28 warps):
+//   warp 0      TMA producer of x tiles (one or two boxes of 128 rows x 64 k, bf16, 128-byte
+//               swizzle, K-major A) and L2 prefetch of the packed weight tiles further ahead
+//   warp 2      TMEM allocation + tcgen05.mma issue (one elected lane)
+//   warps 4-11  epilogue, four warps per accumulator: tcgen05.ld, scale/offset in fp32, bf16 stores
+//   warps 12-27 dequant, two groups of 8 warps taking alternate k-stages: packed weights global ->
 //               registers (128-bit coalesced loads, prefetched two of the group's stages ahead) ->
 //               bf16 tile in the UMMA MN-major 128-byte-swizzle layout
-// Rings: 5 x-tile stages, 4 bf16 weight stages, 2 accumulators of 256 TMEM columns (the epilogue
-// of tile i overlaps the main loop of tile i+1).  Shared-memory bandwidth bounds this kernel (the
+// Rings: 3 x-tile stages of 32 KB, 3 bf16 weight stages of 32 KB.  Shared-memory bandwidth bounds this kernel (the
 // tensor core alone reads 48 KB per 64-k stage), so packed weights go through registers, not
 // through a shared-memory staging ring, and the bf16 tile is written without bank conflicts.
 // Weights never make a round trip through global memory.  Every wait is bounded; on expiry the
@@ -28,11 +31,12 @@
 namespace b200moe {
 
 constexpr int kBM = 128, kBN = 256, kBK = 64;
-constexpr int kNA = 5, kNB = 4;
+constexpr int kTileM = 2 * kBM;  // rows of an output tile (two MMA row halves)
+constexpr int kNA = 3, kNB = 3;
 constexpr int kPrefetch = 2;  // packed stages held in registers ahead of the one being converted
 constexpr int kL2Ahead = 8;   // stages by which the L2 prefetch of packed weights leads the x-tile loads
-constexpr int kGemmThreads = 768;
-constexpr int kWarpA = 0, kWarpMma = 2, kWarpEpi0 = 4, kWarpDq0 = 8;
+constexpr int kGemmThreads = 896;
+constexpr int kWarpA = 0, kWarpMma = 2, kWarpEpi0 = 4, kEpiWarps = 8, kWarpDq0 = 12;
 // The dequant warps form kDqGroups groups; group i converts the k-stages i, i + kDqGroups, ...
 // so a warp pays the barrier handshake once per kDqGroups stages and the groups overlap each
 // other's waits.
@@ -40,8 +44,9 @@ constexpr int kDqGroups = 2;
 constexpr int kDqGroupWarps = 8;
 constexpr int kDqRowStep = 2 * kDqGroupWarps;  // a warp owns two rows; the group covers this many per pass
 constexpr int kDqRows = kBK / kDqRowStep;      // k rows converted by a thread per stage
-constexpr int kSuperRows = 16;  // m-tiles per L2 super-tile
-constexpr int kATileBytes = kBM * kBK * 2;
+constexpr int kSuperRows = 8;  // m-tiles per L2 super-tile
+constexpr int kAHalfBytes = kBM * kBK * 2;   // one 128-row box
+constexpr int kATileBytes = 2 * kAHalfBytes;  // an x stage holds both row halves
 constexpr int kBTileBytes = kBK * kBN * 2;
 constexpr uint32_t kTmemCols = 512;
 
@@ -65,7 +70,7 @@ struct GmTraits {
 struct GmBarriers {
     uint64_t a_full[kNA], a_empty[kNA];
     uint64_t b_full[kNB], b_empty[kNB];
-    uint64_t t_full[2], t_empty[2];
+    uint64_t t_full, t_empty;
     uint64_t drain;
     uint32_t tmem_base;
     int abort;
@@ -74,6 +79,7 @@ struct GmBarriers {
 
 struct TileInfo {
     int g, row0, row_end, n0;
+    int halves;  // 1: at most 128 rows in the tile, 2: more
 };
 
 // Bounded wait on a pipeline barrier.  The fast path is a single try_wait; the slow path polls,
@@ -114,7 +120,7 @@ __device__ __forceinline__ TileInfo locate_tile(int t, const int* tile_prefix, c
     const int g = lo;
     const int j = t - tile_prefix[g];
     const int r0 = row_start[g], r1 = row_start[g + 1];
-    const int mt = (r1 - r0 + kBM - 1) / kBM;
+    const int mt = (r1 - r0 + kTileM - 1) / kTileM;
     // super-tiles of up to kSuperRows m-tiles x all n-tiles keep x rows and the expert's weights
     // L2-resident while they are shared by concurrently running CTAs
     const int per_super = kSuperRows * n_nt;
@@ -125,8 +131,9 @@ __device__ __forceinline__ TileInfo locate_tile(int t, const int* tile_prefix, c
     TileInfo ti;
     ti.g = g;
     ti.n0 = (jj / h) * kBN;
-    ti.row0 = r0 + (base + jj % h) * kBM;
+    ti.row0 = r0 + (base + jj % h) * kTileM;
     ti.row_end = r1;
+    ti.halves = (r1 - ti.row0) > kBM ? 2 : 1;
     return ti;
 }
 
@@ -195,10 +202,11 @@ __device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint8_t
         const uint4 q = r.q[j];
         uint32_t o[8];
         if constexpr (MODE == B200MOE_CT_INT8) {
-            s8x4_to_bf16(q.x, o[0], o[1]);
-            s8x4_to_bf16(q.y, o[2], o[3]);
-            s8x4_to_bf16(q.z, o[4], o[5]);
-            s8x4_to_bf16(q.w, o[6], o[7]);
+            // tile columns 4i..4i+3 hold weight columns 4i, 4i+2, 4i+1, 4i+3 (undone in the epilogue)
+            s8x4_to_bf16_even_odd(q.x, o[0], o[1]);
+            s8x4_to_bf16_even_odd(q.y, o[2], o[3]);
+            s8x4_to_bf16_even_odd(q.z, o[4], o[5]);
+            s8x4_to_bf16_even_odd(q.w, o[6], o[7]);
         } else if constexpr (MODE == B200MOE_CT_FP8) {
             const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -276,14 +284,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         int acc = 0;
         tile_prefix[0] = 0;
         for (int g = 0; g < a.G; ++g) {
-            acc += ((row_start[g + 1] - row_start[g] + kBM - 1) / kBM) * n_nt;
+            acc += ((row_start[g + 1] - row_start[g] + kTileM - 1) / kTileM) * n_nt;
             tile_prefix[g + 1] = acc;
         }
         sb->n_tiles = acc;
         sb->abort = 0;
         for (int i = 0; i < kNA; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->a_full[i]), 1); ptx::mbar_init(ptx::smem_u32(&sb->a_empty[i]), 1); }
         for (int i = 0; i < kNB; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->b_full[i]), kDqGroupWarps); ptx::mbar_init(ptx::smem_u32(&sb->b_empty[i]), 1); }
-        for (int i = 0; i < 2; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->t_full[i]), 1); ptx::mbar_init(ptx::smem_u32(&sb->t_empty[i]), 4); }
+        ptx::mbar_init(ptx::smem_u32(&sb->t_full), 1);
+        ptx::mbar_init(ptx::smem_u32(&sb->t_empty), kEpiWarps);
         ptx::mbar_init(ptx::smem_u32(&sb->drain), 1);
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_x);
@@ -320,8 +329,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     const uint32_t s = ia % kNA, ph = (ia / kNA) & 1;
                     if (ia >= kNA && !gm_wait(&sb->a_empty[s], ph ^ 1, sb, a.status, 10 + (int)s)) { ok = false; break; }
                     const uint32_t bar = ptx::smem_u32(&sb->a_full[s]);
-                    ptx::mbar_arrive_expect_tx(bar, kATileBytes);
+                    ptx::mbar_arrive_expect_tx(bar, ti.halves * kAHalfBytes);
                     ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes), &tmap_x, bar, kt * kBK, ti.row0);
+                    if (ti.halves == 2)
+                        ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes + kAHalfBytes), &tmap_x, bar, kt * kBK,
+                                         ti.row0 + kBM);
                     if (far.valid) {
                         ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0,
                                                 far.ti.g * a.K + far.kt * kBK);
@@ -347,10 +359,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             uint32_t sa = 0, pha = 0, sbb = 0, phb = 0, it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++it) {
-                const uint32_t ab = it & 1, pht = (it >> 1) & 1;
-                if (it >= 2 && !gm_wait(&sb->t_empty[ab], pht ^ 1, sb, a.status, 30 + (int)ab)) { ok = false; break; }
+                const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
+                // the accumulators are single-buffered: the previous tile's epilogue must have drained them
+                if (it >= 1 && !gm_wait(&sb->t_empty, (it - 1) & 1, sb, a.status, 30)) { ok = false; break; }
                 ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + ab * kBN;
                 uint32_t accumulate = 0;
                 for (int kt = 0; kt < n_kt; ++kt) {
                     if (!gm_wait(&sb->a_full[sa], pha, sb, a.status, 40 + (int)sa)) { ok = false; break; }
@@ -359,69 +371,82 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     const uint64_t da = da0 + (uint64_t)(sa * (kATileBytes >> 4));
                     const uint64_t db = db0 + (uint64_t)(sbb * (kBTileBytes >> 4));
 #pragma unroll
-                    for (int k16 = 0; k16 < kBK / 16; ++k16) {
-                        ptx::umma_bf16(d_tmem, da + (uint64_t)(k16 * 2), db + (uint64_t)(k16 * 128), idesc, accumulate);
-                        accumulate = 1;
+                    for (int k16 = 0; k16 < kBK / 16; ++k16)
+                        ptx::umma_bf16(tmem_base, da + (uint64_t)(k16 * 2), db + (uint64_t)(k16 * 128), idesc,
+                                       accumulate | (uint32_t)k16);
+                    if (ti.halves == 2) {
+#pragma unroll
+                        for (int k16 = 0; k16 < kBK / 16; ++k16)
+                            ptx::umma_bf16(tmem_base + kBN, da + (uint64_t)((kAHalfBytes >> 4) + k16 * 2),
+                                           db + (uint64_t)(k16 * 128), idesc, accumulate | (uint32_t)k16);
                     }
+                    accumulate = 1;
                     ptx::umma_commit(ptx::smem_u32(&sb->a_empty[sa]));
                     ptx::umma_commit(ptx::smem_u32(&sb->b_empty[sbb]));
                     if (++sa == kNA) { sa = 0; pha ^= 1; }
                     if (++sbb == kNB) { sbb = 0; phb ^= 1; }
                 }
-                if (ok) ptx::umma_commit(ptx::smem_u32(&sb->t_full[ab]));
+                if (ok) ptx::umma_commit(ptx::smem_u32(&sb->t_full));
             }
             // drain: every issued MMA must have completed before TMEM is released
             ptx::umma_commit(ptx::smem_u32(&sb->drain));
             (void)ptx::mbar_wait(ptx::smem_u32(&sb->drain), 0);
         }
         __syncwarp();
-    } else if (warp >= kWarpEpi0 && warp < kWarpEpi0 + 4) {
+    } else if (warp >= kWarpEpi0 && warp < kWarpEpi0 + kEpiWarps) {
         // ------------------------------ epilogue ------------------------------
-        const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
+        const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31 are the ones this warp may read
+        const int half = (warp - kWarpEpi0) >> 2;     // which accumulator / row half of the tile
         const bool per_channel = (MODE == B200MOE_CT_INT8);
         const bool has_offset = per_channel && a.offset != nullptr;
         uint32_t it = 0;
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++it) {
             const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
-            const uint32_t ab = it & 1, pht = (it >> 1) & 1;
-            if (!__all_sync(0xffffffffu, gm_wait(&sb->t_full[ab], pht, sb, a.status, 60 + (int)ab))) break;
+            if (!__all_sync(0xffffffffu, gm_wait(&sb->t_full, it & 1, sb, a.status, 60))) break;
             ptx::tc_fence_after();
-            const int row = ti.row0 + quarter * 32 + lane;
-            const bool row_ok = row < ti.row_end;
-            const float rs = (has_offset && row_ok) ? __ldg(a.rowsum + row) : 0.f;
-            __nv_bfloat16* yrow = a.y + (size_t)row * a.N + ti.n0;
+            if (half < ti.halves) {
+                const int row = ti.row0 + half * kBM + quarter * 32 + lane;
+                const bool row_ok = row < ti.row_end;
+                const float rs = (has_offset && row_ok) ? __ldg(a.rowsum + row) : 0.f;
+                __nv_bfloat16* yrow = a.y + (size_t)row * a.N + ti.n0;
 #pragma unroll 1
-            for (int c = 0; c < kBN / 32; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32(tmem_base + ab * kBN + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
-                float sv = 1.f, sov = 0.f;
-                if (per_channel) {
-                    const size_t ci = (size_t)ti.g * a.N + ti.n0 + c * 32 + lane;
-                    sv = __bfloat162float(static_cast<const __nv_bfloat16*>(a.scale)[ci]);
-                    if (has_offset) sov = sv * __bfloat162float(a.offset[ci]);
-                }
-                ptx::tmem_ld_wait();
-                uint32_t o[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
+                for (int c = 0; c < kBN / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(tmem_base + half * kBN + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
+                    float sv = 1.f, sov = 0.f;
                     if (per_channel) {
-                        const float s0 = __shfl_sync(0xffffffffu, sv, 2 * j), s1 = __shfl_sync(0xffffffffu, sv, 2 * j + 1);
-                        const float so0 = __shfl_sync(0xffffffffu, sov, 2 * j), so1 = __shfl_sync(0xffffffffu, sov, 2 * j + 1);
-                        v0 = fmaf(so0, rs, s0 * v0);
-                        v1 = fmaf(so1, rs, s1 * v1);
+                        const size_t ci = (size_t)ti.g * a.N + ti.n0 + c * 32 + lane;
+                        sv = __bfloat162float(static_cast<const __nv_bfloat16*>(a.scale)[ci]);
+                        if (has_offset) sov = sv * __bfloat162float(a.offset[ci]);
                     }
-                    o[j] = pack_bf16x2(v0, v1);
-                }
-                if (row_ok) {
-                    uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
+                    ptx::tmem_ld_wait();
+                    uint32_t o[16];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) dst[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                    for (int j = 0; j < 16; ++j) {
+                        // output columns 2j, 2j+1; the int8 dequant stores columns (0,2,1,3) of every
+                        // group of four, so column c sits at accumulator position pos(c)
+                        constexpr bool kPerm = (MODE == B200MOE_CT_INT8);
+                        const int p0 = kPerm ? ((2 * j) & ~3) + (((2 * j) & 3) == 2 ? 1 : 0) : 2 * j;
+                        const int p1 = kPerm ? ((2 * j) & ~3) + (((2 * j) & 3) == 2 ? 3 : 2) : 2 * j + 1;
+                        float v0 = __uint_as_float(r[p0]), v1 = __uint_as_float(r[p1]);
+                        if (per_channel) {
+                            const float s0 = __shfl_sync(0xffffffffu, sv, 2 * j), s1 = __shfl_sync(0xffffffffu, sv, 2 * j + 1);
+                            const float so0 = __shfl_sync(0xffffffffu, sov, 2 * j), so1 = __shfl_sync(0xffffffffu, sov, 2 * j + 1);
+                            v0 = fmaf(so0, rs, s0 * v0);
+                            v1 = fmaf(so1, rs, s1 * v1);
+                        }
+                        o[j] = pack_bf16x2(v0, v1);
+                    }
+                    if (row_ok) {
+                        uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) dst[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                    }
                 }
             }
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->t_empty[ab]));
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->t_empty));
         }
     } else if (warp >= kWarpDq0) {
         // ------------------------------ dequant ------------------------------
