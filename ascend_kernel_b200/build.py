@@ -1,8 +1,8 @@
 """In-tree build of the native code: ``libb200moe.so`` (CUDA kernels + C ABI, nvcc, sm_100a) and
 the ``cinfer_ascendc`` torch extension (g++, thin binding over the C ABI).
 
-    python -m ascend_kernel_b200.build            # build what is stale
-    python -m ascend_kernel_b200.build --force
+    python ascend_kernel_b200/build.py            # build what is stale
+    python ascend_kernel_b200/build.py --force
 
 nvcc cross-compiles without a GPU.  Objects go to ``ascend_kernel_b200/build/``; the two shared
 objects land next to this file so they travel with the source tree.
