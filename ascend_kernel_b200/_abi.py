@@ -23,6 +23,7 @@ EXPORTS = [
     "b200moe_grouped_gemm", "b200moe_grouped_gemm_workspace_bytes", "b200moe_grouped_gemv",
     "b200moe_grouped_gemv_workspace_bytes", "b200moe_fp4_dequant", "b200moe_fp4_layout", "b200moe_silu_mul",
     "b200moe_gather_rows", "b200moe_combine", "b200moe_read_status", "b200moe_strerror", "b200moe_version",
+    "b200moe_grouped_gemm_int8_noalloc", "b200moe_grouped_gemm_int8_noalloc_max_rows", "b200moe_noalloc_read_status",
 ]
 
 
@@ -35,7 +36,7 @@ class B200MoeError(RuntimeError):
 def _load() -> ctypes.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m ascend_kernel_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python ascend_kernel_b200/build.py` "
             "(there is no CPU or PyTorch fallback for these operators)")
     lib = ctypes.CDLL(LIB_PATH)
     vp, i64, i32, sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
@@ -47,6 +48,12 @@ def _load() -> ctypes.CDLL:
     for f in (lib.b200moe_grouped_gemm_workspace_bytes, lib.b200moe_grouped_gemv_workspace_bytes):
         f.argtypes = [i64, i64, i64, i64, i32, i32]
         f.restype = sz
+    lib.b200moe_grouped_gemm_int8_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, vp]
+    lib.b200moe_grouped_gemm_int8_noalloc.restype = i32
+    lib.b200moe_grouped_gemm_int8_noalloc_max_rows.argtypes = []
+    lib.b200moe_grouped_gemm_int8_noalloc_max_rows.restype = i64
+    lib.b200moe_noalloc_read_status.argtypes = [ctypes.POINTER(ctypes.c_int32), vp]
+    lib.b200moe_noalloc_read_status.restype = i32
     lib.b200moe_fp4_dequant.argtypes = [vp, vp, vp, i64, i32, vp]
     lib.b200moe_fp4_dequant.restype = i32
     lib.b200moe_fp4_layout.argtypes = [vp, vp, i64, i64, i64, i32, vp]

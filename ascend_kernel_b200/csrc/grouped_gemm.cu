@@ -25,6 +25,8 @@
 // Weights never make a round trip through global memory.  Every wait is bounded; on expiry the
 // kernel records an error status, all roles wind down, copies in flight are given time to land
 // and TMEM is released.
+#include <mutex>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -607,4 +609,94 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
         w = ws;
     }
     return gm_launch<B200MOE_CT_FP4>(x, w, a, s);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------------------------
+// Some hosts of these kernels may not call cudaMalloc at all: a plug-in that runs inside another
+// framework's execution step, where every device allocation is owned by that framework's arena and
+// a foreign cudaMalloc would fragment or deadlock it; a real-time serving loop that forbids
+// allocation after start-up.  The regular
+// entry point asks such callers for a workspace they have no way to provide.  This one keeps the
+// kernel's scratch (two status words and one fp32 row sum per row of x) in a fixed array that is
+// part of the loaded library image, so the caller passes inputs and outputs only.
+namespace b200moe {
+
+constexpr long long kNoAllocMaxRows = 65536;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[B200MOE_STATUS_BYTES + kNoAllocMaxRows * sizeof(float)];
+
+// Device address of the scratch array on the current device, resolved once per device.  The array's
+// name is only a host-side handle: a kernel must be given the address cudaGetSymbolAddress returns.
+static int noalloc_scratch(void** out) {
+    static void* addr[64];
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200MOE_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(mu);
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) {
+            (void)cudaGetLastError();
+            return B200MOE_ERR_CUDA;
+        }
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return B200MOE_OK;
+}
+
+}  // namespace b200moe
+
+extern "C" int64_t b200moe_grouped_gemm_int8_noalloc_max_rows(void) { return kNoAllocMaxRows; }
+
+extern "C" int b200moe_grouped_gemm_int8_noalloc(const void* x, const void* weight, const void* scale,
+                                                 const void* offset, const int64_t* group_list, void* y, int64_t M,
+                                                 int64_t K, int64_t N, int64_t G, int group_list_type, void* stream) {
+    if (group_list_type != B200MOE_GROUP_LIST_CUMSUM && group_list_type != B200MOE_GROUP_LIST_COUNTS)
+        return B200MOE_ERR_ARGUMENT;
+    if (M < 0 || K <= 0 || N <= 0 || G <= 0 || G > kMaxExperts || K > 0x7FFFFFF0LL || N > 0x7FFFFFF0LL ||
+        G * K > 0x7FFFFFF0LL)
+        return B200MOE_ERR_SHAPE;
+    if (M > kNoAllocMaxRows) return B200MOE_ERR_NOALLOC_LIMIT;
+    if ((K % kBK) != 0 || (N % kBN) != 0) return B200MOE_ERR_SHAPE;
+    if (M == 0) return B200MOE_OK;
+    if (!x || !weight || !scale || !group_list || !y) return B200MOE_ERR_NULL_POINTER;
+    if (!aligned16(x) || !aligned16(weight) || !aligned16(scale) || !aligned16(y) || (offset && !aligned16(offset)))
+        return B200MOE_ERR_ALIGNMENT;
+
+    void* scratch = nullptr;
+    const int rc = noalloc_scratch(&scratch);
+    if (rc != B200MOE_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the array keeps whatever the previous call left: the status words must start at zero
+    B200MOE_CUDA_TRY(cudaMemsetAsync(scratch, 0, 16, s));
+    GemmArgs a;
+    a.scale = scale;
+    a.offset = nullptr;
+    a.rowsum = nullptr;
+    a.group_list = group_list;
+    a.y = static_cast<__nv_bfloat16*>(y);
+    a.M = (int)M; a.K = (int)K; a.N = (int)N; a.G = (int)G;
+    a.gl_type = group_list_type;
+    a.status = static_cast<int*>(scratch);
+    if (offset != nullptr) {
+        float* rowsum = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + B200MOE_STATUS_BYTES);
+        rowsum_kernel<<<(unsigned)((M + 7) / 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rowsum, (int)M, (int)K);
+        B200MOE_CUDA_TRY(cudaGetLastError());
+        a.offset = static_cast<const __nv_bfloat16*>(offset);
+        a.rowsum = rowsum;
+    }
+    return gm_launch<B200MOE_CT_INT8>(x, weight, a, s);
+}
+
+extern "C" int b200moe_noalloc_read_status(int32_t out[2], void* stream) {
+    if (out == nullptr) return B200MOE_ERR_NULL_POINTER;
+    void* scratch = nullptr;
+    const int rc = noalloc_scratch(&scratch);
+    if (rc != B200MOE_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    B200MOE_CUDA_TRY(cudaMemcpyAsync(out, scratch, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    B200MOE_CUDA_TRY(cudaStreamSynchronize(s));
+    return B200MOE_OK;
 }

@@ -67,6 +67,7 @@ const char* b200moe_strerror(int code) {
         case B200MOE_ERR_ARGUMENT: return "invalid argument";
         case B200MOE_ERR_CUDA: return "CUDA call failed";
         case B200MOE_ERR_UNSUPPORTED: return "not implemented for this combination";
+        case B200MOE_ERR_NOALLOC_LIMIT: return "too many rows for the allocation-free entry point (see b200moe_grouped_gemm_int8_noalloc_max_rows)";
         default: return "unknown b200moe status";
     }
 }

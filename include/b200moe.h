@@ -44,7 +44,8 @@ enum {
     B200MOE_ERR_WORKSPACE = 5,    /* workspace missing or smaller than *_workspace_bytes()   */
     B200MOE_ERR_ARGUMENT = 6,     /* invalid enum value (group_list_type, layout, ...)       */
     B200MOE_ERR_CUDA = 7,         /* a CUDA runtime / driver call failed at launch           */
-    B200MOE_ERR_UNSUPPORTED = 8   /* valid request this build does not implement             */
+    B200MOE_ERR_UNSUPPORTED = 8,  /* valid request this build does not implement             */
+    B200MOE_ERR_NOALLOC_LIMIT = 9 /* more rows than the allocation-free entry point can hold  */
 };
 
 /* ---- compute types (the reference's `computeType` string) ------------------------------- */
@@ -81,6 +82,28 @@ int b200moe_grouped_gemm(const void* x, const void* weight, const void* scale, c
 
 size_t b200moe_grouped_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t G, int compute_type,
                                             int weight_layout);
+
+/* Allocation-free int8 grouped GEMM.  (No counterpart in the reference: its host binding always
+ * obtains a workspace with aclrtMalloc.)  For callers that must not allocate device memory -- a
+ * plug-in running inside another framework's step whose allocator owns all device memory, or a
+ * serving loop that forbids allocation after start-up -- and so cannot hand the regular entry
+ * point a workspace.  Same arguments and results as
+ * b200moe_grouped_gemm with compute_type int8 and the canonical layout, minus the workspace: the
+ * scratch (status words, one fp32 row sum per row of x) lives in a fixed array inside the library,
+ * 256 B + 4 B x b200moe_grouped_gemm_int8_noalloc_max_rows() = 256.25 KiB held on every GPU that
+ * loads the library, until the process exits.  M beyond that limit returns
+ * B200MOE_ERR_NOALLOC_LIMIT and launches nothing.  The call performs no cudaMalloc / cudaFree and
+ * uses no allocating library routine.  The first call on each device looks up the array's device
+ * address (cudaGetSymbolAddress): make that first call before any stream capture begins.  All calls
+ * share the one array: calls that overlap on the GPU (different streams) race on it; serialise
+ * them.  The device status words of the last call can be read with b200moe_noalloc_read_status. */
+int b200moe_grouped_gemm_int8_noalloc(const void* x, const void* weight, const void* scale, const void* offset,
+                                      const int64_t* group_list, void* y, int64_t M, int64_t K, int64_t N,
+                                      int64_t G, int group_list_type, void* stream);
+int64_t b200moe_grouped_gemm_int8_noalloc_max_rows(void);
+/* Copies the two device status words left by the last allocation-free call on the current device to
+ * the host (synchronises the stream). */
+int b200moe_noalloc_read_status(int32_t out[2], void* stream);
 
 /* Grouped GEMV for decode-sized expert batches (any number of rows per expert is accepted;
  * it is bandwidth-optimal up to 4 rows per expert).  Dequantised weights stay fp32, x is
