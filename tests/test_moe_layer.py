@@ -74,22 +74,30 @@ def _free_port():
     return p
 
 
-def _rank_main(rank, world, port, q):
+def _rank_main(rank, world, port, q, cuda=False, case_kw=None):
     import torch.distributed as dist
 
-    from ascend_kernel_b200.moe_layer import MoELayer
+    from ascend_kernel_b200.moe_layer import CudaRowOps, MoELayer
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    if cuda:
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    else:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        c = small_case()
+        c = small_case(**(case_kw or {}))
+        dev = torch.device("cuda", rank) if cuda else torch.device("cpu")
         el, tl = c["E"] // world, c["x"].shape[0] // world
         sl = slice(rank * el, (rank + 1) * el)
-        layer = MoELayer(c["w13"][sl], c["s13"][sl], c["o13"][sl], c["w2"][sl], c["s2"][sl], c["o2"][sl], c["E"],
-                         c["top_k"], dist.group.WORLD, TorchRowOps)
-        out = layer.forward(c["x"][rank * tl:(rank + 1) * tl], c["logits"][rank * tl:(rank + 1) * tl])
-        q.put((rank, out.view(torch.int16).numpy()))
+        w = [c[k][sl].contiguous().to(dev) for k in ("w13", "s13", "o13", "w2", "s2", "o2")]
+        layer = MoELayer(*w, c["E"], c["top_k"], dist.group.WORLD, CudaRowOps if cuda else TorchRowOps)
+        out = layer.forward(c["x"][rank * tl:(rank + 1) * tl].to(dev), c["logits"][rank * tl:(rank + 1) * tl].to(dev))
+        if cuda:
+            torch.cuda.synchronize()
+        q.put((rank, out.cpu().view(torch.int16).numpy()))
     finally:
         dist.destroy_process_group()
 
@@ -151,3 +159,27 @@ def test_aux_kernels_match_torch():
     got = ak.combine(src.cuda(), slot.cuda(), w.cuda()).cpu().float()
     want = (src[slot.long()].float() * w.unsqueeze(-1)).sum(1)
     assert torch.allclose(got, want, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.gpu
+def test_two_gpu_ranks_match_oracle():
+    """Expert-parallel layer over NCCL on two GPUs (skipped on a single-GPU box)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    kw = dict(T=200, H=256, E=8, I=256, k=2)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q, True, kw)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    c = small_case(**kw)
+    gold = O.moe_layer(c["x"], c["logits"], c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], c["top_k"])
+    out = torch.cat([torch.from_numpy(got[r]).view(torch.bfloat16) for r in range(2)])
+    close(out, gold)
