@@ -19,22 +19,26 @@
 //   warps 12-27 dequant, two groups of 8 warps taking alternate k-stages: packed weights global ->
 //               registers (128-bit coalesced loads, prefetched two of the group's stages ahead) ->
 //               bf16 tile in the UMMA MN-major 128-byte-swizzle layout
-// Rings: 3 x-tile stages of 32 KB, 3 bf16 weight stages of 32 KB.  Shared-memory bandwidth bounds this kernel (the
+// One ring of 3 stages (x boxes 32 KB + bf16 weights 32 KB), one full and one empty barrier per
+// stage: the single MMA-issuing thread pays one wait and one commit per stage.  Shared-memory bandwidth bounds this kernel (the
 // tensor core alone reads 48 KB per 64-k stage), so packed weights go through registers, not
 // through a shared-memory staging ring, and the bf16 tile is written without bank conflicts.
 // Weights never make a round trip through global memory.  Every wait is bounded; on expiry the
 // kernel records an error status, all roles wind down, copies in flight are given time to land
 // and TMEM is released.
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
+#include "gemm_args.cuh"
 #include "ptx.cuh"
 
 namespace b200moe {
 
 constexpr int kBM = 128, kBN = 256, kBK = 64;
 constexpr int kTileM = 2 * kBM;  // rows of an output tile (two MMA row halves)
-constexpr int kNA = 3, kNB = 3;
+constexpr int kNS = 3;  // ring stages, each an x stage (32 KB) and a bf16 weight stage (32 KB)
 constexpr int kPrefetch = 2;  // packed stages held in registers ahead of the one being converted
 constexpr int kL2Ahead = 8;   // stages by which the L2 prefetch of packed weights leads the x-tile loads
 constexpr int kGemmThreads = 896;
@@ -52,16 +56,6 @@ constexpr int kATileBytes = 2 * kAHalfBytes;  // an x stage holds both row halve
 constexpr int kBTileBytes = kBK * kBN * 2;
 constexpr uint32_t kTmemCols = 512;
 
-struct GemmArgs {
-    const void* scale;
-    const __nv_bfloat16* offset;
-    const float* rowsum;  // [M] sum_k x[m,k]; only read when offset != nullptr
-    const int64_t* group_list;
-    __nv_bfloat16* y;
-    int M, K, N, G, gl_type;
-    int* status;
-};
-
 template <int MODE>
 struct GmTraits {
     static constexpr bool kNibbles = (MODE == B200MOE_CT_FP4 || MODE == B200MOE_CT_INT4);
@@ -70,8 +64,8 @@ struct GmTraits {
 };
 
 struct GmBarriers {
-    uint64_t a_full[kNA], a_empty[kNA];
-    uint64_t b_full[kNB], b_empty[kNB];
+    uint64_t full[kNS];   // TMA bytes of the x boxes + the dequant warps of the stage's group
+    uint64_t empty[kNS];  // one tcgen05.commit per stage
     uint64_t t_full, t_empty;
     uint64_t drain;
     uint32_t tmem_base;
@@ -272,8 +266,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* a_ring = base;
-    uint8_t* b_ring = a_ring + kNA * kATileBytes;
-    GmBarriers* sb = reinterpret_cast<GmBarriers*>(b_ring + kNB * kBTileBytes);
+    uint8_t* b_ring = a_ring + kNS * kATileBytes;
+    GmBarriers* sb = reinterpret_cast<GmBarriers*>(b_ring + kNS * kBTileBytes);
     int* row_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sb) + 256);
     int* tile_prefix = row_start + (a.G + 1);
 
@@ -291,8 +285,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
         sb->n_tiles = acc;
         sb->abort = 0;
-        for (int i = 0; i < kNA; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->a_full[i]), 1); ptx::mbar_init(ptx::smem_u32(&sb->a_empty[i]), 1); }
-        for (int i = 0; i < kNB; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->b_full[i]), kDqGroupWarps); ptx::mbar_init(ptx::smem_u32(&sb->b_empty[i]), 1); }
+        for (int i = 0; i < kNS; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->full[i]), 1 + kDqGroupWarps); ptx::mbar_init(ptx::smem_u32(&sb->empty[i]), 1); }
         ptx::mbar_init(ptx::smem_u32(&sb->t_full), 1);
         ptx::mbar_init(ptx::smem_u32(&sb->t_empty), kEpiWarps);
         ptx::mbar_init(ptx::smem_u32(&sb->drain), 1);
@@ -328,9 +321,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
                 for (int kt = 0; kt < n_kt; ++kt, ++ia) {
-                    const uint32_t s = ia % kNA, ph = (ia / kNA) & 1;
-                    if (ia >= kNA && !gm_wait(&sb->a_empty[s], ph ^ 1, sb, a.status, 10 + (int)s)) { ok = false; break; }
-                    const uint32_t bar = ptx::smem_u32(&sb->a_full[s]);
+                    const uint32_t s = ia % kNS, ph = (ia / kNS) & 1;
+                    if (ia >= kNS && !gm_wait(&sb->empty[s], ph ^ 1, sb, a.status, 10 + (int)s)) { ok = false; break; }
+                    const uint32_t bar = ptx::smem_u32(&sb->full[s]);
                     ptx::mbar_arrive_expect_tx(bar, ti.halves * kAHalfBytes);
                     ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes), &tmap_x, bar, kt * kBK, ti.row0);
                     if (ti.halves == 2)
@@ -344,8 +337,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 }
             }
             if (!ok)
-                for (uint32_t j = (ia > kNA ? ia - kNA : 0); j < ia; ++j)
-                    (void)ptx::mbar_wait(ptx::smem_u32(&sb->a_full[j % kNA]), (j / kNA) & 1);
+                for (uint32_t j = (ia > kNS ? ia - kNS : 0); j < ia; ++j)
+                    (void)ptx::mbar_wait(ptx::smem_u32(&sb->full[j % kNS]), (j / kNS) & 1);
         }
     } else if (warp == kWarpMma) {
         // ------------------------------ MMA issuer ------------------------------
@@ -358,7 +351,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             const uint64_t da0 = ptx::umma_desc_sw128(ptx::smem_u32(a_ring), 0, 1024);
             // B: MN-major, 64-column blocks kBK*128 B apart (LBO), 8-k groups 1024 B apart (SBO)
             const uint64_t db0 = ptx::umma_desc_sw128(ptx::smem_u32(b_ring), kBK * 128, 1024);
-            uint32_t sa = 0, pha = 0, sbb = 0, phb = 0, it = 0;
+            uint32_t sa = 0, pha = 0, it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++it) {
                 const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
@@ -367,11 +360,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 ptx::tc_fence_after();
                 uint32_t accumulate = 0;
                 for (int kt = 0; kt < n_kt; ++kt) {
-                    if (!gm_wait(&sb->a_full[sa], pha, sb, a.status, 40 + (int)sa)) { ok = false; break; }
-                    if (!gm_wait(&sb->b_full[sbb], phb, sb, a.status, 50 + (int)sbb)) { ok = false; break; }
+                    if (!gm_wait(&sb->full[sa], pha, sb, a.status, 40 + (int)sa)) { ok = false; break; }
                     ptx::tc_fence_after();
                     const uint64_t da = da0 + (uint64_t)(sa * (kATileBytes >> 4));
-                    const uint64_t db = db0 + (uint64_t)(sbb * (kBTileBytes >> 4));
+                    const uint64_t db = db0 + (uint64_t)(sa * (kBTileBytes >> 4));
 #pragma unroll
                     for (int k16 = 0; k16 < kBK / 16; ++k16)
                         ptx::umma_bf16(tmem_base, da + (uint64_t)(k16 * 2), db + (uint64_t)(k16 * 128), idesc,
@@ -383,10 +375,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                                            db + (uint64_t)(k16 * 128), idesc, accumulate | (uint32_t)k16);
                     }
                     accumulate = 1;
-                    ptx::umma_commit(ptx::smem_u32(&sb->a_empty[sa]));
-                    ptx::umma_commit(ptx::smem_u32(&sb->b_empty[sbb]));
-                    if (++sa == kNA) { sa = 0; pha ^= 1; }
-                    if (++sbb == kNB) { sbb = 0; phb ^= 1; }
+                    ptx::umma_commit(ptx::smem_u32(&sb->empty[sa]));
+                    if (++sa == kNS) { sa = 0; pha ^= 1; }
                 }
                 if (ok) ptx::umma_commit(ptx::smem_u32(&sb->t_full));
             }
@@ -475,14 +465,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 #pragma unroll
             for (int u = 0; u < kPrefetch; ++u) {
                 if (!cur.valid) break;
-                const uint32_t sbb = ib % kNB, phb = (ib / kNB) & 1;
+                const uint32_t sbb = ib % kNS, phb = (ib / kNS) & 1;
                 bool got = true;
-                if (ib >= kNB) got = gm_wait(&sb->b_empty[sbb], phb ^ 1, sb, a.status, 80 + (int)sbb);
+                if (ib >= kNS) got = gm_wait(&sb->empty[sbb], phb ^ 1, sb, a.status, 80 + (int)sbb);
                 if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
                 convert_stage<MODE>(regs[u], b_ring + sbb * kBTileBytes, a, cur.ti, cur.kt, d);
                 ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->b_full[sbb]));
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->full[sbb]));
                 if (pf.valid) load_packed<MODE>(regs[u], weight, a, pf.ti, pf.kt, d);
 #pragma unroll
                 for (int i = 0; i < kDqGroups; ++i) {
@@ -520,7 +510,7 @@ __global__ void rowsum_kernel(const __nv_bfloat16* __restrict__ x, float* __rest
 }
 
 static size_t gm_smem_bytes(int G) {
-    return 1024 + (size_t)kNA * kATileBytes + (size_t)kNB * kBTileBytes + 256 + sizeof(int) * 2 * (size_t)(G + 1);
+    return 1024 + (size_t)kNS * (kATileBytes + kBTileBytes) + 256 + sizeof(int) * 2 * (size_t)(G + 1);
 }
 
 template <int MODE>
@@ -540,6 +530,17 @@ static int gm_launch(const void* x, const void* w, const GemmArgs& a, cudaStream
 }
 
 static size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+// Kernel variant: the single-CTA kernel of this file (default; the faster one on B200 as measured)
+// or the CTA-pair (cta_group::2) kernel of grouped_gemm_pair.cu, selected with the environment
+// variable B200MOE_GEMM_KERNEL=pair (read once per process).
+static bool use_pair_kernel() {
+    static const bool pair = [] {
+        const char* e = getenv("B200MOE_GEMM_KERNEL");
+        return e != nullptr && strcmp(e, "pair") == 0;
+    }();
+    return pair;
+}
 
 }  // namespace b200moe
 
@@ -599,15 +600,20 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
             a.offset = static_cast<const __nv_bfloat16*>(offset);
             a.rowsum = rowsum;
         }
+        if (use_pair_kernel()) return launch_grouped_gemm_pair(B200MOE_CT_INT8, x, weight, a, s);
         return gm_launch<B200MOE_CT_INT8>(x, weight, a, s);
     }
-    if (compute_type == B200MOE_CT_FP8) return gm_launch<B200MOE_CT_FP8>(x, weight, a, s);
+    if (compute_type == B200MOE_CT_FP8) {
+        if (use_pair_kernel()) return launch_grouped_gemm_pair(B200MOE_CT_FP8, x, weight, a, s);
+        return gm_launch<B200MOE_CT_FP8>(x, weight, a, s);
+    }
     const void* w = weight;
     if (weight_layout == B200MOE_LAYOUT_ASCEND) {
         int rc = b200moe_fp4_layout(weight, ws, G, K, N, 0, stream);
         if (rc != B200MOE_OK) return rc;
         w = ws;
     }
+    if (use_pair_kernel()) return launch_grouped_gemm_pair(B200MOE_CT_FP4, x, w, a, s);
     return gm_launch<B200MOE_CT_FP4>(x, w, a, s);
 }
 

@@ -57,6 +57,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking poll of a barrier phase.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait: gives up after ~kWaitLimitNs of wall time and reports false.  No wait in these
 // kernels may spin forever: on expiry the caller records an error status and winds down.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
@@ -174,6 +189,15 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
         : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
+}
+// TMA load issued by a CTA of a pair whose completion bytes are counted on a barrier that may
+// live in the peer CTA (`bar_cluster` is a shared::cluster address, e.g. from mapa).  No multicast:
+// the data lands only in the issuing CTA's shared memory.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(x), "r"(y)
+        : "memory");
 }
 // TMEM allocation for a CTA pair: one warp of EACH of the two CTAs executes these collectively.
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
