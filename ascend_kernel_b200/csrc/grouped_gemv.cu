@@ -1,7 +1,7 @@
 // Grouped GEMV for decode-sized expert batches (HBM-bandwidth kernel).
 //
-// Work item = (non-empty expert, slab of 256 output columns); persistent CTAs (two per SM) take
-// items with a static stride.  The expert's x rows (up to 4 per pass) are copied to shared memory
+// Work item = (non-empty expert, slab of 256 output columns); persistent CTAs (two per SM) draw
+// items from a ticket counter, experts with the most rows first.  The expert's x rows (up to 4 per pass) are copied to shared memory
 // once per item.  Every warp streams its share of the k rows straight from global memory with
 // 128-bit coalesced loads, eight row pairs (8 x 512 B per warp) in flight before the first is
 // consumed, decodes the packed weights in registers (byte / nibble unpack, no shared-memory
@@ -242,19 +242,34 @@ __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvA
 
     load_row_starts(a.group_list, a.G, a.M, a.gl_type, row_start, a.status);
     if (threadIdx.x == 0) {
+        // non-empty experts, those with the most rows first (counting sort on min(rows, 5)): with
+        // the ticket counter below the long items start early and the short ones fill the tail
         int n = 0;
-        for (int g = 0; g < a.G; ++g)
-            if (row_start[g + 1] > row_start[g]) active[n++] = g;
+        for (int b = 5; b >= 1; --b)
+            for (int g = 0; g < a.G; ++g) {
+                const int rows = row_start[g + 1] - row_start[g];
+                if ((rows >= 5 ? 5 : rows) == b) active[n++] = g;
+            }
         *n_active_p = n;
     }
     __syncthreads();
 
     const int n_slabs = a.N / kGvSlabN;
-    const int n_items = *n_active_p * n_slabs;
+    const int n_act = *n_active_p;
+    const int n_items = n_act * n_slabs;
     const int kvec = a.K / 8;  // 16-byte vectors per x row
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const int g = active[item / n_slabs];
-        const int n0 = (item % n_slabs) * kGvSlabN;
+    int* ticket = a.status + 2;  // zeroed by the host before the launch
+    __shared__ int s_item;
+    for (;;) {
+        __syncthreads();
+        if (threadIdx.x == 0) s_item = atomicAdd(ticket, 1);
+        __syncthreads();
+        const int item = s_item;
+        if (item >= n_items) break;
+        // slab-major order: neighbouring CTAs work on different experts, so experts with more rows
+        // (slower items) are spread over the grid instead of landing on 16 adjacent CTAs
+        const int g = active[item % n_act];
+        const int n0 = (item / n_act) * kGvSlabN;
         const int r0 = row_start[g], r1 = row_start[g + 1];
         for (int r = r0; r < r1; r += kGvRows) {
             const int rows = min(kGvRows, r1 - r);
