@@ -23,7 +23,7 @@ EXPORTS = [
     "b200moe_grouped_gemm", "b200moe_grouped_gemm_workspace_bytes", "b200moe_grouped_gemv",
     "b200moe_grouped_gemv_workspace_bytes", "b200moe_fp4_dequant", "b200moe_fp4_layout", "b200moe_silu_mul",
     "b200moe_gather_rows", "b200moe_combine", "b200moe_read_status", "b200moe_strerror", "b200moe_version",
-    "b200moe_grouped_gemm_int8_noalloc", "b200moe_grouped_gemm_int8_noalloc_max_rows", "b200moe_noalloc_read_status",
+    "b200moe_moe_route", "b200moe_moe_regroup_index", "b200moe_grouped_gemm_int8_noalloc", "b200moe_grouped_gemm_int8_noalloc_max_rows", "b200moe_noalloc_read_status",
 ]
 
 
@@ -64,6 +64,10 @@ def _load() -> ctypes.CDLL:
     lib.b200moe_gather_rows.restype = i32
     lib.b200moe_combine.argtypes = [vp, vp, vp, vp, i64, i64, i64, vp]
     lib.b200moe_combine.restype = i32
+    lib.b200moe_moe_route.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp]
+    lib.b200moe_moe_route.restype = i32
+    lib.b200moe_moe_regroup_index.argtypes = [vp, i64, i64, vp, vp, vp, vp]
+    lib.b200moe_moe_regroup_index.restype = i32
     lib.b200moe_read_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
     lib.b200moe_read_status.restype = i32
     lib.b200moe_strerror.argtypes = [i32]

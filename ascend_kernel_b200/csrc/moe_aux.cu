@@ -54,9 +54,158 @@ __global__ void combine_kernel(const uint4* __restrict__ y, const int32_t* __res
     }
 }
 
+// ---- routing: softmax -> top-k -> renormalise, and the sort of (token, k) pairs by expert -------
+// One warp per token.  The renormalised top-k weights of a softmax only need the k largest logits:
+// w_i = exp(l_i - l_max) / sum_{j in top-k} exp(l_j - l_max).  Ties go to the lower expert index.
+constexpr int kRouteMaxPerLane = 32;  // E <= 1024
+
+__global__ void route_topk_kernel(const __nv_bfloat16* __restrict__ logits, int T, int E, int k,
+                                  int32_t* __restrict__ idx, float* __restrict__ w, int32_t* __restrict__ hist) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (t >= T) return;
+    float v[kRouteMaxPerLane];
+    const int per = (E + 31) / 32;
+#pragma unroll
+    for (int i = 0; i < kRouteMaxPerLane; ++i) {
+        const int e = i * 32 + lane;
+        v[i] = (i < per && e < E) ? __bfloat162float(logits[(size_t)t * E + e]) : -INFINITY;
+    }
+    float top0 = 0.f, denom = 0.f, mine = 0.f;
+    int mine_idx = 0;
+    for (int j = 0; j < k; ++j) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < kRouteMaxPerLane; ++i) {
+            const int e = i * 32 + lane;
+            if (i < per && (v[i] > best || (v[i] == best && e < bi))) { best = v[i]; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (j == 0) top0 = best;
+        const float p = __expf(best - top0);
+        denom += p;
+        if (lane == j) { mine = p; mine_idx = bi; }
+        if ((bi & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < kRouteMaxPerLane; ++i)
+                if (i == (bi >> 5)) v[i] = -INFINITY;
+        }
+    }
+    if (lane < k) {
+        idx[(size_t)t * k + lane] = mine_idx;
+        w[(size_t)t * k + lane] = mine / denom;
+        atomicAdd(&hist[mine_idx], 1);
+    }
+}
+
+// Single CTA: exclusive prefix of the per-expert histogram -> cursor[e] (start of expert e in the
+// sorted order) and the int64 counts the grouped GEMM takes as group_list.
+__global__ void route_prefix_kernel(const int32_t* __restrict__ hist, int E, int32_t* __restrict__ cursor,
+                                    long long* __restrict__ counts64) {
+    __shared__ int s[1024];
+    const int e = threadIdx.x;
+    const int c = e < E ? hist[e] : 0;
+    s[e] = c;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {
+        const int add = e >= o ? s[e - o] : 0;
+        __syncthreads();
+        s[e] += add;
+        __syncthreads();
+    }
+    if (e < E) {
+        cursor[e] = s[e] - c;
+        counts64[e] = c;
+    }
+}
+
+// Every (token, j) pair takes the next free position of its expert.  Order inside an expert is
+// arbitrary (rows are independent); slot[t, j] remembers where the pair went.
+__global__ void route_scatter_kernel(const int32_t* __restrict__ idx, long long n_pairs, int k,
+                                     int32_t* __restrict__ cursor, int32_t* __restrict__ token_of,
+                                     int32_t* __restrict__ slot) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_pairs) return;
+    const int pos = atomicAdd(&cursor[idx[i]], 1);
+    token_of[pos] = (int32_t)(i / k);
+    slot[i] = pos;
+}
+
+// Expert-parallel regroup: rows arrive ordered (source rank, local expert); the grouped GEMM wants
+// them expert-major.  cnt[r, e] rows per block; pos[i] = expert-major position of received row i.
+__global__ void regroup_index_kernel(const long long* __restrict__ cnt, int world, int e_local,
+                                     int32_t* __restrict__ pos, int32_t* __restrict__ inv,
+                                     long long* __restrict__ local_counts) {
+    __shared__ int src_start[1024], em_start[1024], size[1024];
+    const int nb = world * e_local;
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int b = 0; b < nb; ++b) { size[b] = (int)cnt[b]; src_start[b] = acc; acc += size[b]; }
+        acc = 0;
+        for (int e = 0; e < e_local; ++e) {
+            int tot = 0;
+            for (int r = 0; r < world; ++r) { em_start[r * e_local + e] = acc; acc += size[r * e_local + e]; tot += size[r * e_local + e]; }
+            local_counts[e] = tot;
+        }
+    }
+    __syncthreads();
+    for (int b = 0; b < nb; ++b) {
+        const int s0 = src_start[b], d0 = em_start[b];
+        for (int i = threadIdx.x; i < size[b]; i += blockDim.x) {
+            pos[s0 + i] = d0 + i;
+            inv[d0 + i] = s0 + i;
+        }
+    }
+}
+
 }  // namespace b200moe
 
 using namespace b200moe;
+
+extern "C" int b200moe_moe_route(const void* logits, int64_t n_tokens, int64_t n_experts, int64_t top_k, int32_t* idx,
+                                 float* weight, int64_t* counts, int32_t* token_of, int32_t* slot, int32_t* scratch,
+                                 void* stream) {
+    if (n_tokens < 0 || n_experts <= 0 || n_experts > 1024 || top_k <= 0 || top_k > 32 || top_k > n_experts ||
+        n_tokens * top_k > 0x7FFFFFF0LL)
+        return B200MOE_ERR_SHAPE;
+    if (!logits || !idx || !weight || !counts || !token_of || !slot || !scratch) return B200MOE_ERR_NULL_POINTER;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int32_t* hist = scratch;
+    int32_t* cursor = scratch + n_experts;
+    B200MOE_CUDA_TRY(cudaMemsetAsync(hist, 0, sizeof(int32_t) * (size_t)n_experts, s));
+    if (n_tokens > 0) {
+        route_topk_kernel<<<(unsigned)((n_tokens + 7) / 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(logits),
+                                                                         (int)n_tokens, (int)n_experts, (int)top_k, idx,
+                                                                         weight, hist);
+        B200MOE_CUDA_TRY(cudaGetLastError());
+    }
+    route_prefix_kernel<<<1, 1024, 0, s>>>(hist, (int)n_experts, cursor, reinterpret_cast<long long*>(counts));
+    B200MOE_CUDA_TRY(cudaGetLastError());
+    const long long n_pairs = n_tokens * top_k;
+    if (n_pairs > 0) {
+        route_scatter_kernel<<<(unsigned)((n_pairs + 255) / 256), 256, 0, s>>>(idx, n_pairs, (int)top_k, cursor, token_of,
+                                                                                slot);
+        B200MOE_CUDA_TRY(cudaGetLastError());
+    }
+    return B200MOE_OK;
+}
+
+extern "C" int b200moe_moe_regroup_index(const int64_t* recv_counts, int64_t world, int64_t e_local, int32_t* pos,
+                                         int32_t* inv, int64_t* local_counts, void* stream) {
+    if (world <= 0 || e_local <= 0 || world * e_local > 1024) return B200MOE_ERR_SHAPE;
+    if (!recv_counts || !pos || !inv || !local_counts) return B200MOE_ERR_NULL_POINTER;
+    regroup_index_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const long long*>(recv_counts), (int)world, (int)e_local, pos, inv,
+        reinterpret_cast<long long*>(local_counts));
+    B200MOE_CUDA_TRY(cudaGetLastError());
+    return B200MOE_OK;
+}
 
 extern "C" int b200moe_silu_mul(const void* h, void* out, int64_t rows, int64_t inter, void* stream) {
     if (rows < 0 || inter <= 0 || (inter % 8) != 0) return B200MOE_ERR_SHAPE;

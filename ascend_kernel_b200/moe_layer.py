@@ -3,10 +3,11 @@
 One process per GPU; experts are sharded contiguously over the ranks (expert e lives on rank
 e // (E / world)).  Per step:
 
-  route (softmax -> top-k -> renormalise)            torch, tiny
-  sort the (token, k) pairs by expert, gather rows   b200moe_gather_rows
+  route (softmax -> top-k -> renormalise) and sort   b200moe_moe_route
+  of the (token, k) pairs by expert
+  gather rows into expert order                      b200moe_gather_rows
   all-to-all of per-expert counts, then of rows      NCCL (torch.distributed), world > 1 only
-  regroup received rows expert-major                 b200moe_gather_rows, world > 1 only
+  regroup received rows expert-major                 b200moe_moe_regroup_index + b200moe_gather_rows, world > 1 only
   grouped GEMM gate|up  [H -> 2I], int8 antiquant    b200moe_grouped_gemm  (tcgen05)
   SiLU(gate) * up                                    b200moe_silu_mul
   grouped GEMM down     [I -> H], int8 antiquant     b200moe_grouped_gemm
@@ -14,8 +15,8 @@ e // (E / world)).  Per step:
   weighted sum over each token's k results           b200moe_combine
 
 Data from peers always lands in this GPU's own memory (the NCCL receive buffer) before a kernel
-reads it.  torch is used for device memory, streams, the router's few small tensor ops and the
-process group; every row-sized operation is one of the package's CUDA kernels.
+reads it.  torch is used for device memory, streams and the process group; routing, permutation
+and every row-sized operation are this package's CUDA kernels.
 """
 from __future__ import annotations
 
@@ -27,6 +28,8 @@ from . import ops
 class CudaRowOps:
     """The row-sized operations of the layer, on this package's CUDA kernels."""
 
+    route = staticmethod(ops.moe_route)
+    regroup_index = staticmethod(ops.moe_regroup_index)
     gather_rows = staticmethod(ops.gather_rows)
     combine = staticmethod(ops.combine)
     silu_mul = staticmethod(ops.silu_mul)
@@ -55,12 +58,6 @@ class MoELayer:
         self.device = w13.device
         self.timing = None  # optional dict of CUDA event pairs filled by forward(record=True)
 
-    # ---- routing ---------------------------------------------------------------------------
-    def route(self, logits):
-        p = torch.softmax(logits.float(), dim=-1)
-        w, idx = torch.topk(p, self.top_k, dim=-1)
-        return (w / w.sum(dim=-1, keepdim=True)).contiguous(), idx
-
     def _experts(self, rows, counts, record):
         """rows [R, H] expert-major with per-local-expert counts -> [R, H]."""
         R = rows.shape[0]
@@ -87,16 +84,8 @@ class MoELayer:
     # ---- one step --------------------------------------------------------------------------
     def forward(self, x, logits, record: bool = False):
         """x bf16 [T, H], logits bf16 [T, E] on this rank's device -> bf16 [T, H]."""
-        T = x.shape[0]
-        wts, idx = self.route(logits)
-        flat = idx.reshape(-1)
-        order = torch.argsort(flat, stable=True)                 # pair indices sorted by expert
-        token_of = (order // self.top_k).to(torch.int32)
-        slot = torch.empty_like(order)
-        slot[order] = torch.arange(order.numel(), device=self.device)
-        slot = slot.reshape(T, self.top_k).to(torch.int32)       # position of pair (t, j) in sorted order
-        counts = torch.bincount(flat, minlength=self.n_experts)  # int64 [E]
-        send = self.ops.gather_rows(x, token_of)                      # [T*k, H] sorted by expert
+        idx, wts, counts, token_of, slot = self.ops.route(logits, self.top_k)
+        send = self.ops.gather_rows(x, token_of)                 # [T*k, H] sorted by expert
 
         if self.world == 1:
             y = self._experts(send, counts, record)
@@ -116,19 +105,10 @@ class MoELayer:
         dist.all_to_all_single(recv, send, out_split, in_split, group=self.group)
 
         # received order is (source rank, expert); the grouped GEMM wants expert-major
-        local_counts = recv_counts.sum(0)
-        blk = recv_counts.reshape(-1)                                          # block sizes, source-major
-        src_start = torch.cumsum(blk, 0) - blk                                 # where each block sits now
-        em = recv_counts.t().contiguous().reshape(-1)                          # block sizes, expert-major
-        em_start = (torch.cumsum(em, 0) - em).reshape(self.e_local, self.world).t().reshape(-1)
-        # for every received row: its position in expert-major order
-        pos = torch.repeat_interleave(em_start - src_start, blk, output_size=n_recv) + torch.arange(
-            n_recv, device=self.device)
-        inv = torch.empty_like(pos)
-        inv[pos] = torch.arange(n_recv, device=self.device)
-        rows = self.ops.gather_rows(recv, inv.to(torch.int32))                      # expert-major
+        pos, inv, local_counts = self.ops.regroup_index(recv_counts, n_recv)
+        rows = self.ops.gather_rows(recv, inv)
         y = self._experts(rows, local_counts, record)
-        back = self.ops.gather_rows(y, pos.to(torch.int32))                         # source-major again
+        back = self.ops.gather_rows(y, pos)                      # source-major again
         ret = torch.empty(send.shape[0], self.hidden, dtype=torch.bfloat16, device=self.device)
         dist.all_to_all_single(ret, back, in_split, out_split, group=self.group)
         return self.ops.combine(ret, slot, wts)

@@ -188,6 +188,47 @@ def combine(y, slot, weight, out=None):
     return out
 
 
+def moe_route(logits, top_k: int):
+    """logits bf16 [T, E] -> (idx int32 [T,k], weight fp32 [T,k], counts int64 [E], token_of int32 [T*k],
+    slot int32 [T,k])."""
+    _need_cuda(logits=logits)
+    if logits.dtype != torch.bfloat16:
+        raise RuntimeError("logits must be bfloat16")
+    T, E = logits.shape
+    dev = logits.device
+    idx = torch.empty(T, top_k, dtype=torch.int32, device=dev)
+    w = torch.empty(T, top_k, dtype=torch.float32, device=dev)
+    counts = torch.empty(E, dtype=torch.int64, device=dev)
+    token_of = torch.empty(T * top_k, dtype=torch.int32, device=dev)
+    slot = torch.empty(T, top_k, dtype=torch.int32, device=dev)
+    scratch = torch.empty(2 * E, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.b200moe_moe_route(_ptr(logits), T, E, top_k, _ptr(idx), _ptr(w), _ptr(counts), _ptr(token_of),
+                                    _ptr(slot), _ptr(scratch), _stream())
+    _abi.check(rc, "moe_route")
+    _count(3)
+    return idx, w, counts, token_of, slot
+
+
+def moe_regroup_index(recv_counts, n_recv: int):
+    """recv_counts int64 [world, e_local] (rows per source rank and local expert, arrival order) ->
+    (pos int32 [n_recv], inv int32 [n_recv], local_counts int64 [e_local])."""
+    _need_cuda(recv_counts=recv_counts)
+    if recv_counts.dtype != torch.int64:
+        raise RuntimeError("recv_counts must be int64")
+    world, e_local = recv_counts.shape
+    dev = recv_counts.device
+    pos = torch.empty(n_recv, dtype=torch.int32, device=dev)
+    inv = torch.empty(n_recv, dtype=torch.int32, device=dev)
+    local_counts = torch.empty(e_local, dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.b200moe_moe_regroup_index(_ptr(recv_counts), world, e_local, _ptr(pos), _ptr(inv),
+                                            _ptr(local_counts), _stream())
+    _abi.check(rc, "moe_regroup_index")
+    _count(1)
+    return pos, inv, local_counts
+
+
 def read_status(ws):
     import ctypes
 

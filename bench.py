@@ -71,7 +71,7 @@ class ClockSampler:
         self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return
-        time.sleep(0.15)
+        time.sleep(0.25)  # let at least a few samples through even for a short timed region
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)

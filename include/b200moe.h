@@ -138,6 +138,20 @@ int b200moe_gather_rows(const void* src, const int32_t* index, void* dst, int64_
 int b200moe_combine(const void* y, const int32_t* slot, const float* weight, void* out, int64_t n_tokens,
                     int64_t top_k, int64_t width, void* stream);
 
+/* Router of the MoE layer: softmax over the experts -> top_k -> weights renormalised to sum 1
+ * (ties go to the lower expert index), and the sort of the (token, j) pairs by expert.
+ * logits bf16 [T, E] (E <= 1024); outputs: idx int32 [T, top_k], weight fp32 [T, top_k],
+ * counts int64 [E] (rows per expert, usable as a counts group_list), token_of int32 [T*top_k]
+ * (source token of each sorted row), slot int32 [T, top_k] (sorted position of each pair; the order
+ * inside an expert is arbitrary).  scratch: 2*E int32. */
+int b200moe_moe_route(const void* logits, int64_t n_tokens, int64_t n_experts, int64_t top_k, int32_t* idx,
+                      float* weight, int64_t* counts, int32_t* token_of, int32_t* slot, int32_t* scratch, void* stream);
+/* Expert-parallel regroup index: recv_counts int64 [world, e_local] = rows received per (source
+ * rank, local expert), in arrival order; pos[i] = expert-major position of received row i, inv its
+ * inverse, local_counts int64 [e_local] the rows per local expert.  world*e_local <= 1024. */
+int b200moe_moe_regroup_index(const int64_t* recv_counts, int64_t world, int64_t e_local, int32_t* pos, int32_t* inv,
+                              int64_t* local_counts, void* stream);
+
 /* Copies the two device status words of a workspace to the host (synchronises the stream). */
 int b200moe_read_status(const void* workspace, int32_t out[2], void* stream);
 

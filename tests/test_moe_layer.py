@@ -18,6 +18,30 @@ class TorchRowOps:
     """CPU stand-ins with the semantics of the CUDA row kernels (tests only)."""
 
     @staticmethod
+    def route(logits, top_k):
+        w, idx = O.route_topk(logits, top_k)
+        T = logits.shape[0]
+        flat = idx.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        token_of = (order // top_k).to(torch.int32)
+        slot = torch.empty_like(order)
+        slot[order] = torch.arange(order.numel())
+        counts = torch.bincount(flat, minlength=logits.shape[1])
+        return idx.to(torch.int32), w.contiguous(), counts, token_of, slot.reshape(T, top_k).to(torch.int32)
+
+    @staticmethod
+    def regroup_index(recv_counts, n_recv):
+        world, e_local = recv_counts.shape
+        blk = recv_counts.reshape(-1)
+        src_start = torch.cumsum(blk, 0) - blk
+        em = recv_counts.t().contiguous().reshape(-1)
+        em_start = (torch.cumsum(em, 0) - em).reshape(e_local, world).t().reshape(-1)
+        pos = torch.repeat_interleave(em_start - src_start, blk, output_size=n_recv) + torch.arange(n_recv)
+        inv = torch.empty_like(pos)
+        inv[pos] = torch.arange(n_recv)
+        return pos.to(torch.int32), inv.to(torch.int32), recv_counts.sum(0)
+
+    @staticmethod
     def gather_rows(src, index, out=None):
         return src[index.long()].contiguous()
 
@@ -183,3 +207,38 @@ def test_two_gpu_ranks_match_oracle():
     gold = O.moe_layer(c["x"], c["logits"], c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], c["top_k"])
     out = torch.cat([torch.from_numpy(got[r]).view(torch.bfloat16) for r in range(2)])
     close(out, gold)
+
+
+@pytest.mark.gpu
+def test_route_and_regroup_kernels_match_torch():
+    import ascend_kernel_b200 as ak
+    from ascend_kernel_b200 import ops
+
+    gen = torch.Generator().manual_seed(3)
+    T, E, k = 333, 256, 8
+    # distinct, bf16-exact logits per token (no ties, so the selected set is unambiguous)
+    logits = torch.stack([torch.randperm(E, generator=gen) for _ in range(T)]).float().div(16).sub(8).to(torch.bfloat16)
+    idx, w, counts, token_of, slot = ops.moe_route(logits.cuda(), k)
+    torch.cuda.synchronize()
+    rw, ridx = O.route_topk(logits, k)
+    # same expert sets and weights
+    got_sorted, order = torch.sort(idx.cpu().long(), dim=1)
+    want_sorted, worder = torch.sort(ridx, dim=1)
+    tie_free = (got_sorted == want_sorted).all(1)
+    assert tie_free.all()
+    assert torch.allclose(torch.gather(w.cpu(), 1, order)[tie_free], torch.gather(rw, 1, worder)[tie_free], rtol=1e-4, atol=1e-6)
+    assert torch.allclose(w.cpu().sum(1), torch.ones(T), atol=1e-5)
+    assert torch.equal(counts.cpu(), torch.bincount(idx.cpu().long().reshape(-1), minlength=E))
+    # slot / token_of are a consistent permutation, grouped by expert
+    pos = slot.cpu().long().reshape(-1)
+    assert torch.equal(torch.sort(pos)[0], torch.arange(T * k))
+    assert torch.equal(token_of.cpu().long()[pos], torch.arange(T * k) // k)
+    expert_of_pos = torch.empty(T * k, dtype=torch.long)
+    expert_of_pos[pos] = idx.cpu().long().reshape(-1)
+    assert (expert_of_pos[1:] >= expert_of_pos[:-1]).all()
+    # regroup index
+    rc = torch.randint(0, 7, (4, 16), generator=gen)
+    n = int(rc.sum())
+    p, inv, lc = ops.moe_regroup_index(rc.cuda(), n)
+    tp, tinv, tlc = TorchRowOps.regroup_index(rc, n)
+    assert torch.equal(p.cpu(), tp) and torch.equal(inv.cpu(), tinv) and torch.equal(lc.cpu(), tlc)
