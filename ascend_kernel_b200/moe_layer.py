@@ -56,7 +56,8 @@ class MoELayer:
         assert self.e_local * self.world == n_experts
         self.hidden, self.inter = w13.shape[1], w2.shape[1]
         self.device = w13.device
-        self.timing = None  # optional dict of CUDA event pairs filled by forward(record=True)
+        self.timing = None  # [ev0..ev3] around GEMM1 / SiLU / GEMM2, filled by forward(record=True)
+        self.phases = None  # [(name, event)] phase boundaries of the last forward(record=True)
 
     def _experts(self, rows, counts, record):
         """rows [R, H] expert-major with per-local-expert counts -> [R, H]."""
@@ -84,12 +85,26 @@ class MoELayer:
     # ---- one step --------------------------------------------------------------------------
     def forward(self, x, logits, record: bool = False):
         """x bf16 [T, H], logits bf16 [T, E] on this rank's device -> bf16 [T, H]."""
+        marks = [] if record else None
+
+        def mark(name):
+            if marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
         idx, wts, counts, token_of, slot = self.ops.route(logits, self.top_k)
         send = self.ops.gather_rows(x, token_of)                 # [T*k, H] sorted by expert
+        mark("route+gather")
 
         if self.world == 1:
             y = self._experts(send, counts, record)
-            return self.ops.combine(y, slot, wts)
+            mark("experts")
+            out = self.ops.combine(y, slot, wts)
+            mark("combine")
+            self.phases = marks
+            return out
 
         import torch.distributed as dist
 
@@ -103,15 +118,22 @@ class MoELayer:
         n_recv = int(sum(out_split))
         recv = torch.empty(n_recv, self.hidden, dtype=torch.bfloat16, device=self.device)
         dist.all_to_all_single(recv, send, out_split, in_split, group=self.group)
+        mark("dispatch")
 
         # received order is (source rank, expert); the grouped GEMM wants expert-major
         pos, inv, local_counts = self.ops.regroup_index(recv_counts, n_recv)
         rows = self.ops.gather_rows(recv, inv)
+        mark("regroup")
         y = self._experts(rows, local_counts, record)
+        mark("experts")
         back = self.ops.gather_rows(y, pos)                      # source-major again
         ret = torch.empty(send.shape[0], self.hidden, dtype=torch.bfloat16, device=self.device)
         dist.all_to_all_single(ret, back, in_split, out_split, group=self.group)
-        return self.ops.combine(ret, slot, wts)
+        mark("return")
+        out = self.ops.combine(ret, slot, wts)
+        mark("combine")
+        self.phases = marks
+        return out
 
     def forward_host(self, x_host, logits_host, out_host=None):
         """End-to-end call with host buffers: pinned host -> device copies of this step's inputs,

@@ -326,7 +326,7 @@ def run_ours(args):
         layer.forward(x, lg)
     barrier()
     ops.LAUNCHES = 0
-    gemm_ms, gemm_events = 0.0, []
+    gemm_ms, gemm_events, phase_events = 0.0, [], []
     with ClockSampler(local_rank) as clk:
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -336,6 +336,8 @@ def run_ours(args):
             layer.forward(x, lg, record=True)
             if layer.timing is not None:
                 gemm_events.append(layer.timing)
+            if layer.phases is not None:
+                phase_events.append(layer.phases)
         ev1.record()
         barrier()
         torch.cuda.profiler.stop()
@@ -345,6 +347,10 @@ def run_ours(args):
         gemm_ms += ev[0].elapsed_time(ev[1]) + ev[2].elapsed_time(ev[3])
     ms_per_step = total_ms / args.steps
     value = T / (ms_per_step / 1e3)
+    phases = {}
+    for marks in phase_events:
+        for (n0, e0), (n1, e1) in zip(marks[:-1], marks[1:]):
+            phases[n1] = phases.get(n1, 0.0) + e0.elapsed_time(e1) / len(phase_events)
 
     # ---- end to end through the host-buffer call ----
     out_host = torch.empty(t_local, CFG["hidden"], dtype=torch.bfloat16).pin_memory()
@@ -379,7 +385,7 @@ def run_ours(args):
         "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms},
         "gpu_launches": launches * args.steps, "gpu_launches_per_step": launches,
-        "roofline": roofline, "clocks": clk.result,
+        "roofline": roofline, "clocks": clk.result, "phases_ms_rank0": {k: round(v, 4) for k, v in phases.items()},
     }
     if world == 1 and rank == 0:
         del layer, c
