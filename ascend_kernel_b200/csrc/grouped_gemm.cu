@@ -59,6 +59,10 @@ constexpr uint32_t kTmemCols = 512;
 template <int MODE>
 struct GmTraits {
     static constexpr bool kNibbles = (MODE == B200MOE_CT_FP4 || MODE == B200MOE_CT_INT4);
+    // int4 with per-128-k scale/offset: (w + o) * s does not fit bf16, so every k block is fed to
+    // the tensor core twice -- stage 2i carries hi = bf16(v), stage 2i+1 carries lo = bf16(v - hi) --
+    // against the same x block; the fp32 accumulator then holds x @ v to about 2^-16 relative.
+    static constexpr int kParts = (MODE == B200MOE_CT_INT4) ? 2 : 1;
     static constexpr int kPRowBytes = kNibbles ? kBN / 2 : kBN;
     static constexpr int kPTileBytes = kPRowBytes * kBK;
 };
@@ -169,7 +173,8 @@ __device__ __forceinline__ void load_packed(PackedRegs<MODE>& r, const uint8_t* 
                                             const TileInfo& ti, int kt, const DqLane& d) {
     using T = GmTraits<MODE>;
     const size_t row_bytes = T::kNibbles ? (size_t)a.N / 2 : (size_t)a.N;
-    const uint8_t* base = w + ((size_t)ti.g * a.K + (size_t)kt * kBK + d.row) * row_bytes +
+    const int kb = kt / T::kParts;
+    const uint8_t* base = w + ((size_t)ti.g * a.K + (size_t)kb * kBK + d.row) * row_bytes +
                           (T::kNibbles ? (ti.n0 >> 1) + d.c16 * 8 : ti.n0 + d.c16 * 16);
 #pragma unroll
     for (int j = 0; j < kDqRows; ++j) {
@@ -216,6 +221,35 @@ __device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint8_t
                 }
                 o[2 * i] = pack_bf16x2(f[0], f[1]);
                 o[2 * i + 1] = pack_bf16x2(f[2], f[3]);
+            }
+        } else if constexpr (MODE == B200MOE_CT_INT4) {
+            // v = (w + o) * s in fp32 with the scale / offset of the row's 128-k group, then the
+            // hi or lo bf16 part according to the stage's parity
+            const int kb = kt >> 1;
+            const bool lo_part = (kt & 1) != 0;
+            const size_t so = ((size_t)ti.g * (a.K >> 7) + ((kb * kBK + k) >> 7)) * a.N + ti.n0 + c16 * 16;
+            const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.scale) + so);
+            const uint4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
+            uint4 o0 = make_uint4(0u, 0u, 0u, 0u), o1 = o0;
+            if (a.offset != nullptr) {
+                const uint4* op = reinterpret_cast<const uint4*>(a.offset + so);
+                o0 = __ldg(op);
+                o1 = __ldg(op + 1);
+            }
+            const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            const uint32_t ow[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+            const uint32_t w2[2] = {q.x ^ 0x88888888u, q.y ^ 0x88888888u};  // nibble + 8
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {  // output pair i = columns 2i, 2i+1
+                const uint32_t word = w2[i >> 2];
+                const int sh = 8 * (i & 3);
+                const float w0 = __uint_as_float(((word >> sh) & 0xFu) | 0x4B000000u) - 8388616.0f;        // 2^23 + 8
+                const float w1 = __uint_as_float(((word >> (sh + 4)) & 0xFu) | 0x4B000000u) - 8388616.0f;
+                const float sc0 = __uint_as_float(sw[i] << 16), sc1 = __uint_as_float(sw[i] & 0xFFFF0000u);
+                const float of0 = __uint_as_float(ow[i] << 16), of1 = __uint_as_float(ow[i] & 0xFFFF0000u);
+                const float v0 = (w0 + of0) * sc0, v1 = (w1 + of1) * sc1;
+                const uint32_t hi = pack_bf16x2(v0, v1);
+                o[i] = lo_part ? pack_bf16x2(v0 - __uint_as_float(hi << 16), v1 - __uint_as_float(hi & 0xFFFF0000u)) : hi;
             }
         } else {  // FP4: 8 bytes = 16 codes, bf16 scale per 16 k rows per column
             const uint4* sp = reinterpret_cast<const uint4*>(
@@ -273,7 +307,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_nt = a.N / kBN;
-    const int n_kt = a.K / kBK;
+    const int n_kt = (a.K / kBK) * GmTraits<MODE>::kParts;  // stages per tile
 
     load_row_starts(a.group_list, a.G, a.M, a.gl_type, row_start, a.status);
     if (threadIdx.x == 0) {
@@ -315,7 +349,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             StageIter far;
             iter_start(far, n_tiles, tile_prefix, row_start, a.G, n_nt);
             for (int i = 0; i < kL2Ahead && far.valid; ++i) {
-                ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0, far.ti.g * a.K + far.kt * kBK);
+                ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0, far.ti.g * a.K + (far.kt / T::kParts) * kBK);
                 iter_next(far, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
             }
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
@@ -325,13 +359,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     if (ia >= kNS && !gm_wait(&sb->empty[s], ph ^ 1, sb, a.status, 10 + (int)s)) { ok = false; break; }
                     const uint32_t bar = ptx::smem_u32(&sb->full[s]);
                     ptx::mbar_arrive_expect_tx(bar, ti.halves * kAHalfBytes);
-                    ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes), &tmap_x, bar, kt * kBK, ti.row0);
+                    const int kx = (kt / T::kParts) * kBK;
+                    ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes), &tmap_x, bar, kx, ti.row0);
                     if (ti.halves == 2)
-                        ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes + kAHalfBytes), &tmap_x, bar, kt * kBK,
+                        ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes + kAHalfBytes), &tmap_x, bar, kx,
                                          ti.row0 + kBM);
                     if (far.valid) {
                         ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0,
-                                                far.ti.g * a.K + far.kt * kBK);
+                                                far.ti.g * a.K + (far.kt / T::kParts) * kBK);
                         iter_next(far, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
                     }
                 }
@@ -549,7 +584,7 @@ using namespace b200moe;
 extern "C" size_t b200moe_grouped_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t G, int compute_type,
                                                        int weight_layout) {
     size_t b = B200MOE_STATUS_BYTES;
-    if (compute_type == B200MOE_CT_INT8 || compute_type == B200MOE_CT_INT4) b += align256((size_t)M * sizeof(float));
+    if (compute_type == B200MOE_CT_INT8) b += align256((size_t)M * sizeof(float));
     if (compute_type == B200MOE_CT_FP4 && weight_layout == B200MOE_LAYOUT_ASCEND)
         b += (size_t)G * (size_t)K * (size_t)(N / 2);
     return b;
@@ -569,7 +604,7 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
         return B200MOE_ERR_SHAPE;
     if ((K % kBK) != 0 || (N % kBN) != 0) return B200MOE_ERR_SHAPE;
     if (compute_type == B200MOE_CT_FP8 && (K % 128) != 0) return B200MOE_ERR_SHAPE;
-    if (compute_type == B200MOE_CT_INT4) return B200MOE_ERR_UNSUPPORTED;
+    if (compute_type == B200MOE_CT_INT4 && (K % 128) != 0) return B200MOE_ERR_SHAPE;
     if (M == 0) return B200MOE_OK;
     if (!x || !weight || !scale || !group_list || !y) return B200MOE_ERR_NULL_POINTER;
     if (!aligned16(x) || !aligned16(weight) || !aligned16(scale) || !aligned16(y) || (offset && !aligned16(offset)))
@@ -602,6 +637,10 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
         }
         if (use_pair_kernel()) return launch_grouped_gemm_pair(B200MOE_CT_INT8, x, weight, a, s);
         return gm_launch<B200MOE_CT_INT8>(x, weight, a, s);
+    }
+    if (compute_type == B200MOE_CT_INT4) {
+        a.offset = static_cast<const __nv_bfloat16*>(offset);  // folded into the weights by the dequant warps
+        return gm_launch<B200MOE_CT_INT4>(x, weight, a, s);
     }
     if (compute_type == B200MOE_CT_FP8) {
         if (use_pair_kernel()) return launch_grouped_gemm_pair(B200MOE_CT_FP8, x, weight, a, s);

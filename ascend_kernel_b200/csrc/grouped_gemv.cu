@@ -80,7 +80,7 @@ struct GvTraits {
 
 // Decode the lane's 16 columns of one weight row into eight fp32 pairs.
 template <int MODE>
-__device__ __forceinline__ void gv_decode(const uint4& q, f32x2 (&w)[8], const f32x2 (&sc)[8]) {
+__device__ __forceinline__ void gv_decode(const uint4& q, f32x2 (&w)[8], const f32x2 (&sc)[8], const f32x2 (&tc)[8]) {
     if constexpr (MODE == B200MOE_CT_INT8) {
         const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
         const f32x2 kneg = pack2(-8388736.0f, -8388736.0f);  // -(2^23 + 128)
@@ -107,6 +107,18 @@ __device__ __forceinline__ void gv_decode(const uint4& q, f32x2 (&w)[8], const f
             }
             w[2 * i] = mul2(pack2(f[0], f[1]), k120);
             w[2 * i + 1] = mul2(pack2(f[2], f[3]), k120);
+        }
+    } else if constexpr (MODE == B200MOE_CT_INT4) {
+        // (w + o) * s = w * s + o * s in fp32: sc holds s, tc holds o * s of the row's 128-k group
+        const uint32_t w2[2] = {q.x ^ 0x88888888u, q.y ^ 0x88888888u};  // nibble + 8
+        const f32x2 kneg = pack2(-8388616.0f, -8388616.0f);             // -(2^23 + 8)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t word = w2[i >> 2];
+            const int sh = 8 * (i & 3);
+            const float f0 = __uint_as_float(((word >> sh) & 0xFu) | 0x4B000000u);
+            const float f1 = __uint_as_float(((word >> (sh + 4)) & 0xFu) | 0x4B000000u);
+            w[i] = fma2(add2(pack2(f0, f1), kneg), sc[i], tc[i]);
         }
     } else {  // FP4: q.x, q.y hold 16 codes; per-column scale of the current 16-row group
         const uint32_t w2[2] = {q.x, q.y};
@@ -137,9 +149,9 @@ __device__ __forceinline__ void gv_compute(const GemvArgs& a, const __nv_bfloat1
 #pragma unroll
         for (int c = 0; c < 8; ++c) acc[m][c] = 0ull;
 
-    f32x2 sc[8];
+    f32x2 sc[8], tc[8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) sc[c] = 0ull;
+    for (int c = 0; c < 8; ++c) sc[c] = tc[c] = 0ull;
 
     for (int k0 = warp * kGvWarpRows; k0 < a.K; k0 += kGvIterRows) {
         // ---- issue all loads of this step first ----
@@ -174,11 +186,29 @@ __device__ __forceinline__ void gv_compute(const GemvArgs& a, const __nv_bfloat1
             const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
             for (int c = 0; c < 8; ++c) sc[c] = pack2(__uint_as_float(sw[c] << 16), __uint_as_float(sw[c] & 0xFFFF0000u));
+        } else if constexpr (MODE == B200MOE_CT_INT4) {
+            // one scale / offset row per 128 k rows; the 16 rows of this step lie inside one group
+            const size_t so = ((size_t)g * (a.K >> 7) + (k0 >> 7)) * a.N + col0;
+            const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.scale) + so);
+            const uint4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
+            uint4 o0 = make_uint4(0u, 0u, 0u, 0u), o1 = o0;
+            if (a.offset != nullptr) {
+                const uint4* op = reinterpret_cast<const uint4*>(a.offset + so);
+                o0 = __ldg(op);
+                o1 = __ldg(op + 1);
+            }
+            const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            const uint32_t ow[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                sc[c] = pack2(__uint_as_float(sw[c] << 16), __uint_as_float(sw[c] & 0xFFFF0000u));
+                tc[c] = mul2(pack2(__uint_as_float(ow[c] << 16), __uint_as_float(ow[c] & 0xFFFF0000u)), sc[c]);
+            }
         }
 #pragma unroll
         for (int u = 0; u < kGvUnroll; ++u) {
             f32x2 w[8];
-            gv_decode<MODE>(q[u], w, sc);
+            gv_decode<MODE>(q[u], w, sc, tc);
 #pragma unroll
             for (int m = 0; m < MB; ++m) {
                 float xv = __uint_as_float(half ? (xw[m][u] & 0xFFFF0000u) : (xw[m][u] << 16));
@@ -348,7 +378,7 @@ extern "C" int b200moe_grouped_gemv(const void* x, const void* weight, const voi
         return B200MOE_ERR_SHAPE;
     if ((K % 64) != 0 || (N % kGvSlabN) != 0) return B200MOE_ERR_SHAPE;
     if (compute_type == B200MOE_CT_FP8 && ((K % 128) != 0 || (N % 128) != 0)) return B200MOE_ERR_SHAPE;
-    if (compute_type == B200MOE_CT_INT4) return B200MOE_ERR_UNSUPPORTED;
+    if (compute_type == B200MOE_CT_INT4 && (K % 128) != 0) return B200MOE_ERR_SHAPE;
     if (M == 0) return B200MOE_OK;
     if (!x || !weight || !scale || !group_list || !y) return B200MOE_ERR_NULL_POINTER;
     if (!aligned16(x) || !aligned16(weight) || !aligned16(scale) || !aligned16(y) ||
@@ -379,6 +409,7 @@ extern "C" int b200moe_grouped_gemv(const void* x, const void* weight, const voi
     switch (compute_type) {
         case B200MOE_CT_INT8: return gv_launch<B200MOE_CT_INT8>(a, s);
         case B200MOE_CT_FP8: return gv_launch<B200MOE_CT_FP8>(a, s);
+        case B200MOE_CT_INT4: return gv_launch<B200MOE_CT_INT4>(a, s);
         default: return gv_launch<B200MOE_CT_FP4>(a, s);
     }
 }

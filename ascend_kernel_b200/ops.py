@@ -100,8 +100,8 @@ def grouped_gemm(x, weight, antiquantScaleOptional, antiquantOffsetOptional, gro
     ws = _run(_lib.b200moe_grouped_gemm, _lib.b200moe_grouped_gemm_workspace_bytes, "grouped_gemm", x, weight,
               antiquantScaleOptional, offset, groupListOptional, output, ct, group_list_type,
               LAYOUT[weight_layout], M, K, N, G)
-    if M > 0:  # GEMM + row sums for the offset term + layout conversion of pre-shuffled fp4 weights
-        _count(1 + (offset is not None) + (ct == CT["fp4"] and weight_layout == "ascend"))
+    if M > 0:  # GEMM + row sums for the int8 offset term + layout conversion of pre-shuffled fp4 weights
+        _count(1 + (offset is not None and ct == CT["int8"]) + (ct == CT["fp4"] and weight_layout == "ascend"))
     return ws if return_workspace else None
 
 

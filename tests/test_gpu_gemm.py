@@ -125,3 +125,28 @@ def test_bad_group_list_is_clamped_and_reported():
     x, w, scale, offset, cnt = _int8_case([10, 20], 64, 256, 9, False)
     out, st = run_gemm(x, w, scale, None, torch.tensor([20, 5]), "int8")
     assert st[0] == 1 and st[1] == 1
+
+
+def _int4_case(counts, K, N, seed, with_offset):
+    gen = torch.Generator().manual_seed(seed)
+    G = len(counts)
+    counts = torch.tensor(counts, dtype=torch.int64)
+    M = int(counts.sum())
+    x = torch.randn(M, K, generator=gen).to(torch.bfloat16)
+    w = torch.randint(0, 256, (G, K, N // 2), generator=gen, dtype=torch.uint8).view(torch.int8)
+    scale = (torch.rand(G, K // 128, N, generator=gen) * 0.045 + 0.005).to(torch.bfloat16)
+    offset = (torch.rand(G, K // 128, N, generator=gen) * 4 - 2).to(torch.bfloat16) if with_offset else None
+    return x, w, scale, offset, counts
+
+
+@pytest.mark.parametrize("counts,K,N,with_offset", [
+    ([16, 48, 32, 32], 256, 512, True),
+    ([127, 129, 0, 1, 300], 384, 256, True),
+    ([70, 3], 128, 512, False),
+])
+def test_int4_per_group_scales_match_oracle(counts, K, N, with_offset):
+    x, w, scale, offset, cnt = _int4_case(counts, K, N, 23, with_offset)
+    gold = O.golden_f32(x, w, scale, offset, cnt, "int4", O.GROUP_LIST_COUNTS)
+    out, st = run_gemm(x, w, scale, offset, cnt, "int4", gl_type=1)
+    assert st == (0, 0)
+    assert_close_to_golden(out, gold)

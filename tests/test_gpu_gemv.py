@@ -104,3 +104,19 @@ def test_bad_group_list_is_clamped_and_reported():
     bad = torch.tensor([1, 0, 99], dtype=torch.int64)  # not monotone, then beyond M
     out, st = run_gemv(x, w, scale, bad, "int8")
     assert st[0] == 1
+
+
+@pytest.mark.parametrize("counts,K,N,with_offset", [([1, 0, 2, 4, 0, 3], 256, 512, True), ([1, 6], 384, 256, False)])
+def test_int4_per_group_scales_match_oracle(counts, K, N, with_offset):
+    gen = torch.Generator().manual_seed(29)
+    G = len(counts)
+    cnt = torch.tensor(counts, dtype=torch.int64)
+    M = int(cnt.sum())
+    x = torch.randn(M, K, generator=gen).to(torch.bfloat16)
+    w = torch.randint(0, 256, (G, K, N // 2), generator=gen, dtype=torch.uint8).view(torch.int8)
+    scale = (torch.rand(G, K // 128, N, generator=gen) * 0.045 + 0.005).to(torch.bfloat16)
+    offset = (torch.rand(G, K // 128, N, generator=gen) * 4 - 2).to(torch.bfloat16) if with_offset else None
+    gold = O.golden_f32(x, w, scale, offset, cnt, "int4", O.GROUP_LIST_COUNTS, gemv=True)
+    out, st = run_gemv(x, w, scale, cnt, "int4", offset, gl_type=1)
+    assert st == (0, 0)
+    assert_close_to_golden(out, gold)
