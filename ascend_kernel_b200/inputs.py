@@ -106,6 +106,31 @@ def config3(device, n_rows=65536, n_experts=256, K=7168, N=4096, seed=3, alpha=1
     return dict(x=x, weight=w, scale=scale, offset=offset, counts=counts.to(device))
 
 
+def config3_variants(device, kind, n_rows=65536, n_experts=256, K=7168, N=4096, seed=3, alpha=1.2):
+    """Same shape and row split as config3 with another weight format:
+    "int4": two's-complement pairs [G,K,N/2], bf16 scale U(0.005,0.05) / offset U(-2,2) [G,K/128,N];
+    "fp8":  e4m3 codes [G,K,N] (uniform bytes), fp32 scale ~N(0,1) [G,K/128,N/128] (reference format);
+    "fp4":  e2m1 pairs [G,K,N/2] canonical order, bf16 scale U(0.25,3.25) [G,K/16,N] (reference format)."""
+    counts = zipf_counts(n_experts, n_rows, alpha, seed)
+    gen = _gen(seed, device)
+    x = torch.randn(n_rows, K, generator=gen, device=device).to(torch.bfloat16)
+    cols = N if kind == "fp8" else N // 2
+    w = torch.empty(n_experts, K, cols, dtype=torch.uint8, device=device)
+    for g in range(n_experts):
+        w[g] = torch.randint(0, 256, (K, cols), generator=gen, device=device, dtype=torch.uint8)
+    offset = None
+    if kind == "int4":
+        scale = _uniform((n_experts, K // 128, N), 0.005, 0.05, gen, device)
+        offset = _uniform((n_experts, K // 128, N), -2.0, 2.0, gen, device)
+        w = w.view(torch.int8)
+    elif kind == "fp8":
+        scale = torch.randn(n_experts, K // 128, N // 128, generator=gen, device=device, dtype=torch.float32)
+    else:
+        scale = _uniform((n_experts, K // 16, N), 0.25, 3.25, gen, device)
+        w = w.view(torch.int8)
+    return dict(x=x, weight=w, scale=scale, offset=offset, counts=counts.to(device))
+
+
 def config4(device, n_tokens=4096, hidden=7168, n_experts=256, inter=2048, top_k=8, seed=4,
             expert_lo=0, expert_hi=None):
     """MoE FFN layer inputs.  Tokens and router logits are global; weights are drawn per expert so

@@ -29,6 +29,7 @@ class CudaRowOps:
     """The row-sized operations of the layer, on this package's CUDA kernels."""
 
     route = staticmethod(ops.moe_route)
+    combine_to_host = staticmethod(ops.combine_to_host)
     regroup_index = staticmethod(ops.moe_regroup_index)
     gather_rows = staticmethod(ops.gather_rows)
     combine = staticmethod(ops.combine)
@@ -83,8 +84,14 @@ class MoELayer:
         return y
 
     # ---- one step --------------------------------------------------------------------------
-    def forward(self, x, logits, record: bool = False):
-        """x bf16 [T, H], logits bf16 [T, E] on this rank's device -> bf16 [T, H]."""
+    def forward(self, x, logits, record: bool = False, out_host=None):
+        """x bf16 [T, H], logits bf16 [T, E] on this rank's device -> bf16 [T, H] (on the device, or
+        written by the combine kernel into the pinned host tensor ``out_host`` when one is given)."""
+        def finish(y, slot, wts):
+            if out_host is not None:
+                return self.ops.combine_to_host(y, slot, wts, out_host)
+            return self.ops.combine(y, slot, wts)
+
         marks = [] if record else None
 
         def mark(name):
@@ -101,7 +108,7 @@ class MoELayer:
         if self.world == 1:
             y = self._experts(send, counts, record)
             mark("experts")
-            out = self.ops.combine(y, slot, wts)
+            out = finish(y, slot, wts)
             mark("combine")
             self.phases = marks
             return out
@@ -130,7 +137,7 @@ class MoELayer:
         ret = torch.empty(send.shape[0], self.hidden, dtype=torch.bfloat16, device=self.device)
         dist.all_to_all_single(ret, back, in_split, out_split, group=self.group)
         mark("return")
-        out = self.ops.combine(ret, slot, wts)
+        out = finish(ret, slot, wts)
         mark("combine")
         self.phases = marks
         return out
@@ -138,11 +145,10 @@ class MoELayer:
     def forward_host(self, x_host, logits_host, out_host=None):
         """End-to-end call with host buffers: pinned host -> device copies of this step's inputs,
         the layer, and the device -> host read of the result."""
-        x = x_host.to(self.device, non_blocking=True)
         lg = logits_host.to(self.device, non_blocking=True)
-        out = self.forward(x, lg)
+        x = x_host.to(self.device, non_blocking=True)
         if out_host is None:
-            out_host = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
-        out_host.copy_(out, non_blocking=True)
+            out_host = torch.empty(x_host.shape, dtype=torch.bfloat16, pin_memory=True)
+        self.forward(x, lg, out_host=out_host)
         torch.cuda.current_stream().synchronize()
         return out_host

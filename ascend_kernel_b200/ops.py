@@ -229,6 +229,24 @@ def moe_regroup_index(recv_counts, n_recv: int):
     return pos, inv, local_counts
 
 
+def combine_to_host(y, slot, weight, out_host):
+    """combine() writing its result straight into pinned host memory (the device -> host transfer of
+    the layer output rides on the kernel's stores instead of a separate copy)."""
+    _need_cuda(y=y, slot=slot, weight=weight)
+    if not (isinstance(out_host, torch.Tensor) and out_host.is_pinned() and out_host.is_contiguous()
+            and out_host.dtype == torch.bfloat16):
+        raise RuntimeError("out_host must be a contiguous pinned bfloat16 host tensor")
+    T, top_k = slot.shape
+    if tuple(out_host.shape) != (T, y.shape[1]):
+        raise RuntimeError("out_host has the wrong shape")
+    with torch.cuda.device(y.device):
+        rc = _lib.b200moe_combine(_ptr(y), _ptr(slot), _ptr(weight), out_host.data_ptr(), T, top_k, y.shape[1],
+                                  _stream())
+    _abi.check(rc, "combine")
+    _count(1)
+    return out_host
+
+
 def read_status(ws):
     import ctypes
 

@@ -190,8 +190,12 @@ def workload_config(n_gpus):
 # per-kernel lines (N = 1)
 # ------------------------------------------------------------------------------------------------
 def time_launches(fn, n_warm, n_iter):
+    """Median CUDA-event time of one call of fn (its own kernels only), after an idle second so a
+    kernel timed alone is not measured at the power-capped clock the previous one left behind."""
     import torch
 
+    torch.cuda.synchronize()
+    time.sleep(1.0)
     for _ in range(n_warm):
         fn()
     torch.cuda.synchronize()
@@ -241,6 +245,24 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
                                              "shape": {"M": Mv, "K": K, "N": N, "G": G, "active_experts": n_act}}
     del c, y, xv, yv
     torch.cuda.empty_cache()
+    # ---- the other weight formats at the prefill shape (int4 = configuration 3 variant B; fp8 / fp4 = the
+    # reference's own formats, cumulative group_list, canonical fp4 layout) ----
+    if "gemm" in which:
+        for kind in ("int4", "fp8", "fp4"):
+            c = (inputs.config3_variants(dev, kind) if not quick
+                 else inputs.config3_variants(dev, kind, n_rows=8192, n_experts=32))
+            M, K = c["x"].shape
+            y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            gl = c["counts"] if kind == "int4" else torch.cumsum(c["counts"], 0)
+            off = c["offset"] if kind == "int4" else torch.zeros(1, device=dev)
+            fn = (lambda: ak.grouped_gemm(c["x"], c["weight"], c["scale"], off, gl, kind, y,
+                                          group_list_type=1 if kind == "int4" else 0, weight_layout="canonical"))
+            ms = time_launches(fn, 2, 5)
+            flops = 2.0 * M * K * N
+            out[f"grouped_gemm_prefill_{kind}"] = {"ms": ms, "tflops": flops / ms / 1e9,
+                                                   "frac_of_measured_sustained": flops / ms / 1e9 / peaks["bf16_tflops_sustained"]}
+            del c, y
+            torch.cuda.empty_cache()
     if not quick and "gemv" in which:
         gen = torch.Generator(device=dev).manual_seed(11)
         K2, N2 = 2048, 7168
