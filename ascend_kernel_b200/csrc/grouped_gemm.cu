@@ -222,35 +222,6 @@ __device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint8_t
                 o[2 * i] = pack_bf16x2(f[0], f[1]);
                 o[2 * i + 1] = pack_bf16x2(f[2], f[3]);
             }
-        } else if constexpr (MODE == B200MOE_CT_INT4) {
-            // v = (w + o) * s in fp32 with the scale / offset of the row's 128-k group, then the
-            // hi or lo bf16 part according to the stage's parity
-            const int kb = kt >> 1;
-            const bool lo_part = (kt & 1) != 0;
-            const size_t so = ((size_t)ti.g * (a.K >> 7) + ((kb * kBK + k) >> 7)) * a.N + ti.n0 + c16 * 16;
-            const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.scale) + so);
-            const uint4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
-            uint4 o0 = make_uint4(0u, 0u, 0u, 0u), o1 = o0;
-            if (a.offset != nullptr) {
-                const uint4* op = reinterpret_cast<const uint4*>(a.offset + so);
-                o0 = __ldg(op);
-                o1 = __ldg(op + 1);
-            }
-            const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-            const uint32_t ow[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
-            const uint32_t w2[2] = {q.x ^ 0x88888888u, q.y ^ 0x88888888u};  // nibble + 8
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {  // output pair i = columns 2i, 2i+1
-                const uint32_t word = w2[i >> 2];
-                const int sh = 8 * (i & 3);
-                const float w0 = __uint_as_float(((word >> sh) & 0xFu) | 0x4B000000u) - 8388616.0f;        // 2^23 + 8
-                const float w1 = __uint_as_float(((word >> (sh + 4)) & 0xFu) | 0x4B000000u) - 8388616.0f;
-                const float sc0 = __uint_as_float(sw[i] << 16), sc1 = __uint_as_float(sw[i] & 0xFFFF0000u);
-                const float of0 = __uint_as_float(ow[i] << 16), of1 = __uint_as_float(ow[i] & 0xFFFF0000u);
-                const float v0 = (w0 + of0) * sc0, v1 = (w1 + of1) * sc1;
-                const uint32_t hi = pack_bf16x2(v0, v1);
-                o[i] = lo_part ? pack_bf16x2(v0 - __uint_as_float(hi << 16), v1 - __uint_as_float(hi & 0xFFFF0000u)) : hi;
-            }
         } else {  // FP4: 8 bytes = 16 codes, bf16 scale per 16 k rows per column
             const uint4* sp = reinterpret_cast<const uint4*>(
                 static_cast<const __nv_bfloat16*>(a.scale) +
@@ -266,6 +237,45 @@ __device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint8_t
         }
         *reinterpret_cast<uint4*>(bt + btile_offset(k, 2 * c16)) = make_uint4(o[0], o[1], o[2], o[3]);
         *reinterpret_cast<uint4*>(bt + btile_offset(k, 2 * c16 + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
+// int4 with per-128-k scale / offset: one pass over a k block produces both stages it feeds to the
+// tensor core, hi = bf16(v) and lo = bf16(v - hi) with v = (w + o) * s in fp32.  The thread's four
+// rows lie in the same 128-k group, so scale and offset are unpacked once per column pair.
+__device__ __forceinline__ void convert_block_int4(const PackedRegs<B200MOE_CT_INT4>& r, uint8_t* bt_hi, uint8_t* bt_lo,
+                                                   const GemmArgs& a, const TileInfo& ti, int kb, const DqLane& d) {
+    const int c16 = d.c16;
+    const size_t so = ((size_t)ti.g * (a.K >> 7) + ((kb * kBK) >> 7)) * a.N + ti.n0 + c16 * 16;
+    const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.scale) + so);
+    const uint4* op = a.offset != nullptr ? reinterpret_cast<const uint4*>(a.offset + so) : nullptr;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {  // columns 8h .. 8h+7: one 16-byte chunk of the bf16 tile per row
+        const uint4 s4 = __ldg(sp + h);
+        const uint4 o4 = op != nullptr ? __ldg(op + h) : make_uint4(0u, 0u, 0u, 0u);
+        const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w}, ow[4] = {o4.x, o4.y, o4.z, o4.w};
+        uint32_t hi[kDqRows][4], lo[kDqRows][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // column pair 8h + 2i, 8h + 2i + 1 = byte i of the word
+            const float sc0 = __uint_as_float(sw[i] << 16), sc1 = __uint_as_float(sw[i] & 0xFFFF0000u);
+            const float t0 = __uint_as_float(ow[i] << 16) * sc0, t1 = __uint_as_float(ow[i] & 0xFFFF0000u) * sc1;
+#pragma unroll
+            for (int j = 0; j < kDqRows; ++j) {
+                const uint32_t word = (h == 0 ? r.q[j].x : r.q[j].y) ^ 0x88888888u;  // nibble + 8
+                const float w0 = __uint_as_float(((word >> (8 * i)) & 0xFu) | 0x4B000000u) - 8388616.0f;  // 2^23 + 8
+                const float w1 = __uint_as_float(((word >> (8 * i + 4)) & 0xFu) | 0x4B000000u) - 8388616.0f;
+                const float v0 = fmaf(w0, sc0, t0), v1 = fmaf(w1, sc1, t1);
+                const uint32_t hh = pack_bf16x2(v0, v1);
+                hi[j][i] = hh;
+                lo[j][i] = pack_bf16x2(v0 - __uint_as_float(hh << 16), v1 - __uint_as_float(hh & 0xFFFF0000u));
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kDqRows; ++j) {
+            const uint32_t off = btile_offset(d.row + kDqRowStep * j, 2 * c16 + h);
+            *reinterpret_cast<uint4*>(bt_hi + off) = make_uint4(hi[j][0], hi[j][1], hi[j][2], hi[j][3]);
+            *reinterpret_cast<uint4*>(bt_lo + off) = make_uint4(lo[j][0], lo[j][1], lo[j][2], lo[j][3]);
+        }
     }
 }
 
@@ -477,12 +487,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
     } else if (warp >= kWarpDq0) {
         // ------------------------------ dequant ------------------------------
+        // A unit of work is one k block: one stage, or for int4 the hi and lo stages it produces.
+        constexpr int P = T::kParts;
         const int dq_tid = threadIdx.x - kWarpDq0 * 32;
         const int grp = dq_tid / (kDqGroupWarps * 32);
         const DqLane d = dq_lane(dq_tid % (kDqGroupWarps * 32));
         StageIter cur, pf;
         iter_start(cur, n_tiles, tile_prefix, row_start, a.G, n_nt);
-        for (int i = 0; i < grp && cur.valid; ++i) iter_next(cur, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
+        for (int i = 0; i < grp * P && cur.valid; ++i) iter_next(cur, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
         pf = cur;
         PackedRegs<MODE> regs[kPrefetch];
 #pragma unroll
@@ -490,31 +502,43 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             if (pf.valid) {
                 load_packed<MODE>(regs[u], weight, a, pf.ti, pf.kt, d);
 #pragma unroll
-                for (int i = 0; i < kDqGroups; ++i)
+                for (int i = 0; i < kDqGroups * P; ++i)
                     if (pf.valid) iter_next(pf, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
             }
         }
-        uint32_t ib = grp;
+        uint32_t ib = grp * P;
         bool ok = true;
         while (cur.valid && ok) {
 #pragma unroll
             for (int u = 0; u < kPrefetch; ++u) {
                 if (!cur.valid) break;
-                const uint32_t sbb = ib % kNS, phb = (ib / kNS) & 1;
+                uint32_t slot[P];
                 bool got = true;
-                if (ib >= kNS) got = gm_wait(&sb->empty[sbb], phb ^ 1, sb, a.status, 80 + (int)sbb);
+#pragma unroll
+                for (int p = 0; p < P; ++p) {
+                    const uint32_t n = ib + p;
+                    slot[p] = n % kNS;
+                    if (got && n >= kNS) got = gm_wait(&sb->empty[slot[p]], ((n / kNS) & 1) ^ 1, sb, a.status, 80 + (int)slot[p]);
+                }
                 if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-                convert_stage<MODE>(regs[u], b_ring + sbb * kBTileBytes, a, cur.ti, cur.kt, d);
+                if constexpr (MODE == B200MOE_CT_INT4)
+                    convert_block_int4(regs[u], b_ring + slot[0] * kBTileBytes, b_ring + slot[P - 1] * kBTileBytes, a, cur.ti,
+                                       cur.kt / P, d);
+                else
+                    convert_stage<MODE>(regs[u], b_ring + slot[0] * kBTileBytes, a, cur.ti, cur.kt, d);
                 ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->full[sbb]));
+                if (lane == 0) {
+#pragma unroll
+                    for (int p = 0; p < P; ++p) ptx::mbar_arrive(ptx::smem_u32(&sb->full[slot[p]]));
+                }
                 if (pf.valid) load_packed<MODE>(regs[u], weight, a, pf.ti, pf.kt, d);
 #pragma unroll
-                for (int i = 0; i < kDqGroups; ++i) {
+                for (int i = 0; i < kDqGroups * P; ++i) {
                     if (pf.valid) iter_next(pf, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
                     if (cur.valid) iter_next(cur, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
                 }
-                ib += kDqGroups;
+                ib += kDqGroups * P;
             }
         }
     }
