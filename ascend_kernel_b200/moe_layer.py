@@ -152,3 +152,55 @@ class MoELayer:
         self.forward(x, lg, out_host=out_host)
         torch.cuda.current_stream().synchronize()
         return out_host
+
+
+class HostPipeline:
+    """Host-buffer calls with ``depth`` steps in flight.
+
+    ``submit`` enqueues one step: the copy of its pinned-host inputs on a copy-in stream, the layer
+    on the caller's current stream, the copy of its result to pinned host memory on a copy-out
+    stream.  Step i+1's input copy and step i-1's output copy overlap step i's kernels (PCIe is
+    full duplex, the copy engines are independent of the SMs); every step still moves all of its
+    inputs and its whole result.  ``submit`` returns an event that completes when the step's result
+    is in ``out_host``; ``drain`` waits for everything submitted."""
+
+    def __init__(self, layer: MoELayer, depth: int = 2):
+        self.layer, self.depth = layer, depth
+        self.s_in, self.s_out = torch.cuda.Stream(layer.device), torch.cuda.Stream(layer.device)
+        self.slots = [dict(x=None, lg=None, out=None, in_done=None, comp_done=None, out_done=None)
+                      for _ in range(depth)]
+        self.n = 0
+
+    def submit(self, x_host, logits_host, out_host):
+        sl = self.slots[self.n % self.depth]
+        self.n += 1
+        main = torch.cuda.current_stream()
+        if sl["x"] is None or sl["x"].shape != x_host.shape:
+            sl["x"] = torch.empty(x_host.shape, dtype=x_host.dtype, device=self.layer.device)
+            sl["lg"] = torch.empty(logits_host.shape, dtype=logits_host.dtype, device=self.layer.device)
+        with torch.cuda.stream(self.s_in):
+            if sl["comp_done"] is not None:          # the step that last read these input buffers
+                self.s_in.wait_event(sl["comp_done"])
+            sl["lg"].copy_(logits_host, non_blocking=True)
+            sl["x"].copy_(x_host, non_blocking=True)
+            sl["in_done"] = torch.cuda.Event()
+            sl["in_done"].record(self.s_in)
+        main.wait_event(sl["in_done"])
+        if sl["out_done"] is not None:               # the copy that last read this slot's result
+            main.wait_event(sl["out_done"])
+        sl["out"] = self.layer.forward(sl["x"], sl["lg"])
+        sl["comp_done"] = torch.cuda.Event()
+        sl["comp_done"].record(main)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(sl["comp_done"])
+            out_host.copy_(sl["out"], non_blocking=True)
+            sl["out_done"] = torch.cuda.Event()
+            sl["out_done"].record(self.s_out)
+        return sl["out_done"]
+
+    def drain(self):
+        main = torch.cuda.current_stream()
+        for sl in self.slots:
+            if sl["out_done"] is not None:
+                main.wait_event(sl["out_done"])
+        main.synchronize()

@@ -12,8 +12,10 @@ scale/offset) over a batch of seeded synthetic tokens.  The global batch is fixe
 scaling): each of the N ranks holds 4096/N tokens and 256/N experts.
 
 Rank 0 prints ONE JSON line.  `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is
-the same metric through the public host-buffer call (pinned host -> device copies of the step's
-inputs and the device -> host read of the result inside the timed region); `roofline` covers the
+the same metric through the public host-buffer call (`HostPipeline.submit`: pinned host -> device
+copies of every step's inputs and the device -> host read of every step's result inside the timed
+region, two steps in flight so that the copies of neighbouring steps overlap the kernels;
+`single_step_latency_ms` is the unpipelined `MoELayer.forward_host`); `roofline` covers the
 dominant kernel of the step (the tcgen05 grouped GEMM, both launches); `kernels` (N=1 only) holds
 the three hot-path kernels at their own benchmark configurations (prefill grouped GEMM, decode
 grouped GEMV, FP4 dequant) with their roofline fractions of the measured peaks; `cpu_baseline` is
@@ -385,6 +387,23 @@ def run_ours(args):
         layer.forward_host(x_host, lg_host, out_host)
     e1.record()
     barrier()
+    latency_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    # the same calls with two steps in flight (copy-in / kernels / copy-out on three streams)
+    from ascend_kernel_b200.moe_layer import HostPipeline
+
+    pipe = HostPipeline(layer, depth=2)
+    outs = [out_host, torch.empty_like(out_host).pin_memory()]
+    for i in range(min(3, args.warmup)):
+        pipe.submit(x_host, lg_host, outs[i % 2])
+    pipe.drain()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        pipe.submit(x_host, lg_host, outs[i % 2])
+    pipe.drain()
+    e1.record()
+    barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
     h2d = (x_host.numel() * 2 + lg_host.numel() * 2) * world
     d2h = out_host.numel() * 2 * world
@@ -405,7 +424,7 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "bf16 x int8 -> fp32 accumulate", "data": "synthetic",
         "config": workload_config(world),
         "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms},
+                "ms_per_step": e2e_ms, "steps_in_flight": 2, "single_step_latency_ms": latency_ms},
         "gpu_launches": launches * args.steps, "gpu_launches_per_step": launches,
         "roofline": roofline, "clocks": clk.result, "phases_ms_rank0": {k: round(v, 4) for k, v in phases.items()},
     }

@@ -167,6 +167,28 @@ def test_cuda_layer_matches_oracle():
 
 
 @pytest.mark.gpu
+def test_host_pipeline_matches_single_calls():
+    """Five different batches through the two-steps-in-flight host pipeline give the bits of the
+    one-at-a-time host call (buffer reuse across slots must not mix steps up)."""
+    from ascend_kernel_b200.moe_layer import HostPipeline, MoELayer
+
+    c = small_case(T=200, H=256, E=8, I=256, k=2)
+    d = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
+    layer = MoELayer(d["w13"], d["s13"], d["o13"], d["w2"], d["s2"], d["o2"], c["E"], c["top_k"])
+    g = torch.Generator().manual_seed(11)
+    xs = [torch.randn(c["x"].shape, generator=g).to(torch.bfloat16).pin_memory() for _ in range(5)]
+    lgs = [c["logits"][torch.randperm(c["logits"].shape[0], generator=g)].contiguous().pin_memory() for _ in range(5)]
+    want = [layer.forward_host(x, lg).clone() for x, lg in zip(xs, lgs)]
+    pipe = HostPipeline(layer, depth=2)
+    outs = [torch.empty(c["x"].shape, dtype=torch.bfloat16).pin_memory() for _ in range(5)]
+    for x, lg, o in zip(xs, lgs, outs):
+        pipe.submit(x, lg, o)
+    pipe.drain()
+    for o, w in zip(outs, want):
+        assert torch.equal(o.view(torch.int16), w.view(torch.int16))
+
+
+@pytest.mark.gpu
 def test_aux_kernels_match_torch():
     import ascend_kernel_b200 as ak
 
