@@ -219,7 +219,10 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
     dev = "cuda"
     out = {}
     # ---- prefill grouped GEMM (configuration 3, variant A) ----
-    c = inputs.config3(dev) if not quick else inputs.config3(dev, n_rows=8192, n_experts=32)
+    # quick cases stay larger than L2 and below 2 GB of weights; the GEMV one has 64 experts so that
+    # its work items (active experts x 16 slabs) fill the 296 resident CTAs more than twice
+    n_quick = 64 if tuple(which) == ("gemv",) else 32
+    c = inputs.config3(dev) if not quick else inputs.config3(dev, n_rows=8192, n_experts=n_quick)
     M, K = c["x"].shape
     G, _, N = c["weight"].shape
     y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
