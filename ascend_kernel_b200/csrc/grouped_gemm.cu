@@ -48,8 +48,9 @@ constexpr int kWarpA = 0, kWarpMma = 2, kWarpEpi0 = 4, kEpiWarps = 8, kWarpDq0 =
 // other's waits.
 constexpr int kDqGroups = 2;
 constexpr int kDqGroupWarps = 8;
-constexpr int kDqRowStep = 2 * kDqGroupWarps;  // a warp owns two rows; the group covers this many per pass
-constexpr int kDqRows = kBK / kDqRowStep;      // k rows converted by a thread per stage
+constexpr int kDqRows = kBK / (2 * kDqGroupWarps);  // k rows converted by a thread per stage
+constexpr int kDqRowStep = 2;                        // distance between a thread's rows
+constexpr int kDqWarpRows = 2 * kDqRows;             // a warp owns this many consecutive k rows
 constexpr int kSuperRows = 8;  // m-tiles per L2 super-tile
 constexpr int kAHalfBytes = kBM * kBK * 2;   // one 128-row box
 constexpr int kATileBytes = 2 * kAHalfBytes;  // an x stage holds both row halves
@@ -144,20 +145,21 @@ __device__ __forceinline__ uint32_t btile_offset(int k, int nchunk16) {  // nchu
     return (uint32_t)((nchunk16 >> 3) * (kBK * 128) + k * 128 + (((nchunk16 & 7) ^ (k & 7)) << 4));
 }
 
-// Thread -> (row, 16-column chunk) assignment of the dequant warps.  A warp owns two consecutive
-// k rows (an even one and the next).  Each quarter-warp holds four lanes on the even row in
+// Thread -> (row, 16-column chunk) assignment of the dequant warps.  A warp owns kDqWarpRows
+// consecutive k rows (inside one 16-row scale group of the fp4 format) and converts them two at a
+// time (an even one and the next).  Each quarter-warp holds four lanes on the even row in
 // 64-column block p and four lanes on the odd row in block p^1: the 128-bit stores of a quarter
 // then hit eight different 16-byte bank groups (the swizzle term k&7 differs in its low bit
 // between the two rows), and the packed loads of a warp still cover both rows contiguously.
 struct DqLane {
-    int row;  // 0 .. kDqRowStep-1: the thread converts k = row + kDqRowStep * j, j < kDqRows, of its stages
+    int row;  // the thread converts k = row + kDqRowStep * j, j < kDqRows, of its stages
     int c16;  // 16-column chunk 0..15
 };
 __device__ __forceinline__ DqLane dq_lane(int tid) {
     const int w = tid >> 5, l = tid & 31;
     const int p = l >> 3, q = l & 7, odd = q >> 2;
     DqLane d;
-    d.row = 2 * w + odd;
+    d.row = kDqWarpRows * w + odd;
     d.c16 = 4 * (p ^ odd) + (q & 3);
     return d;
 }
@@ -166,6 +168,7 @@ __device__ __forceinline__ DqLane dq_lane(int tid) {
 template <int MODE>
 struct PackedRegs {
     uint4 q[kDqRows];  // fp4 / int4 use only .x/.y of each
+    uint4 s[2];        // fp4 only: the bf16 scales of the thread's 16 columns (one 16-row group)
 };
 
 template <int MODE>
@@ -185,6 +188,13 @@ __device__ __forceinline__ void load_packed(PackedRegs<MODE>& r, const uint8_t* 
         } else {
             r.q[j] = __ldg(reinterpret_cast<const uint4*>(p));
         }
+    }
+    if constexpr (MODE == B200MOE_CT_FP4) {
+        const uint4* sp = reinterpret_cast<const uint4*>(
+            static_cast<const __nv_bfloat16*>(a.scale) +
+            ((size_t)ti.g * (a.K >> 4) + ((kb * kBK + d.row) >> 4)) * a.N + ti.n0 + d.c16 * 16);
+        r.s[0] = __ldg(sp);
+        r.s[1] = __ldg(sp + 1);
     }
 }
 
@@ -209,24 +219,24 @@ __device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint8_t
             s8x4_to_bf16_even_odd(q.z, o[4], o[5]);
             s8x4_to_bf16_even_odd(q.w, o[6], o[7]);
         } else if constexpr (MODE == B200MOE_CT_FP8) {
+            // e4m3 byte -> bf16 with the 4 exponent and 3 mantissa bits placed under the bf16 exponent
+            // (exact after * 2^120, subnormals included), two values per instruction; widened to fp32,
+            // scaled with the block's fp32 scale and rounded once to bf16.
             const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                float f[4];
 #pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    const uint32_t p = prmt(w4[i], 0u, 0x0444u | (b << 12));
-                    const uint32_t dd = ((p >> 4) & 0x07F00000u) | (p & 0x80000000u);
-                    f[b] = (__uint_as_float(dd) * 1.329227995784916e36f) * sf;  // exact * 2^120, then fp32 scale
+                for (int hp = 0; hp < 2; ++hp) {
+                    const uint32_t t = prmt(w4[i], 0u, hp == 0 ? 0x1404u : 0x3424u);
+                    const uint32_t xb = ((t >> 4) & 0x07F007F0u) | (t & 0x80008000u);
+                    const uint32_t yb = mul_bf16x2(xb, 0x7B807B80u);  // * 2^120
+                    const float2 f = mul_f32x2(make_float2(__uint_as_float(yb << 16), __uint_as_float(yb & 0xFFFF0000u)),
+                                               make_float2(sf, sf));
+                    o[2 * i + hp] = pack_bf16x2(f.x, f.y);
                 }
-                o[2 * i] = pack_bf16x2(f[0], f[1]);
-                o[2 * i + 1] = pack_bf16x2(f[2], f[3]);
             }
-        } else {  // FP4: 8 bytes = 16 codes, bf16 scale per 16 k rows per column
-            const uint4* sp = reinterpret_cast<const uint4*>(
-                static_cast<const __nv_bfloat16*>(a.scale) +
-                ((size_t)ti.g * (a.K >> 4) + ((kt * kBK + k) >> 4)) * a.N + ti.n0 + c16 * 16);
-            const uint4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
+        } else {  // FP4: 8 bytes = 16 codes; the thread's rows share one 16-row scale group
+            const uint4 s0 = r.s[0], s1 = r.s[1];
             uint32_t v[4];
             e2m1x8_to_bf16(q.x, v);
             o[0] = mul_bf16x2(v[0], s0.x); o[1] = mul_bf16x2(v[1], s0.y);
