@@ -38,7 +38,7 @@ namespace b200moe {
 
 constexpr int kBM = 128, kBN = 256, kBK = 64;
 constexpr int kTileM = 2 * kBM;  // rows of an output tile (two MMA row halves)
-constexpr int kNS = 3;  // ring stages, each an x stage (32 KB) and a bf16 weight stage (32 KB)
+constexpr int kNS = 3;  // ring stages, each an x stage (32 KB) and a bf16 weight stage (32 KB); int4: 2 stages of 32 + 2 x 32 KB
 constexpr int kPrefetch = 2;  // packed stages held in registers ahead of the one being converted
 constexpr int kL2Ahead = 8;   // stages by which the L2 prefetch of packed weights leads the x-tile loads
 constexpr int kGemmThreads = 896;
@@ -61,9 +61,11 @@ template <int MODE>
 struct GmTraits {
     static constexpr bool kNibbles = (MODE == B200MOE_CT_FP4 || MODE == B200MOE_CT_INT4);
     // int4 with per-128-k scale/offset: (w + o) * s does not fit bf16, so every k block is fed to
-    // the tensor core twice -- stage 2i carries hi = bf16(v), stage 2i+1 carries lo = bf16(v - hi) --
-    // against the same x block; the fp32 accumulator then holds x @ v to about 2^-16 relative.
+    // the tensor core twice -- a stage carries two weight tiles, hi = bf16(v) and lo = bf16(v - hi),
+    // multiplied with the same x block; the fp32 accumulator then holds x @ v to about 2^-16 relative.
     static constexpr int kParts = (MODE == B200MOE_CT_INT4) ? 2 : 1;
+    // ring depth: 3 x (32 + 32 KB) or 2 x (32 + 64 KB), 192 KB either way
+    static constexpr int kStages = (kParts == 1) ? kNS : 2;
     static constexpr int kPRowBytes = kNibbles ? kBN / 2 : kBN;
     static constexpr int kPTileBytes = kPRowBytes * kBK;
 };
@@ -176,7 +178,7 @@ __device__ __forceinline__ void load_packed(PackedRegs<MODE>& r, const uint8_t* 
                                             const TileInfo& ti, int kt, const DqLane& d) {
     using T = GmTraits<MODE>;
     const size_t row_bytes = T::kNibbles ? (size_t)a.N / 2 : (size_t)a.N;
-    const int kb = kt / T::kParts;
+    const int kb = kt;
     const uint8_t* base = w + ((size_t)ti.g * a.K + (size_t)kb * kBK + d.row) * row_bytes +
                           (T::kNibbles ? (ti.n0 >> 1) + d.c16 * 8 : ti.n0 + d.c16 * 16);
 #pragma unroll
@@ -207,6 +209,7 @@ __device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint8_t
         sf = __ldg(static_cast<const float*>(a.scale) +
                    ((size_t)ti.g * (a.K >> 7) + ((kt * kBK) >> 7)) * (a.N >> 7) + ((ti.n0 + c16 * 16) >> 7));
     }
+    const f32x2 sf2 = pack_f32x2(sf, sf);
 #pragma unroll
     for (int j = 0; j < kDqRows; ++j) {
         const int k = d.row + kDqRowStep * j;
@@ -230,9 +233,8 @@ __device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint8_t
                     const uint32_t t = prmt(w4[i], 0u, hp == 0 ? 0x1404u : 0x3424u);
                     const uint32_t xb = ((t >> 4) & 0x07F007F0u) | (t & 0x80008000u);
                     const uint32_t yb = mul_bf16x2(xb, 0x7B807B80u);  // * 2^120
-                    const float2 f = mul_f32x2(make_float2(__uint_as_float(yb << 16), __uint_as_float(yb & 0xFFFF0000u)),
-                                               make_float2(sf, sf));
-                    o[2 * i + hp] = pack_bf16x2(f.x, f.y);
+                    const f32x2 f = mul_f32x2(pack_u32x2(yb << 16, yb & 0xFFFF0000u), sf2);
+                    o[2 * i + hp] = pack_bf16x2(f32x2_lo(f), f32x2_hi(f));
                 }
             }
         } else {  // FP4: 8 bytes = 16 codes; the thread's rows share one 16-row scale group
@@ -251,33 +253,57 @@ __device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint8_t
 }
 
 // int4 with per-128-k scale / offset: one pass over a k block produces both stages it feeds to the
-// tensor core, hi = bf16(v) and lo = bf16(v - hi) with v = (w + o) * s in fp32.  The thread's four
-// rows lie in the same 128-k group, so scale and offset are unpacked once per column pair.
-__device__ __forceinline__ void convert_block_int4(const PackedRegs<B200MOE_CT_INT4>& r, uint8_t* bt_hi, uint8_t* bt_lo,
-                                                   const GemmArgs& a, const TileInfo& ti, int kb, const DqLane& d) {
-    const int c16 = d.c16;
-    const size_t so = ((size_t)ti.g * (a.K >> 7) + ((kb * kBK) >> 7)) * a.N + ti.n0 + c16 * 16;
+// tensor core, hi = bf16(v) and lo = bf16(v - hi) with v = w * s + o * s in fp32.  The thread's
+// rows lie in the same 128-k group, so its 16 scales and offsets are loaded once per k block
+// (before the wait for the stage, so that their latency is hidden by it).
+struct Int4Scales {
+    uint4 s[2], o[2];
+};
+__device__ __forceinline__ Int4Scales load_int4_scales(const GemmArgs& a, const TileInfo& ti, int kb, const DqLane& d) {
+    const size_t so = ((size_t)ti.g * (a.K >> 7) + ((kb * kBK) >> 7)) * a.N + ti.n0 + d.c16 * 16;
     const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.scale) + so);
-    const uint4* op = a.offset != nullptr ? reinterpret_cast<const uint4*>(a.offset + so) : nullptr;
+    Int4Scales r;
+    r.s[0] = __ldg(sp);
+    r.s[1] = __ldg(sp + 1);
+    if (a.offset != nullptr) {
+        const uint4* op = reinterpret_cast<const uint4*>(a.offset + so);
+        r.o[0] = __ldg(op);
+        r.o[1] = __ldg(op + 1);
+    } else {
+        r.o[0] = r.o[1] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    return r;
+}
+
+__device__ __forceinline__ void convert_block_int4(const PackedRegs<B200MOE_CT_INT4>& r, const Int4Scales& sc,
+                                                   uint8_t* bt_hi, uint8_t* bt_lo, const DqLane& d) {
+    const int c16 = d.c16;
+    const f32x2 kMagic = pack_f32x2(8388616.0f, 8388616.0f);  // 2^23 + 8
 #pragma unroll
     for (int h = 0; h < 2; ++h) {  // columns 8h .. 8h+7: one 16-byte chunk of the bf16 tile per row
-        const uint4 s4 = __ldg(sp + h);
-        const uint4 o4 = op != nullptr ? __ldg(op + h) : make_uint4(0u, 0u, 0u, 0u);
-        const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w}, ow[4] = {o4.x, o4.y, o4.z, o4.w};
+        const uint32_t sw[4] = {sc.s[h].x, sc.s[h].y, sc.s[h].z, sc.s[h].w};
+        const uint32_t ow[4] = {sc.o[h].x, sc.o[h].y, sc.o[h].z, sc.o[h].w};
+        uint32_t lo_n[kDqRows], hi_n[kDqRows];
+#pragma unroll
+        for (int j = 0; j < kDqRows; ++j) {
+            const uint32_t word = (h == 0 ? r.q[j].x : r.q[j].y) ^ 0x88888888u;  // nibble + 8, unsigned
+            lo_n[j] = word & 0x0F0F0F0Fu;         // even columns, one per byte
+            hi_n[j] = (word >> 4) & 0x0F0F0F0Fu;  // odd columns
+        }
         uint32_t hi[kDqRows][4], lo[kDqRows][4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {  // column pair 8h + 2i, 8h + 2i + 1 = byte i of the word
-            const float sc0 = __uint_as_float(sw[i] << 16), sc1 = __uint_as_float(sw[i] & 0xFFFF0000u);
-            const float t0 = __uint_as_float(ow[i] << 16) * sc0, t1 = __uint_as_float(ow[i] & 0xFFFF0000u) * sc1;
+            const f32x2 s2 = pack_f32x2(__uint_as_float(sw[i] << 16), __uint_as_float(sw[i] & 0xFFFF0000u));
+            const f32x2 t2 = mul_f32x2(pack_f32x2(__uint_as_float(ow[i] << 16), __uint_as_float(ow[i] & 0xFFFF0000u)), s2);
 #pragma unroll
             for (int j = 0; j < kDqRows; ++j) {
-                const uint32_t word = (h == 0 ? r.q[j].x : r.q[j].y) ^ 0x88888888u;  // nibble + 8
-                const float w0 = __uint_as_float(((word >> (8 * i)) & 0xFu) | 0x4B000000u) - 8388616.0f;  // 2^23 + 8
-                const float w1 = __uint_as_float(((word >> (8 * i + 4)) & 0xFu) | 0x4B000000u) - 8388616.0f;
-                const float v0 = fmaf(w0, sc0, t0), v1 = fmaf(w1, sc1, t1);
-                const uint32_t hh = pack_bf16x2(v0, v1);
+                // byte i under the fp32 pattern of 2^23: the float 2^23 + nibble + 8
+                const f32x2 wm = pack_u32x2(prmt(lo_n[j], 0x4B000000u, 0x7440u + i), prmt(hi_n[j], 0x4B000000u, 0x7440u + i));
+                const f32x2 v = fma_f32x2(sub_f32x2(wm, kMagic), s2, t2);
+                const uint32_t hh = pack_bf16x2(f32x2_lo(v), f32x2_hi(v));
                 hi[j][i] = hh;
-                lo[j][i] = pack_bf16x2(v0 - __uint_as_float(hh << 16), v1 - __uint_as_float(hh & 0xFFFF0000u));
+                const f32x2 l = sub_f32x2(v, pack_u32x2(hh << 16, hh & 0xFFFF0000u));
+                lo[j][i] = pack_bf16x2(f32x2_lo(l), f32x2_hi(l));
             }
         }
 #pragma unroll
@@ -320,14 +346,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* a_ring = base;
-    uint8_t* b_ring = a_ring + kNS * kATileBytes;
-    GmBarriers* sb = reinterpret_cast<GmBarriers*>(b_ring + kNS * kBTileBytes);
+    constexpr int NS = T::kStages, P = T::kParts;
+    uint8_t* b_ring = a_ring + NS * kATileBytes;
+    GmBarriers* sb = reinterpret_cast<GmBarriers*>(b_ring + NS * P * kBTileBytes);
     int* row_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sb) + 256);
     int* tile_prefix = row_start + (a.G + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_nt = a.N / kBN;
-    const int n_kt = (a.K / kBK) * GmTraits<MODE>::kParts;  // stages per tile
+    const int n_kt = a.K / kBK;  // stages per tile
 
     load_row_starts(a.group_list, a.G, a.M, a.gl_type, row_start, a.status);
     if (threadIdx.x == 0) {
@@ -339,7 +366,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
         sb->n_tiles = acc;
         sb->abort = 0;
-        for (int i = 0; i < kNS; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->full[i]), 1 + kDqGroupWarps); ptx::mbar_init(ptx::smem_u32(&sb->empty[i]), 1); }
+        for (int i = 0; i < NS; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->full[i]), 1 + kDqGroupWarps); ptx::mbar_init(ptx::smem_u32(&sb->empty[i]), 1); }
         ptx::mbar_init(ptx::smem_u32(&sb->t_full), 1);
         ptx::mbar_init(ptx::smem_u32(&sb->t_empty), kEpiWarps);
         ptx::mbar_init(ptx::smem_u32(&sb->drain), 1);
@@ -369,31 +396,31 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             StageIter far;
             iter_start(far, n_tiles, tile_prefix, row_start, a.G, n_nt);
             for (int i = 0; i < kL2Ahead && far.valid; ++i) {
-                ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0, far.ti.g * a.K + (far.kt / T::kParts) * kBK);
+                ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0, far.ti.g * a.K + far.kt * kBK);
                 iter_next(far, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
             }
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
                 for (int kt = 0; kt < n_kt; ++kt, ++ia) {
-                    const uint32_t s = ia % kNS, ph = (ia / kNS) & 1;
-                    if (ia >= kNS && !gm_wait(&sb->empty[s], ph ^ 1, sb, a.status, 10 + (int)s)) { ok = false; break; }
+                    const uint32_t s = ia % NS, ph = (ia / NS) & 1;
+                    if (ia >= NS && !gm_wait(&sb->empty[s], ph ^ 1, sb, a.status, 10 + (int)s)) { ok = false; break; }
                     const uint32_t bar = ptx::smem_u32(&sb->full[s]);
                     ptx::mbar_arrive_expect_tx(bar, ti.halves * kAHalfBytes);
-                    const int kx = (kt / T::kParts) * kBK;
+                    const int kx = kt * kBK;
                     ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes), &tmap_x, bar, kx, ti.row0);
                     if (ti.halves == 2)
                         ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes + kAHalfBytes), &tmap_x, bar, kx,
                                          ti.row0 + kBM);
                     if (far.valid) {
                         ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0,
-                                                far.ti.g * a.K + (far.kt / T::kParts) * kBK);
+                                                far.ti.g * a.K + far.kt * kBK);
                         iter_next(far, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
                     }
                 }
             }
             if (!ok)
-                for (uint32_t j = (ia > kNS ? ia - kNS : 0); j < ia; ++j)
-                    (void)ptx::mbar_wait(ptx::smem_u32(&sb->full[j % kNS]), (j / kNS) & 1);
+                for (uint32_t j = (ia > NS ? ia - NS : 0); j < ia; ++j)
+                    (void)ptx::mbar_wait(ptx::smem_u32(&sb->full[j % NS]), (j / NS) & 1);
         }
     } else if (warp == kWarpMma) {
         // ------------------------------ MMA issuer ------------------------------
@@ -418,20 +445,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     if (!gm_wait(&sb->full[sa], pha, sb, a.status, 40 + (int)sa)) { ok = false; break; }
                     ptx::tc_fence_after();
                     const uint64_t da = da0 + (uint64_t)(sa * (kATileBytes >> 4));
-                    const uint64_t db = db0 + (uint64_t)(sa * (kBTileBytes >> 4));
 #pragma unroll
-                    for (int k16 = 0; k16 < kBK / 16; ++k16)
-                        ptx::umma_bf16(tmem_base, da + (uint64_t)(k16 * 2), db + (uint64_t)(k16 * 128), idesc,
-                                       accumulate | (uint32_t)k16);
-                    if (ti.halves == 2) {
+                    for (int p = 0; p < P; ++p) {  // int4: the hi tile, then the lo tile, against the same x stage
+                        const uint64_t db = db0 + (uint64_t)((sa * P + p) * (kBTileBytes >> 4));
 #pragma unroll
                         for (int k16 = 0; k16 < kBK / 16; ++k16)
-                            ptx::umma_bf16(tmem_base + kBN, da + (uint64_t)((kAHalfBytes >> 4) + k16 * 2),
-                                           db + (uint64_t)(k16 * 128), idesc, accumulate | (uint32_t)k16);
+                            ptx::umma_bf16(tmem_base, da + (uint64_t)(k16 * 2), db + (uint64_t)(k16 * 128), idesc,
+                                           accumulate | (uint32_t)(k16 + p));
+                        if (ti.halves == 2) {
+#pragma unroll
+                            for (int k16 = 0; k16 < kBK / 16; ++k16)
+                                ptx::umma_bf16(tmem_base + kBN, da + (uint64_t)((kAHalfBytes >> 4) + k16 * 2),
+                                               db + (uint64_t)(k16 * 128), idesc, accumulate | (uint32_t)(k16 + p));
+                        }
                     }
                     accumulate = 1;
                     ptx::umma_commit(ptx::smem_u32(&sb->empty[sa]));
-                    if (++sa == kNS) { sa = 0; pha ^= 1; }
+                    if (++sa == NS) { sa = 0; pha ^= 1; }
                 }
                 if (ok) ptx::umma_commit(ptx::smem_u32(&sb->t_full));
             }
@@ -497,14 +527,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
     } else if (warp >= kWarpDq0) {
         // ------------------------------ dequant ------------------------------
-        // A unit of work is one k block: one stage, or for int4 the hi and lo stages it produces.
-        constexpr int P = T::kParts;
+        // A unit of work is one stage (one k block); for int4 it holds the hi and the lo tile.
         const int dq_tid = threadIdx.x - kWarpDq0 * 32;
         const int grp = dq_tid / (kDqGroupWarps * 32);
         const DqLane d = dq_lane(dq_tid % (kDqGroupWarps * 32));
         StageIter cur, pf;
         iter_start(cur, n_tiles, tile_prefix, row_start, a.G, n_nt);
-        for (int i = 0; i < grp * P && cur.valid; ++i) iter_next(cur, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
+        for (int i = 0; i < grp && cur.valid; ++i) iter_next(cur, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
         pf = cur;
         PackedRegs<MODE> regs[kPrefetch];
 #pragma unroll
@@ -512,43 +541,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             if (pf.valid) {
                 load_packed<MODE>(regs[u], weight, a, pf.ti, pf.kt, d);
 #pragma unroll
-                for (int i = 0; i < kDqGroups * P; ++i)
+                for (int i = 0; i < kDqGroups; ++i)
                     if (pf.valid) iter_next(pf, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
             }
         }
-        uint32_t ib = grp * P;
+        uint32_t ib = grp;
         bool ok = true;
         while (cur.valid && ok) {
 #pragma unroll
             for (int u = 0; u < kPrefetch; ++u) {
                 if (!cur.valid) break;
-                uint32_t slot[P];
+                const uint32_t slot = ib % NS;
+                Int4Scales sc4;
+                if constexpr (MODE == B200MOE_CT_INT4) sc4 = load_int4_scales(a, cur.ti, cur.kt, d);
                 bool got = true;
-#pragma unroll
-                for (int p = 0; p < P; ++p) {
-                    const uint32_t n = ib + p;
-                    slot[p] = n % kNS;
-                    if (got && n >= kNS) got = gm_wait(&sb->empty[slot[p]], ((n / kNS) & 1) ^ 1, sb, a.status, 80 + (int)slot[p]);
-                }
+                if (ib >= NS) got = gm_wait(&sb->empty[slot], ((ib / NS) & 1) ^ 1, sb, a.status, 80 + (int)slot);
                 if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+                uint8_t* bt = b_ring + slot * P * kBTileBytes;
                 if constexpr (MODE == B200MOE_CT_INT4)
-                    convert_block_int4(regs[u], b_ring + slot[0] * kBTileBytes, b_ring + slot[P - 1] * kBTileBytes, a, cur.ti,
-                                       cur.kt / P, d);
+                    convert_block_int4(regs[u], sc4, bt, bt + kBTileBytes, d);
                 else
-                    convert_stage<MODE>(regs[u], b_ring + slot[0] * kBTileBytes, a, cur.ti, cur.kt, d);
+                    convert_stage<MODE>(regs[u], bt, a, cur.ti, cur.kt, d);
                 ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
                 __syncwarp();
-                if (lane == 0) {
-#pragma unroll
-                    for (int p = 0; p < P; ++p) ptx::mbar_arrive(ptx::smem_u32(&sb->full[slot[p]]));
-                }
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->full[slot]));
                 if (pf.valid) load_packed<MODE>(regs[u], weight, a, pf.ti, pf.kt, d);
 #pragma unroll
-                for (int i = 0; i < kDqGroups * P; ++i) {
+                for (int i = 0; i < kDqGroups; ++i) {
                     if (pf.valid) iter_next(pf, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
                     if (cur.valid) iter_next(cur, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
                 }
-                ib += kDqGroups * P;
+                ib += kDqGroups;
             }
         }
     }
