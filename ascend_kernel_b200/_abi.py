@@ -24,7 +24,22 @@ EXPORTS = [
     "b200moe_grouped_gemv_workspace_bytes", "b200moe_fp4_dequant", "b200moe_fp4_layout", "b200moe_silu_mul",
     "b200moe_gather_rows", "b200moe_combine", "b200moe_read_status", "b200moe_strerror", "b200moe_version",
     "b200moe_moe_route", "b200moe_moe_regroup_index", "b200moe_grouped_gemm_int8_noalloc", "b200moe_grouped_gemm_int8_noalloc_max_rows", "b200moe_noalloc_read_status",
+    "b200moe_ep_post_counts", "b200moe_ep_dispatch", "b200moe_ep_wait", "b200moe_ep_post", "b200moe_ep_combine",
+    "b200moe_silu_mul_dyn", "b200moe_ipc_alloc", "b200moe_ipc_open", "b200moe_ipc_close", "b200moe_ipc_free",
 ]
+
+EP_MAX_WORLD = 8
+IPC_HANDLE_BYTES = 64
+EP_SIG_COUNTS, EP_SIG_ROWS, EP_SIG_RESULTS = 0, 1, 2
+
+
+class EpComm(ctypes.Structure):
+    """``b200moe_ep_comm`` of include/b200moe.h."""
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("n_experts", ctypes.c_int32),
+                ("reserved", ctypes.c_int32), ("cap_rows", ctypes.c_int64), ("hidden", ctypes.c_int64),
+                ("peer_recv_x", ctypes.c_void_p * EP_MAX_WORLD), ("peer_y", ctypes.c_void_p * EP_MAX_WORLD),
+                ("peer_counts", ctypes.c_void_p * EP_MAX_WORLD), ("peer_signal", ctypes.c_void_p * EP_MAX_WORLD),
+                ("status", ctypes.c_void_p)]
 
 
 class B200MoeError(RuntimeError):
@@ -68,6 +83,21 @@ def _load() -> ctypes.CDLL:
     lib.b200moe_moe_route.restype = i32
     lib.b200moe_moe_regroup_index.argtypes = [vp, i64, i64, vp, vp, vp, vp]
     lib.b200moe_moe_regroup_index.restype = i32
+    u64, comm = ctypes.c_uint64, ctypes.POINTER(EpComm)
+    lib.b200moe_ep_post_counts.argtypes = [comm, vp, u64, vp]
+    lib.b200moe_ep_dispatch.argtypes = [comm, vp, vp, i64, u64, vp, vp, vp, vp, vp]
+    lib.b200moe_ep_wait.argtypes = [comm, i32, u64, vp]
+    lib.b200moe_ep_post.argtypes = [comm, i32, u64, vp]
+    lib.b200moe_ep_combine.argtypes = [comm, vp, vp, vp, vp, i64, i64, u64, vp]
+    lib.b200moe_silu_mul_dyn.argtypes = [vp, vp, vp, i64, vp]
+    lib.b200moe_ipc_alloc.argtypes = [sz, ctypes.POINTER(vp), ctypes.c_char_p]
+    lib.b200moe_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+    lib.b200moe_ipc_close.argtypes = [vp]
+    lib.b200moe_ipc_free.argtypes = [vp]
+    for f in (lib.b200moe_ep_post_counts, lib.b200moe_ep_dispatch, lib.b200moe_ep_wait, lib.b200moe_ep_post,
+              lib.b200moe_ep_combine, lib.b200moe_silu_mul_dyn, lib.b200moe_ipc_alloc, lib.b200moe_ipc_open,
+              lib.b200moe_ipc_close, lib.b200moe_ipc_free):
+        f.restype = i32
     lib.b200moe_read_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
     lib.b200moe_read_status.restype = i32
     lib.b200moe_strerror.argtypes = [i32]

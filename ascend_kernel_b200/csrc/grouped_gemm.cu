@@ -171,6 +171,7 @@ template <int MODE>
 struct PackedRegs {
     uint4 q[kDqRows];  // fp4 / int4 use only .x/.y of each
     uint4 s[2];        // fp4 only: the bf16 scales of the thread's 16 columns (one 16-row group)
+    float sf;          // fp8 only: the fp32 scale of the thread's 128 x 128 block
 };
 
 template <int MODE>
@@ -191,6 +192,10 @@ __device__ __forceinline__ void load_packed(PackedRegs<MODE>& r, const uint8_t* 
             r.q[j] = __ldg(reinterpret_cast<const uint4*>(p));
         }
     }
+    if constexpr (MODE == B200MOE_CT_FP8) {
+        r.sf = __ldg(static_cast<const float*>(a.scale) +
+                     ((size_t)ti.g * (a.K >> 7) + ((kb * kBK) >> 7)) * (a.N >> 7) + ((ti.n0 + d.c16 * 16) >> 7));
+    }
     if constexpr (MODE == B200MOE_CT_FP4) {
         const uint4* sp = reinterpret_cast<const uint4*>(
             static_cast<const __nv_bfloat16*>(a.scale) +
@@ -204,11 +209,7 @@ template <int MODE>
 __device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint8_t* bt, const GemmArgs& a,
                                               const TileInfo& ti, int kt, const DqLane& d) {
     const int c16 = d.c16;
-    float sf = 1.f;
-    if constexpr (MODE == B200MOE_CT_FP8) {
-        sf = __ldg(static_cast<const float*>(a.scale) +
-                   ((size_t)ti.g * (a.K >> 7) + ((kt * kBK) >> 7)) * (a.N >> 7) + ((ti.n0 + c16 * 16) >> 7));
-    }
+    const float sf = (MODE == B200MOE_CT_FP8) ? r.sf : 1.f;
     const f32x2 sf2 = pack_f32x2(sf, sf);
 #pragma unroll
     for (int j = 0; j < kDqRows; ++j) {
@@ -584,10 +585,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     }
 }
 
-// Row sums of x in fp32 (the offset term of the int8 epilogue): one warp per row.
-__global__ void rowsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int M, int K) {
+// Row sums of x in fp32 (the offset term of the int8 epilogue): one warp per row.  Rows past the
+// last group are skipped (a caller may pass a buffer sized for the worst case as x).
+__global__ void rowsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int M, int K,
+                              const long long* __restrict__ group_list, int G, int gl_type) {
+    __shared__ long long s_used;
+    if (threadIdx.x == 0) s_used = 0;
+    __syncthreads();
+    long long v = 0;
+    for (int g = threadIdx.x; g < G; g += blockDim.x) {
+        const long long c = group_list[g];
+        if (gl_type == B200MOE_GROUP_LIST_COUNTS) v += c > 0 ? c : 0; else v = c > v ? c : v;
+    }
+    if (gl_type == B200MOE_GROUP_LIST_COUNTS) {
+        if (v) atomicAdd(reinterpret_cast<unsigned long long*>(&s_used), (unsigned long long)v);
+    } else {
+        if (v) atomicMax(&s_used, v);
+    }
+    __syncthreads();
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= M) return;
+    if (row >= M || row >= s_used) return;
     const uint4* p = reinterpret_cast<const uint4*>(x + (size_t)row * K);
     float s = 0.f;
     for (int i = threadIdx.x & 31; i < K / 8; i += 32) {
@@ -687,7 +704,8 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
         ws += align256((size_t)M * sizeof(float));
         if (offset != nullptr) {
             rowsum_kernel<<<(unsigned)((M + 7) / 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rowsum, (int)M,
-                                                                   (int)K);
+                                                                   (int)K, reinterpret_cast<const long long*>(group_list),
+                                                                   (int)G, group_list_type);
             B200MOE_CUDA_TRY(cudaGetLastError());
             a.offset = static_cast<const __nv_bfloat16*>(offset);
             a.rowsum = rowsum;
@@ -784,7 +802,9 @@ extern "C" int b200moe_grouped_gemm_int8_noalloc(const void* x, const void* weig
     a.status = static_cast<int*>(scratch);
     if (offset != nullptr) {
         float* rowsum = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + B200MOE_STATUS_BYTES);
-        rowsum_kernel<<<(unsigned)((M + 7) / 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rowsum, (int)M, (int)K);
+        rowsum_kernel<<<(unsigned)((M + 7) / 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rowsum, (int)M, (int)K,
+                                                              reinterpret_cast<const long long*>(group_list), (int)G,
+                                                              group_list_type);
         B200MOE_CUDA_TRY(cudaGetLastError());
         a.offset = static_cast<const __nv_bfloat16*>(offset);
         a.rowsum = rowsum;

@@ -1,0 +1,158 @@
+"""Expert-parallel token exchange over NVLink peer memory (host side).
+
+``PeerExchange`` owns this rank's four exchange buffers (allocated by the C library so that the
+other processes of the node can map them through CUDA IPC), maps every peer's buffers, and wraps
+the exchange kernels of ``include/b200moe.h`` (``b200moe_ep_*``).  torch.distributed is used once,
+at construction, to pass the 64-byte IPC handles around; a layer step itself makes no collective
+call and never synchronises with the host.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _abi, ops
+
+_lib = _abi.lib
+
+
+class _DeviceBuffer:
+    """A raw device allocation exposed to torch through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+def _as_tensor(ptr: int, shape, dtype, device):
+    """Zero-copy torch view of ``ptr`` (bf16 goes through int16: the interface has no bf16 code)."""
+    if dtype == torch.bfloat16:
+        return torch.as_tensor(_DeviceBuffer(ptr, shape, "<i2"), device=device).view(torch.bfloat16)
+    code = {torch.int32: "<i4", torch.int64: "<i8", torch.uint8: "|u1"}[dtype]
+    return torch.as_tensor(_DeviceBuffer(ptr, shape, code), device=device)
+
+
+class PeerExchange:
+    def __init__(self, group, n_experts: int, hidden: int, cap_rows: int, device):
+        """``group``: the expert-parallel process group (all ranks on one node) or None for a single
+        rank.  ``cap_rows``: rows this rank's receive / result buffers hold; the worst case is
+        (tokens of all ranks) x top_k."""
+        self.device = torch.device(device)
+        self.n_experts, self.hidden, self.cap_rows = n_experts, hidden, cap_rows
+        if group is not None:
+            import torch.distributed as dist
+
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        else:
+            self.world, self.rank = 1, 0
+        if self.world > _abi.EP_MAX_WORLD:
+            raise RuntimeError(f"at most {_abi.EP_MAX_WORLD} ranks")
+        self.step = 0
+        sizes = {"recv_x": cap_rows * hidden * 2, "y": cap_rows * hidden * 2,
+                 "counts": self.world * n_experts * 4, "signal": 3 * _abi.EP_MAX_WORLD * 8}
+        self._own, handles = {}, {}
+        with torch.cuda.device(self.device):
+            for name, nbytes in sizes.items():
+                p = ctypes.c_void_p()
+                h = ctypes.create_string_buffer(_abi.IPC_HANDLE_BYTES)
+                _abi.check(_lib.b200moe_ipc_alloc(nbytes, ctypes.byref(p), h), f"ipc_alloc({name})")
+                self._own[name], handles[name] = p.value, bytes(h.raw)
+        # every rank's handles -> pointers valid in this process
+        self._peer = {name: [None] * self.world for name in sizes}
+        self._opened = []
+        if self.world > 1:
+            import torch.distributed as dist
+
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, handles, group=group)
+            with torch.cuda.device(self.device):
+                for r, hs in enumerate(everyone):
+                    for name in sizes:
+                        if r == self.rank:
+                            self._peer[name][r] = self._own[name]
+                            continue
+                        p = ctypes.c_void_p()
+                        _abi.check(_lib.b200moe_ipc_open(hs[name], ctypes.byref(p)), f"ipc_open({name}, rank {r})")
+                        self._peer[name][r] = p.value
+                        self._opened.append(p.value)
+            dist.barrier(group=group)  # nobody starts a step before every mapping exists
+        else:
+            for name in sizes:
+                self._peer[name][0] = self._own[name]
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._done = torch.zeros(1, dtype=torch.int32, device=self.device)
+        c = _abi.EpComm()
+        c.world, c.rank, c.n_experts, c.cap_rows, c.hidden = self.world, self.rank, n_experts, cap_rows, hidden
+        for r in range(self.world):
+            c.peer_recv_x[r], c.peer_y[r] = self._peer["recv_x"][r], self._peer["y"][r]
+            c.peer_counts[r], c.peer_signal[r] = self._peer["counts"][r], self._peer["signal"][r]
+        c.status = self.status.data_ptr()
+        self._comm = c
+        # torch views of the two local row buffers (inputs / outputs of the grouped GEMMs)
+        self.recv_x = _as_tensor(self._own["recv_x"], (cap_rows, hidden), torch.bfloat16, self.device)
+        self.y = _as_tensor(self._own["y"], (cap_rows, hidden), torch.bfloat16, self.device)
+
+    # ---- one step ---------------------------------------------------------------------------
+    def _s(self):
+        return torch.cuda.current_stream().cuda_stream
+
+    def begin_step(self) -> int:
+        self.step += 1
+        return self.step
+
+    def post_counts(self, counts):
+        with torch.cuda.device(self.device):
+            _abi.check(_lib.b200moe_ep_post_counts(ctypes.byref(self._comm), counts.data_ptr(), self.step, self._s()),
+                       "ep_post_counts")
+        ops._count(1)
+
+    def dispatch(self, x, token_of):
+        """-> (remote_pos int32 [rows], local_counts int64 [E/world], n_recv int64 [1])"""
+        n_rows = token_of.numel()
+        remote_pos = torch.empty(n_rows, dtype=torch.int32, device=self.device)
+        local_counts = torch.empty(self.n_experts // self.world, dtype=torch.int64, device=self.device)
+        n_recv = torch.empty(1, dtype=torch.int64, device=self.device)
+        with torch.cuda.device(self.device):
+            _abi.check(_lib.b200moe_ep_dispatch(ctypes.byref(self._comm), x.data_ptr(), token_of.data_ptr(), n_rows,
+                                                self.step, remote_pos.data_ptr(), local_counts.data_ptr(),
+                                                n_recv.data_ptr(), self._done.data_ptr(), self._s()), "ep_dispatch")
+        ops._count(1)
+        return remote_pos, local_counts, n_recv
+
+    def wait(self, which: int):
+        with torch.cuda.device(self.device):
+            _abi.check(_lib.b200moe_ep_wait(ctypes.byref(self._comm), which, self.step, self._s()), "ep_wait")
+        ops._count(1)
+
+    def post(self, which: int):
+        with torch.cuda.device(self.device):
+            _abi.check(_lib.b200moe_ep_post(ctypes.byref(self._comm), which, self.step, self._s()), "ep_post")
+        ops._count(1)
+
+    def combine(self, remote_pos, slot, weight, out=None):
+        T, top_k = slot.shape
+        if out is None:
+            out = torch.empty(T, self.hidden, dtype=torch.bfloat16, device=self.device)
+        with torch.cuda.device(self.device):
+            _abi.check(_lib.b200moe_ep_combine(ctypes.byref(self._comm), remote_pos.data_ptr(), slot.data_ptr(),
+                                               weight.data_ptr(), out.data_ptr(), T, top_k, self.step, self._s()),
+                       "ep_combine")
+        ops._count(1)
+        return out
+
+    def read_status(self):
+        """(0, _) = fine; (1, expert) = a receive buffer overflowed; (2, where) = a wait expired."""
+        s = self.status.cpu()
+        return int(s[0]), int(s[1])
+
+    def close(self):
+        """Unmaps the peers' buffers and frees this rank's.  All ranks must have finished their last
+        step (synchronise and barrier first)."""
+        with torch.cuda.device(self.device):
+            for p in self._opened:
+                _lib.b200moe_ipc_close(p)
+            self._opened = []
+            self.recv_x = self.y = None
+            for name, p in list(self._own.items()):
+                _lib.b200moe_ipc_free(p)
+            self._own = {}

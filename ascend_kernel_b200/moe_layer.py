@@ -14,8 +14,13 @@ e // (E / world)).  Per step:
   inverse regroup, all-to-all back                   world > 1 only
   weighted sum over each token's k results           b200moe_combine
 
-Data from peers always lands in this GPU's own memory (the NCCL receive buffer) before a kernel
-reads it.  torch is used for device memory, streams and the process group; routing, permutation
+With ``exchange="p2p"`` the two all-to-alls, the count exchange, the host read of the split sizes
+and the regroup passes are replaced by this package's exchange kernels (ep_exchange.py): rows are
+stored straight into the owner's receive buffer over NVLink, already expert-major, and the combine
+kernel loads result rows from the owners' buffers.  A step then has no host synchronisation.
+
+With the NCCL exchange, data from peers lands in this GPU's own memory (the NCCL receive buffer)
+before a kernel reads it.  torch is used for device memory, streams and the process group; routing, permutation
 and every row-sized operation are this package's CUDA kernels.
 """
 from __future__ import annotations
@@ -38,11 +43,15 @@ class CudaRowOps:
 
 
 class MoELayer:
-    def __init__(self, w13, s13, o13, w2, s2, o2, n_experts: int, top_k: int, group=None, row_ops=CudaRowOps):
+    def __init__(self, w13, s13, o13, w2, s2, o2, n_experts: int, top_k: int, group=None, row_ops=CudaRowOps,
+                 exchange: str = "nccl", max_tokens: int = 0):
         """w13 int8 [E_local, H, 2I] (gate columns first), w2 int8 [E_local, I, H]; per-channel bf16
         scales/offsets [E_local, N].  ``group``: a torch.distributed process group or None.
         ``row_ops`` exists so the dispatch / regroup / combine index logic can be exercised by CPU
-        ranks in the test-suite with stand-in row operations; the product always uses CudaRowOps."""
+        ranks in the test-suite with stand-in row operations; the product always uses CudaRowOps.
+        ``exchange``: "nccl" (all-to-all collectives) or "p2p" (this package's peer-memory kernels;
+        needs ``max_tokens`` = the largest number of tokens a rank passes to forward, which sizes the
+        receive buffers for the worst case max_tokens x world x top_k rows)."""
         self.ops = row_ops
         self.w13, self.s13, self.o13, self.w2, self.s2, self.o2 = w13, s13, o13, w2, s2, o2
         self.n_experts, self.top_k = n_experts, top_k
@@ -57,14 +66,25 @@ class MoELayer:
         assert self.e_local * self.world == n_experts
         self.hidden, self.inter = w13.shape[1], w2.shape[1]
         self.device = w13.device
+        self.px = None
+        if exchange == "p2p":
+            from .ep_exchange import PeerExchange
+
+            if max_tokens <= 0:
+                raise ValueError('exchange="p2p" needs max_tokens')
+            self.px = PeerExchange(group, n_experts, self.hidden, max_tokens * self.world * top_k, self.device)
+        elif exchange != "nccl":
+            raise ValueError("exchange must be 'nccl' or 'p2p'")
         self.timing = None  # [ev0..ev3] around GEMM1 / SiLU / GEMM2, filled by forward(record=True)
         self.phases = None  # [(name, event)] phase boundaries of the last forward(record=True)
 
-    def _experts(self, rows, counts, record):
-        """rows [R, H] expert-major with per-local-expert counts -> [R, H]."""
+    def _experts(self, rows, counts, record, y=None, n_rows=None):
+        """rows [R, H] expert-major with per-local-expert counts -> [R, H] (into ``y`` when given).
+        ``n_rows``: int64 device tensor with the number of rows in use when R is only a capacity."""
         R = rows.shape[0]
         h = torch.empty(R, 2 * self.inter, dtype=torch.bfloat16, device=self.device)
-        y = torch.empty(R, self.hidden, dtype=torch.bfloat16, device=self.device)
+        if y is None:
+            y = torch.empty(R, self.hidden, dtype=torch.bfloat16, device=self.device)
         if R == 0:
             return y
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if record else None
@@ -74,7 +94,7 @@ class MoELayer:
         self.ops.grouped_gemm(rows, self.w13, self.s13, self.o13, counts, "int8", h, group_list_type=1)
         if ev:
             ev[1].record()
-        act = self.ops.silu_mul(h)
+        act = self.ops.silu_mul(h) if n_rows is None else ops.silu_mul_dyn(h, n_rows)
         if ev:
             ev[2].record()
         self.ops.grouped_gemm(act, self.w2, self.s2, self.o2, counts, "int8", y, group_list_type=1)
@@ -102,6 +122,23 @@ class MoELayer:
 
         mark("start")
         idx, wts, counts, token_of, slot = self.ops.route(logits, self.top_k)
+        if self.px is not None:
+            px = self.px
+            if x.shape[0] * self.world * self.top_k > px.cap_rows:
+                raise RuntimeError("more tokens than max_tokens")
+            px.begin_step()
+            px.post_counts(counts)
+            mark("route")
+            remote_pos, local_counts, n_recv = px.dispatch(x, token_of)
+            px.wait(1)                                            # rows of every source rank have landed
+            mark("dispatch")
+            self._experts(px.recv_x, local_counts, record, y=px.y, n_rows=n_recv)
+            px.post(2)                                            # results of this rank are complete
+            mark("experts")
+            out = px.combine(remote_pos, slot, wts, out=out_host)  # a pinned host tensor is written directly
+            mark("combine")
+            self.phases = marks
+            return out
         send = self.ops.gather_rows(x, token_of)                 # [T*k, H] sorted by expert
         mark("route+gather")
 

@@ -210,6 +210,21 @@ def moe_route(logits, top_k: int):
     return idx, w, counts, token_of, slot
 
 
+def silu_mul_dyn(h, n_rows, out=None):
+    """silu_mul over the first ``n_rows[0]`` rows of h (``n_rows``: int64 device tensor)."""
+    _need_cuda(h=h, n_rows=n_rows, out=out)
+    if h.dtype != torch.bfloat16 or n_rows.dtype != torch.int64:
+        raise RuntimeError("h must be bfloat16 and n_rows int64")
+    R, two_i = h.shape
+    if out is None:
+        out = torch.empty(R, two_i // 2, dtype=torch.bfloat16, device=h.device)
+    with torch.cuda.device(h.device):
+        rc = _lib.b200moe_silu_mul_dyn(_ptr(h), _ptr(out), _ptr(n_rows), two_i // 2, _stream())
+    _abi.check(rc, "silu_mul_dyn")
+    _count(1)
+    return out
+
+
 def moe_regroup_index(recv_counts, n_recv: int):
     """recv_counts int64 [world, e_local] (rows per source rank and local expert, arrival order) ->
     (pos int32 [n_recv], inv int32 [n_recv], local_counts int64 [e_local])."""

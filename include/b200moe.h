@@ -152,6 +152,63 @@ int b200moe_moe_route(const void* logits, int64_t n_tokens, int64_t n_experts, i
 int b200moe_moe_regroup_index(const int64_t* recv_counts, int64_t world, int64_t e_local, int32_t* pos, int32_t* inv,
                               int64_t* local_counts, void* stream);
 
+/* ---- expert-parallel token exchange over NVLink peer memory ----------------------------------
+ * (No reference counterpart: the reference ships the two operators only; chitu exchanges tokens
+ * with its own collectives.  These entry points are the exchange steps of the benchmark's MoE layer
+ * written as kernels that store token rows into, and load result rows from, the memory of the rank
+ * that owns the expert -- no collective library call, staging copy or host synchronisation inside a
+ * step.)  Every rank of one node owns four buffers that all ranks can address (b200moe_ipc_*):
+ *   recv_x  bf16 [cap_rows, hidden]   rows routed to this rank's experts, expert-major
+ *   y       bf16 [cap_rows, hidden]   the rows its experts produced, same positions
+ *   counts  int32 [world, n_experts]  rows per (source rank, expert)
+ *   signal  uint64 [3, B200MOE_EP_MAX_WORLD]  step numbers: counts / rows / results, one per source
+ * `step` is a number that grows by one per layer pass, starting at 1 (the buffers start zeroed).
+ * Waits inside the kernels are bounded (2 s): on expiry status word 0 of `status` becomes 2 and the
+ * kernels carry on without faulting.  world <= B200MOE_EP_MAX_WORLD, n_experts % world == 0,
+ * n_experts <= 1024, cap_rows * world < 2^31. */
+#define B200MOE_EP_MAX_WORLD 8
+#define B200MOE_IPC_HANDLE_BYTES 64
+typedef struct b200moe_ep_comm {
+    int32_t world, rank, n_experts, reserved;
+    int64_t cap_rows, hidden;
+    void* peer_recv_x[B200MOE_EP_MAX_WORLD];
+    void* peer_y[B200MOE_EP_MAX_WORLD];
+    int32_t* peer_counts[B200MOE_EP_MAX_WORLD];
+    uint64_t* peer_signal[B200MOE_EP_MAX_WORLD];
+    int32_t* status; /* local device memory, >= 2 words, zeroed by the caller */
+} b200moe_ep_comm;
+enum { B200MOE_EP_SIG_COUNTS = 0, B200MOE_EP_SIG_ROWS = 1, B200MOE_EP_SIG_RESULTS = 2 };
+
+/* counts int64 [n_experts] (this rank's rows per expert, as b200moe_moe_route returns them) ->
+ * row `rank` of every rank's count table, then the counts signal. */
+int b200moe_ep_post_counts(const b200moe_ep_comm* comm, const int64_t* counts, uint64_t step, void* stream);
+/* Waits for every rank's counts, then stores row x[token_of[i], :] of each of this rank's n_rows
+ * sorted rows into the owner's recv_x and signals every rank.  Outputs (local): remote_pos int32
+ * [n_rows] = owner * cap_rows + position (-1 if the owner's buffer is full), local_counts int64
+ * [n_experts / world] = rows per own expert (a counts group_list), n_recv int64 [1] = their sum.
+ * done_counter: int32 [1], zero before the first call. */
+int b200moe_ep_dispatch(const b200moe_ep_comm* comm, const void* x, const int32_t* token_of, int64_t n_rows,
+                        uint64_t step, int32_t* remote_pos, int64_t* local_counts, int64_t* n_recv,
+                        int32_t* done_counter, void* stream);
+/* One small kernel that waits until every rank has signalled `which` for `step`. */
+int b200moe_ep_wait(const b200moe_ep_comm* comm, int which, uint64_t step, void* stream);
+/* Signals `which` for `step` to every rank (everything this stream wrote before is visible first). */
+int b200moe_ep_post(const b200moe_ep_comm* comm, int which, uint64_t step, void* stream);
+/* Waits for every rank's results signal, then out[t, :] = bf16(sum_j weight[t, j] * y_owner[pos, :])
+ * with (owner, pos) = remote_pos[slot[t, j]]. */
+int b200moe_ep_combine(const b200moe_ep_comm* comm, const int32_t* remote_pos, const int32_t* slot,
+                       const float* weight, void* out, int64_t n_tokens, int64_t top_k, uint64_t step, void* stream);
+/* b200moe_silu_mul over the first *n_rows rows, the count read on the device. */
+int b200moe_silu_mul_dyn(const void* h, void* out, const int64_t* n_rows, int64_t inter, void* stream);
+
+/* Device buffers that other processes of the node can map.  alloc: cudaMalloc + zero fill + IPC
+ * handle; open / close: map / unmap another process's buffer (peer access is enabled on demand);
+ * free: release an own buffer.  These four are the only entry points that allocate. */
+int b200moe_ipc_alloc(size_t bytes, void** ptr, unsigned char handle[B200MOE_IPC_HANDLE_BYTES]);
+int b200moe_ipc_open(const unsigned char handle[B200MOE_IPC_HANDLE_BYTES], void** ptr);
+int b200moe_ipc_close(void* ptr);
+int b200moe_ipc_free(void* ptr);
+
 /* Copies the two device status words of a workspace to the host (synchronises the stream). */
 int b200moe_read_status(const void* workspace, int32_t out[2], void* stream);
 

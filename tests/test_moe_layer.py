@@ -98,7 +98,14 @@ def _free_port():
     return p
 
 
-def _rank_main(rank, world, port, q, cuda=False, case_kw=None):
+def _step_inputs(c, step):
+    """Inputs of step `step`: the case's tokens, rows reversed on odd steps."""
+    if step % 2 == 0:
+        return c["x"], c["logits"]
+    return torch.flip(c["x"], [0]).contiguous(), torch.flip(c["logits"], [0]).contiguous()
+
+
+def _rank_main(rank, world, port, q, cuda=False, case_kw=None, exchange="nccl", steps=1):
     import torch.distributed as dist
 
     from ascend_kernel_b200.moe_layer import CudaRowOps, MoELayer
@@ -117,11 +124,20 @@ def _rank_main(rank, world, port, q, cuda=False, case_kw=None):
         el, tl = c["E"] // world, c["x"].shape[0] // world
         sl = slice(rank * el, (rank + 1) * el)
         w = [c[k][sl].contiguous().to(dev) for k in ("w13", "s13", "o13", "w2", "s2", "o2")]
-        layer = MoELayer(*w, c["E"], c["top_k"], dist.group.WORLD, CudaRowOps if cuda else TorchRowOps)
-        out = layer.forward(c["x"][rank * tl:(rank + 1) * tl].to(dev), c["logits"][rank * tl:(rank + 1) * tl].to(dev))
+        layer = MoELayer(*w, c["E"], c["top_k"], dist.group.WORLD, CudaRowOps if cuda else TorchRowOps,
+                         exchange=exchange, max_tokens=tl)
+        outs = []
+        for step in range(steps):
+            x, lg = _step_inputs(c, step)
+            out = layer.forward(x[rank * tl:(rank + 1) * tl].to(dev), lg[rank * tl:(rank + 1) * tl].to(dev))
+            outs.append(out.cpu().view(torch.int16).numpy())
         if cuda:
             torch.cuda.synchronize()
-        q.put((rank, out.cpu().view(torch.int16).numpy()))
+        status = layer.px.read_status() if layer.px is not None else (0, 0)
+        dist.barrier()  # peers may still be reading this rank's result buffer until they are done too
+        if layer.px is not None:
+            layer.px.close()
+        q.put((rank, (outs if steps > 1 else outs[0], status) if exchange == "p2p" else outs[0]))
     finally:
         dist.destroy_process_group()
 
@@ -229,6 +245,62 @@ def test_two_gpu_ranks_match_oracle():
     gold = O.moe_layer(c["x"], c["logits"], c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], c["top_k"])
     out = torch.cat([torch.from_numpy(got[r]).view(torch.bfloat16) for r in range(2)])
     close(out, gold)
+
+
+@pytest.mark.gpu
+def test_peer_memory_exchange_single_rank_matches_direct_path():
+    """exchange="p2p" with one rank (the rank is its own peer): every exchange kernel runs, and
+    three steps in a row give the bits of the direct path."""
+    from ascend_kernel_b200.moe_layer import MoELayer
+
+    c = small_case(T=200, H=256, E=8, I=256, k=2)
+    d = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
+    w = [d[k] for k in ("w13", "s13", "o13", "w2", "s2", "o2")]
+    direct = MoELayer(*w, c["E"], c["top_k"])
+    p2p = MoELayer(*w, c["E"], c["top_k"], exchange="p2p", max_tokens=256)
+    for step in range(3):
+        x, lg = _step_inputs(c, step)
+        n = 200 - 40 * step  # fewer tokens each step: stale rows of earlier steps must not leak in
+        a = direct.forward(x[:n].cuda(), lg[:n].cuda())
+        b = p2p.forward(x[:n].cuda(), lg[:n].cuda())
+        torch.cuda.synchronize()
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16)), step
+    assert p2p.px.read_status()[0] == 0
+    host = torch.empty(120, 256, dtype=torch.bfloat16).pin_memory()
+    p2p.forward(c["x"][:120].cuda(), c["logits"][:120].cuda(), out_host=host)
+    torch.cuda.synchronize()
+    want = direct.forward(c["x"][:120].cuda(), c["logits"][:120].cuda())
+    assert torch.equal(host.view(torch.int16), want.cpu().view(torch.int16))
+    p2p.px.close()
+
+
+@pytest.mark.gpu
+def test_two_gpu_ranks_peer_memory_exchange_matches_oracle():
+    """The peer-memory exchange on two GPUs, three steps with changing inputs (skipped on a
+    single-GPU box: kernels that wait for each other never share one GPU)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    kw = dict(T=200, H=256, E=8, I=256, k=2)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q, True, kw, "p2p", 3)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    c = small_case(**kw)
+    for r in range(2):
+        assert got[r][1][0] == 0, got[r][1]
+    for step in range(3):
+        x, lg = _step_inputs(c, step)
+        gold = O.moe_layer(x, lg, c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], c["top_k"])
+        out = torch.cat([torch.from_numpy(got[r][0][step]).view(torch.bfloat16) for r in range(2)])
+        close(out, gold)
 
 
 @pytest.mark.gpu
