@@ -327,7 +327,9 @@ def run_ours(args):
     assert E % world == 0 and T % world == 0
     e_local, t_local = E // world, T // world
     c = inputs.config4(dev, expert_lo=rank * e_local, expert_hi=(rank + 1) * e_local, **CFG)
-    layer = MoELayer(c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], E, CFG["top_k"], group)
+    exchange = args.exchange if world > 1 else "direct"
+    layer = MoELayer(c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], E, CFG["top_k"], group,
+                     exchange="p2p" if exchange == "p2p" else "nccl", max_tokens=t_local)
     x_host = c["x"][rank * t_local:(rank + 1) * t_local].contiguous().pin_memory()
     lg_host = c["logits"][rank * t_local:(rank + 1) * t_local].contiguous().pin_memory()
     x, lg = x_host.to(dev), lg_host.to(dev)
@@ -408,6 +410,7 @@ def run_ours(args):
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    exchange_status = list(layer.px.read_status()) if layer.px is not None else None
     h2d = (x_host.numel() * 2 + lg_host.numel() * 2) * world
     d2h = out_host.numel() * 2 * world
 
@@ -425,7 +428,7 @@ def run_ours(args):
         "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16 x int8 -> fp32 accumulate", "data": "synthetic",
-        "config": workload_config(world),
+        "config": {**workload_config(world), "exchange": exchange, "exchange_status": exchange_status},
         "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps_in_flight": 2, "single_step_latency_ms": latency_ms},
         "gpu_launches": launches * args.steps, "gpu_launches_per_step": launches,
@@ -446,6 +449,8 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist
 
+        torch.cuda.synchronize()
+        dist.barrier(group=group)  # peers may read this rank's exchange buffers until they are done too
         dist.destroy_process_group()
 
 
@@ -457,6 +462,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="moe", choices=["moe", "gemm", "gemv", "dequant"],
                     help="moe: the benchmark line; others: one kernel alone (for profiling)")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="token exchange between ranks (N > 1): this package's peer-memory kernels or NCCL all-to-all")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel lines (N=1)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--quick", action="store_true", help="small shapes for the per-kernel lines (profiling)")
