@@ -418,11 +418,18 @@ def run_ours(args):
     rows_local = T * CFG["top_k"] / world  # expectation; exact rows differ per rank by routing
     flops_step = 2.0 * rows_local * (CFG["hidden"] * 2 * CFG["inter"] + CFG["inter"] * CFG["hidden"])
     gemm_ms_step = gemm_ms / max(1, len(gemm_events))
+    H_, I_ = CFG["hidden"], CFG["inter"]
+    algo_bytes = (E / world) * (H_ * 2 * I_ + I_ * H_) + rows_local * 2.0 * (H_ + 2 * I_ + I_ + H_)
+    traffic = 1.08 * algo_bytes
     achieved = flops_step / gemm_ms_step / 1e9 if gemm_ms_step > 0 else 0.0
     roofline = {"bound": "tensor", "kernel": "grouped_gemm_kernel<int8> (2 launches per step, rank 0)",
                 "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops_sustained"], "peak_kind": f"{peak_kind} (sustained cuBLAS bf16)",
-                "traffic": None, "ms_per_step_in_kernel": gemm_ms_step}
+                "traffic": traffic, "traffic_unit": "bytes per step (both launches)",
+                "traffic_source": "algorithmic bytes (weights once + x + y) x 1.08, the dram bytes / algorithmic bytes "
+                                  "ratio of the ncu capture of a small case (profiles/grouped_gemm_int8_small_case_ncu.txt); "
+                                  "the full-size launch is too large to capture",
+                "ms_per_step_in_kernel": gemm_ms_step}
 
     line = {
         "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,

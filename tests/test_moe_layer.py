@@ -275,6 +275,34 @@ def test_peer_memory_exchange_single_rank_matches_direct_path():
 
 
 @pytest.mark.gpu
+def test_peer_memory_wait_expires_with_status_instead_of_hanging():
+    """A wait for a signal nobody posts gives up after its time limit, records status 2 and leaves
+    the context usable: the next complete step is still right."""
+    import time
+
+    from ascend_kernel_b200 import _abi
+    from ascend_kernel_b200.moe_layer import MoELayer
+
+    c = small_case(T=64, H=256, E=8, I=256, k=2)
+    d = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
+    w = [d[k] for k in ("w13", "s13", "o13", "w2", "s2", "o2")]
+    p2p = MoELayer(*w, c["E"], c["top_k"], exchange="p2p", max_tokens=64)
+    p2p.px.begin_step()
+    t0 = time.time()
+    p2p.px.wait(_abi.EP_SIG_ROWS)  # no dispatch ran in this step: the rows signal never comes
+    torch.cuda.synchronize()
+    assert 1.0 < time.time() - t0 < 10.0
+    assert p2p.px.read_status()[0] == 2
+    p2p.px.status.zero_()
+    out = p2p.forward(d["x"], d["logits"])
+    want = MoELayer(*w, c["E"], c["top_k"]).forward(d["x"], d["logits"])
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    assert p2p.px.read_status()[0] == 0
+    p2p.px.close()
+
+
+@pytest.mark.gpu
 def test_two_gpu_ranks_peer_memory_exchange_matches_oracle():
     """The peer-memory exchange on two GPUs, three steps with changing inputs (skipped on a
     single-GPU box: kernels that wait for each other never share one GPU)."""
