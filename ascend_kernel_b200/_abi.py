@@ -39,7 +39,7 @@ class EpComm(ctypes.Structure):
                 ("reserved", ctypes.c_int32), ("cap_rows", ctypes.c_int64), ("hidden", ctypes.c_int64),
                 ("peer_recv_x", ctypes.c_void_p * EP_MAX_WORLD), ("peer_y", ctypes.c_void_p * EP_MAX_WORLD),
                 ("peer_counts", ctypes.c_void_p * EP_MAX_WORLD), ("peer_signal", ctypes.c_void_p * EP_MAX_WORLD),
-                ("status", ctypes.c_void_p)]
+                ("status", ctypes.c_void_p), ("step_counter", ctypes.c_void_p)]
 
 
 class B200MoeError(RuntimeError):

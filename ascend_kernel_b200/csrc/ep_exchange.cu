@@ -42,6 +42,7 @@ struct EpComm {
     int32_t* counts[B200MOE_EP_MAX_WORLD];             // [world, n_experts] on every rank
     unsigned long long* signal[B200MOE_EP_MAX_WORLD];  // [3, B200MOE_EP_MAX_WORLD] on every rank
     int* status;                                       // local: two status words
+    unsigned long long* step_counter;                  // local: the step number when the host passes 0
 };
 
 constexpr int kSigCounts = 0, kSigRows = 1, kSigResults = 2;
@@ -86,7 +87,24 @@ __device__ __forceinline__ void ep_signal_all(const EpComm& c, int which, unsign
         st_release_sys(c.signal[threadIdx.x] + which * B200MOE_EP_MAX_WORLD + c.rank, step);
 }
 
+// The host may pass step 0: the step number then lives on the device (the counts kernel opens a
+// step by incrementing it, the other kernels read it), which keeps the arguments of a whole layer
+// pass constant from step to step.
+__device__ __forceinline__ unsigned long long ep_step(const EpComm& c, unsigned long long step) {
+    return step != 0 ? step : *c.step_counter;
+}
+
 __global__ void ep_post_counts_kernel(EpComm c, const long long* __restrict__ counts, unsigned long long step) {
+    __shared__ unsigned long long s_step;
+    if (threadIdx.x == 0) {
+        if (step == 0) {
+            step = *c.step_counter + 1;
+            *c.step_counter = step;
+        }
+        s_step = step;
+    }
+    __syncthreads();
+    step = s_step;
     for (int e = threadIdx.x; e < c.n_experts; e += blockDim.x) {
         const int v = (int)counts[e];
         for (int d = 0; d < c.world; ++d) c.counts[d][c.rank * c.n_experts + e] = v;
@@ -94,9 +112,11 @@ __global__ void ep_post_counts_kernel(EpComm c, const long long* __restrict__ co
     ep_signal_all(c, kSigCounts, step);
 }
 
-__global__ void ep_post_kernel(EpComm c, int which, unsigned long long step) { ep_signal_all(c, which, step); }
+__global__ void ep_post_kernel(EpComm c, int which, unsigned long long step) { ep_signal_all(c, which, ep_step(c, step)); }
 
-__global__ void ep_wait_kernel(EpComm c, int which, unsigned long long step) { (void)ep_wait_all(c, which, step, 10 + which); }
+__global__ void ep_wait_kernel(EpComm c, int which, unsigned long long step) {
+    (void)ep_wait_all(c, which, ep_step(c, step), 10 + which);
+}
 
 // The plan every CTA derives from the count table (E <= 1024):
 //   s_start[e]  first of this rank's sorted rows that belongs to expert e (s_start[E] = all rows)
@@ -106,6 +126,7 @@ ep_dispatch_kernel(EpComm c, const uint4* __restrict__ x, const int32_t* __restr
                    unsigned long long step, int32_t* __restrict__ remote_pos, long long* __restrict__ local_counts,
                    long long* __restrict__ n_recv, int* __restrict__ done_counter) {
     __shared__ int s_start[kMaxExperts + 1], s_base[kMaxExperts], s_tot[kMaxExperts], s_before[kMaxExperts];
+    step = ep_step(c, step);
     (void)ep_wait_all(c, kSigCounts, step, 1);
     const int E = c.n_experts;
     const int32_t* tab = c.counts[c.rank];
@@ -180,7 +201,7 @@ ep_dispatch_kernel(EpComm c, const uint4* __restrict__ x, const int32_t* __restr
 __global__ void ep_combine_kernel(EpComm c, const int32_t* __restrict__ remote_pos, const int32_t* __restrict__ slot,
                                   const float* __restrict__ weight, uint4* __restrict__ out, int top_k,
                                   unsigned long long step) {
-    (void)ep_wait_all(c, kSigResults, step, 2);
+    (void)ep_wait_all(c, kSigResults, ep_step(c, step), 2);
     const long long t = blockIdx.x;
     __shared__ const uint4* s_row[32];
     __shared__ float s_w[32];
@@ -250,8 +271,9 @@ static int to_comm(const b200moe_ep_comm* h, EpComm* c) {
         c->counts[r] = h->peer_counts[r];
         c->signal[r] = reinterpret_cast<unsigned long long*>(h->peer_signal[r]);
     }
-    if (!h->status) return B200MOE_ERR_NULL_POINTER;
+    if (!h->status || !h->step_counter) return B200MOE_ERR_NULL_POINTER;
     c->status = h->status;
+    c->step_counter = reinterpret_cast<unsigned long long*>(h->step_counter);
     return B200MOE_OK;
 }
 

@@ -69,7 +69,8 @@ __global__ void route_topk_kernel(const __nv_bfloat16* __restrict__ logits, int 
 #pragma unroll
     for (int i = 0; i < kRouteMaxPerLane; ++i) {
         const int e = i * 32 + lane;
-        v[i] = (i < per && e < E) ? __bfloat162float(logits[(size_t)t * E + e]) : -INFINITY;
+        const float f = (i < per && e < E) ? __bfloat162float(logits[(size_t)t * E + e]) : -INFINITY;
+        v[i] = f == f ? f : -INFINITY;  // a NaN logit ranks last instead of derailing the comparisons
     }
     float top0 = 0.f, denom = 0.f, mine = 0.f;
     int mine_idx = 0;
@@ -90,6 +91,7 @@ __global__ void route_topk_kernel(const __nv_bfloat16* __restrict__ logits, int 
         if (j == 0) top0 = best;
         const float p = __expf(best - top0);
         denom += p;
+        bi = bi < E ? bi : E - 1;  // unreachable with k <= E; keeps the histogram index in range regardless
         if (lane == j) { mine = p; mine_idx = bi; }
         if ((bi & 31) == lane) {
 #pragma unroll

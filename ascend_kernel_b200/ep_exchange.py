@@ -86,7 +86,10 @@ class PeerExchange:
         for r in range(self.world):
             c.peer_recv_x[r], c.peer_y[r] = self._peer["recv_x"][r], self._peer["y"][r]
             c.peer_counts[r], c.peer_signal[r] = self._peer["counts"][r], self._peer["signal"][r]
+        self._step_dev = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self.device_steps = False  # True: the step number lives on the device (constant kernel arguments)
         c.status = self.status.data_ptr()
+        c.step_counter = self._step_dev.data_ptr()
         self._comm = c
         # torch views of the two local row buffers (inputs / outputs of the grouped GEMMs)
         self.recv_x = _as_tensor(self._own["recv_x"], (cap_rows, hidden), torch.bfloat16, self.device)
@@ -100,9 +103,19 @@ class PeerExchange:
         self.step += 1
         return self.step
 
+    def use_device_steps(self):
+        """From now on the step number is kept on the device and the kernels get step 0, so a layer
+        pass has the same arguments every time.  Call between steps, with the stream idle."""
+        torch.cuda.current_stream().synchronize()
+        self._step_dev.fill_(self.step)
+        self.device_steps = True
+
+    def _step_arg(self) -> int:
+        return 0 if self.device_steps else self.step
+
     def post_counts(self, counts):
         with torch.cuda.device(self.device):
-            _abi.check(_lib.b200moe_ep_post_counts(ctypes.byref(self._comm), counts.data_ptr(), self.step, self._s()),
+            _abi.check(_lib.b200moe_ep_post_counts(ctypes.byref(self._comm), counts.data_ptr(), self._step_arg(), self._s()),
                        "ep_post_counts")
         ops._count(1)
 
@@ -114,19 +127,19 @@ class PeerExchange:
         n_recv = torch.empty(1, dtype=torch.int64, device=self.device)
         with torch.cuda.device(self.device):
             _abi.check(_lib.b200moe_ep_dispatch(ctypes.byref(self._comm), x.data_ptr(), token_of.data_ptr(), n_rows,
-                                                self.step, remote_pos.data_ptr(), local_counts.data_ptr(),
+                                                self._step_arg(), remote_pos.data_ptr(), local_counts.data_ptr(),
                                                 n_recv.data_ptr(), self._done.data_ptr(), self._s()), "ep_dispatch")
         ops._count(1)
         return remote_pos, local_counts, n_recv
 
     def wait(self, which: int):
         with torch.cuda.device(self.device):
-            _abi.check(_lib.b200moe_ep_wait(ctypes.byref(self._comm), which, self.step, self._s()), "ep_wait")
+            _abi.check(_lib.b200moe_ep_wait(ctypes.byref(self._comm), which, self._step_arg(), self._s()), "ep_wait")
         ops._count(1)
 
     def post(self, which: int):
         with torch.cuda.device(self.device):
-            _abi.check(_lib.b200moe_ep_post(ctypes.byref(self._comm), which, self.step, self._s()), "ep_post")
+            _abi.check(_lib.b200moe_ep_post(ctypes.byref(self._comm), which, self._step_arg(), self._s()), "ep_post")
         ops._count(1)
 
     def combine(self, remote_pos, slot, weight, out=None):
@@ -135,7 +148,7 @@ class PeerExchange:
             out = torch.empty(T, self.hidden, dtype=torch.bfloat16, device=self.device)
         with torch.cuda.device(self.device):
             _abi.check(_lib.b200moe_ep_combine(ctypes.byref(self._comm), remote_pos.data_ptr(), slot.data_ptr(),
-                                               weight.data_ptr(), out.data_ptr(), T, top_k, self.step, self._s()),
+                                               weight.data_ptr(), out.data_ptr(), T, top_k, self._step_arg(), self._s()),
                        "ep_combine")
         ops._count(1)
         return out

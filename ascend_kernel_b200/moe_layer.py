@@ -191,6 +191,49 @@ class MoELayer:
         return out_host
 
 
+class GraphedLayer:
+    """One layer pass recorded as a CUDA graph and replayed: a step then costs the host one graph
+    launch instead of a dozen kernel launches and as many allocations.  Needs a pass without host
+    synchronisation: one rank, or ``exchange="p2p"`` (whose step number moves to the device so that
+    the recorded kernel arguments stay valid).  With several ranks every rank must construct its
+    GraphedLayer and call it the same number of times."""
+
+    def __init__(self, layer: MoELayer, n_tokens: int):
+        if layer.world > 1 and layer.px is None:
+            raise RuntimeError("the NCCL exchange reads split sizes on the host and cannot be recorded")
+        self.layer = layer
+        dev = layer.device
+        self.x = torch.zeros(n_tokens, layer.hidden, dtype=torch.bfloat16, device=dev)
+        self.logits = torch.zeros(n_tokens, layer.n_experts, dtype=torch.bfloat16, device=dev)
+        if layer.px is not None:
+            layer.px.use_device_steps()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):  # warm-up outside the recording (lazy initialisation, allocator pools)
+                layer.forward(self.x, self.logits)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        before = ops.LAUNCHES
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out = layer.forward(self.x, self.logits)
+        self.launches = ops.LAUNCHES - before
+        ops.LAUNCHES = before
+
+    def __call__(self, x=None, logits=None):
+        """Runs one pass on the current stream; ``x`` / ``logits`` (device or pinned host tensors) are
+        copied into the recorded inputs first.  Returns the recorded output tensor, which the next
+        call overwrites."""
+        if x is not None:
+            self.x.copy_(x, non_blocking=True)
+        if logits is not None:
+            self.logits.copy_(logits, non_blocking=True)
+        self.graph.replay()
+        ops._count(self.launches)
+        return self.out
+
+
 class HostPipeline:
     """Host-buffer calls with ``depth`` steps in flight.
 
@@ -201,8 +244,10 @@ class HostPipeline:
     inputs and its whole result.  ``submit`` returns an event that completes when the step's result
     is in ``out_host``; ``drain`` waits for everything submitted."""
 
-    def __init__(self, layer: MoELayer, depth: int = 2):
-        self.layer, self.depth = layer, depth
+    def __init__(self, layer: MoELayer, depth: int = 2, graphed: GraphedLayer = None):
+        """``graphed``: a GraphedLayer of ``layer`` for the token count the pipeline will be fed;
+        the kernels of a step are then one graph launch."""
+        self.layer, self.depth, self.graphed = layer, depth, graphed
         self.s_in, self.s_out = torch.cuda.Stream(layer.device), torch.cuda.Stream(layer.device)
         self.slots = [dict(x=None, lg=None, out=None, in_done=None, comp_done=None, out_done=None)
                       for _ in range(depth)]
@@ -225,7 +270,13 @@ class HostPipeline:
         main.wait_event(sl["in_done"])
         if sl["out_done"] is not None:               # the copy that last read this slot's result
             main.wait_event(sl["out_done"])
-        sl["out"] = self.layer.forward(sl["x"], sl["lg"])
+        if self.graphed is not None:
+            res = self.graphed(sl["x"], sl["lg"])
+            if sl["out"] is None or sl["out"].shape != res.shape:
+                sl["out"] = torch.empty_like(res)
+            sl["out"].copy_(res, non_blocking=True)  # the recorded output is overwritten by the next step
+        else:
+            sl["out"] = self.layer.forward(sl["x"], sl["lg"])
         sl["comp_done"] = torch.cuda.Event()
         sl["comp_done"].record(main)
         with torch.cuda.stream(self.s_out):

@@ -394,9 +394,11 @@ def run_ours(args):
     barrier()
     latency_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
     # the same calls with two steps in flight (copy-in / kernels / copy-out on three streams)
-    from ascend_kernel_b200.moe_layer import HostPipeline
+    from ascend_kernel_b200.moe_layer import GraphedLayer, HostPipeline
 
-    pipe = HostPipeline(layer, depth=2)
+    # the kernels of a step as one CUDA-graph launch where the step has no host synchronisation
+    graphed = GraphedLayer(layer, t_local) if exchange != "nccl" else None
+    pipe = HostPipeline(layer, depth=2, graphed=graphed)
     outs = [out_host, torch.empty_like(out_host).pin_memory()]
     for i in range(min(3, args.warmup)):
         pipe.submit(x_host, lg_host, outs[i % 2])
@@ -437,7 +439,8 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "bf16 x int8 -> fp32 accumulate", "data": "synthetic",
         "config": {**workload_config(world), "exchange": exchange, "exchange_status": exchange_status},
         "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms, "steps_in_flight": 2, "single_step_latency_ms": latency_ms},
+                "ms_per_step": e2e_ms, "steps_in_flight": 2, "cuda_graph": graphed is not None,
+                "single_step_latency_ms": latency_ms},
         "gpu_launches": launches * args.steps, "gpu_launches_per_step": launches,
         "roofline": roofline, "clocks": clk.result, "phases_ms_rank0": {k: round(v, 4) for k, v in phases.items()},
     }

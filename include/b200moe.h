@@ -163,6 +163,9 @@ int b200moe_moe_regroup_index(const int64_t* recv_counts, int64_t world, int64_t
  *   counts  int32 [world, n_experts]  rows per (source rank, expert)
  *   signal  uint64 [3, B200MOE_EP_MAX_WORLD]  step numbers: counts / rows / results, one per source
  * `step` is a number that grows by one per layer pass, starting at 1 (the buffers start zeroed).
+ * A caller that wants identical arguments in every pass (to record the pass once and replay it)
+ * passes step 0 everywhere: b200moe_ep_post_counts then opens a step by incrementing
+ * *step_counter on the device and the other calls read it.
  * Waits inside the kernels are bounded (2 s): on expiry status word 0 of `status` becomes 2 and the
  * kernels carry on without faulting.  world <= B200MOE_EP_MAX_WORLD, n_experts % world == 0,
  * n_experts <= 1024, cap_rows * world < 2^31. */
@@ -175,7 +178,8 @@ typedef struct b200moe_ep_comm {
     void* peer_y[B200MOE_EP_MAX_WORLD];
     int32_t* peer_counts[B200MOE_EP_MAX_WORLD];
     uint64_t* peer_signal[B200MOE_EP_MAX_WORLD];
-    int32_t* status; /* local device memory, >= 2 words, zeroed by the caller */
+    int32_t* status;        /* local device memory, >= 2 words, zeroed by the caller */
+    uint64_t* step_counter; /* local device memory, one word, zeroed by the caller (see `step`) */
 } b200moe_ep_comm;
 enum { B200MOE_EP_SIG_COUNTS = 0, B200MOE_EP_SIG_ROWS = 1, B200MOE_EP_SIG_RESULTS = 2 };
 

@@ -205,6 +205,40 @@ def test_host_pipeline_matches_single_calls():
 
 
 @pytest.mark.gpu
+def test_graphed_layer_replays_match_eager_calls():
+    """The recorded pass (direct path and peer-memory exchange) replayed on new inputs gives the bits
+    of the eager call, also through the host pipeline."""
+    from ascend_kernel_b200.moe_layer import GraphedLayer, HostPipeline, MoELayer
+
+    c = small_case(T=200, H=256, E=8, I=256, k=2)
+    d = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
+    w = [d[k] for k in ("w13", "s13", "o13", "w2", "s2", "o2")]
+    eager = MoELayer(*w, c["E"], c["top_k"])
+    for exchange in ("nccl", "p2p"):  # one rank: "nccl" is the direct path
+        layer = MoELayer(*w, c["E"], c["top_k"], exchange=exchange, max_tokens=200)
+        g = GraphedLayer(layer, 200)
+        for step in range(3):
+            x, lg = _step_inputs(c, step)
+            want = eager.forward(x.cuda(), lg.cuda())
+            got = g(x.cuda(), lg.cuda())
+            torch.cuda.synchronize()
+            assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (exchange, step)
+        pipe = HostPipeline(layer, depth=2, graphed=g)
+        outs = [torch.empty(200, 256, dtype=torch.bfloat16).pin_memory() for _ in range(4)]
+        for step in range(4):
+            x, lg = _step_inputs(c, step)
+            pipe.submit(x.pin_memory(), lg.pin_memory(), outs[step])
+        pipe.drain()
+        for step in range(4):
+            x, lg = _step_inputs(c, step)
+            want = eager.forward(x.cuda(), lg.cuda()).cpu()
+            assert torch.equal(outs[step].view(torch.int16), want.view(torch.int16)), (exchange, step)
+        if layer.px is not None:
+            assert layer.px.read_status()[0] == 0
+            layer.px.close()
+
+
+@pytest.mark.gpu
 def test_aux_kernels_match_torch():
     import ascend_kernel_b200 as ak
 
