@@ -73,7 +73,9 @@ struct GmTraits {
 struct GmBarriers {
     uint64_t full[kNS];   // TMA bytes of the x boxes + the dequant warps of the stage's group
     uint64_t empty[kNS];  // one tcgen05.commit per stage
-    uint64_t t_full, t_empty;
+    // accumulator hand-off, one pair per 256-column accumulator: a two-half tile uses both, a one-half
+    // tile alternates between them so that its epilogue overlaps the next tile's main loop
+    uint64_t t_full[2], t_empty[2];
     uint64_t drain;
     uint32_t tmem_base;
     int abort;
@@ -174,17 +176,50 @@ struct PackedRegs {
     float sf;          // fp8 only: the fp32 scale of the thread's 128 x 128 block
 };
 
+// Position of a dequant thread in the (tile, k-stage) sequence of its CTA, with the address of the
+// thread's first packed row of that stage carried along (advanced by a constant inside a tile).
+struct DqIter {
+    int t, kt, g, n0;
+    bool valid;
+    const uint8_t* wp;
+};
 template <int MODE>
-__device__ __forceinline__ void load_packed(PackedRegs<MODE>& r, const uint8_t* __restrict__ w, const GemmArgs& a,
-                                            const TileInfo& ti, int kt, const DqLane& d) {
+__device__ __forceinline__ void dq_locate(DqIter& it, const uint8_t* __restrict__ w, const GemmArgs& a, const DqLane& d,
+                                          int n_tiles, const int* tile_prefix, const int* row_start, int n_nt) {
+    using T = GmTraits<MODE>;
+    it.valid = it.t < n_tiles;
+    if (!it.valid) return;
+    const TileInfo ti = locate_tile(it.t, tile_prefix, row_start, a.G, n_nt);
+    it.g = ti.g;
+    it.n0 = ti.n0;
+    const size_t row_bytes = T::kNibbles ? (size_t)a.N / 2 : (size_t)a.N;
+    it.wp = w + ((size_t)ti.g * a.K + (size_t)it.kt * kBK + d.row) * row_bytes +
+            (T::kNibbles ? (ti.n0 >> 1) + d.c16 * 8 : ti.n0 + d.c16 * 16);
+}
+template <int MODE>
+__device__ __forceinline__ void dq_advance(DqIter& it, int step, const uint8_t* __restrict__ w, const GemmArgs& a,
+                                           const DqLane& d, int n_kt, int n_tiles, const int* tile_prefix,
+                                           const int* row_start, int n_nt) {
+    using T = GmTraits<MODE>;
+    it.kt += step;
+    if (it.kt < n_kt) {
+        it.wp += (size_t)step * kBK * (T::kNibbles ? (size_t)a.N / 2 : (size_t)a.N);
+        return;
+    }
+    do {
+        it.kt -= n_kt;
+        it.t += gridDim.x;
+    } while (it.kt >= n_kt);
+    dq_locate<MODE>(it, w, a, d, n_tiles, tile_prefix, row_start, n_nt);
+}
+
+template <int MODE>
+__device__ __forceinline__ void load_packed(PackedRegs<MODE>& r, const DqIter& it, const GemmArgs& a, const DqLane& d) {
     using T = GmTraits<MODE>;
     const size_t row_bytes = T::kNibbles ? (size_t)a.N / 2 : (size_t)a.N;
-    const int kb = kt;
-    const uint8_t* base = w + ((size_t)ti.g * a.K + (size_t)kb * kBK + d.row) * row_bytes +
-                          (T::kNibbles ? (ti.n0 >> 1) + d.c16 * 8 : ti.n0 + d.c16 * 16);
 #pragma unroll
     for (int j = 0; j < kDqRows; ++j) {
-        const uint8_t* p = base + (size_t)(kDqRowStep * j) * row_bytes;
+        const uint8_t* p = it.wp + (size_t)(kDqRowStep * j) * row_bytes;
         if constexpr (T::kNibbles) {
             const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
             r.q[j] = make_uint4(v.x, v.y, 0u, 0u);
@@ -194,26 +229,33 @@ __device__ __forceinline__ void load_packed(PackedRegs<MODE>& r, const uint8_t* 
     }
     if constexpr (MODE == B200MOE_CT_FP8) {
         r.sf = __ldg(static_cast<const float*>(a.scale) +
-                     ((size_t)ti.g * (a.K >> 7) + ((kb * kBK) >> 7)) * (a.N >> 7) + ((ti.n0 + d.c16 * 16) >> 7));
+                     ((size_t)it.g * (a.K >> 7) + ((it.kt * kBK) >> 7)) * (a.N >> 7) + ((it.n0 + d.c16 * 16) >> 7));
     }
     if constexpr (MODE == B200MOE_CT_FP4) {
         const uint4* sp = reinterpret_cast<const uint4*>(
             static_cast<const __nv_bfloat16*>(a.scale) +
-            ((size_t)ti.g * (a.K >> 4) + ((kb * kBK + d.row) >> 4)) * a.N + ti.n0 + d.c16 * 16);
+            ((size_t)it.g * (a.K >> 4) + ((it.kt * kBK + d.row) >> 4)) * a.N + it.n0 + d.c16 * 16);
         r.s[0] = __ldg(sp);
         r.s[1] = __ldg(sp + 1);
     }
 }
 
+// 16-byte shared-memory store at a 32-bit shared address.
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+// Shared address of the thread's chunk pair in its row j, from the address `sa` of the pair in its
+// row 0: the thread's rows are k = row0 + 2j with row0 & 7 in {0, 1}, so the swizzle term changes by
+// XOR with 2j (bits 5..6 of the address) and the row offset by j * 256 bytes.  The second chunk of
+// the pair is at the returned address ^ 16.
+__device__ __forceinline__ uint32_t dq_row_addr(uint32_t sa, int j) { return (sa ^ (uint32_t)(j << 5)) + (uint32_t)(j * 256); }
+
 template <int MODE>
-__device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint8_t* bt, const GemmArgs& a,
-                                              const TileInfo& ti, int kt, const DqLane& d) {
-    const int c16 = d.c16;
+__device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint32_t sa) {
     const float sf = (MODE == B200MOE_CT_FP8) ? r.sf : 1.f;
     const f32x2 sf2 = pack_f32x2(sf, sf);
 #pragma unroll
     for (int j = 0; j < kDqRows; ++j) {
-        const int k = d.row + kDqRowStep * j;
         const uint4 q = r.q[j];
         uint32_t o[8];
         if constexpr (MODE == B200MOE_CT_INT8) {
@@ -248,8 +290,9 @@ __device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint8_t
             o[4] = mul_bf16x2(v[0], s1.x); o[5] = mul_bf16x2(v[1], s1.y);
             o[6] = mul_bf16x2(v[2], s1.z); o[7] = mul_bf16x2(v[3], s1.w);
         }
-        *reinterpret_cast<uint4*>(bt + btile_offset(k, 2 * c16)) = make_uint4(o[0], o[1], o[2], o[3]);
-        *reinterpret_cast<uint4*>(bt + btile_offset(k, 2 * c16 + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
+        const uint32_t aj = dq_row_addr(sa, j);
+        sts128(aj, o[0], o[1], o[2], o[3]);
+        sts128(aj ^ 16u, o[4], o[5], o[6], o[7]);
     }
 }
 
@@ -260,8 +303,8 @@ __device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint8_t
 struct Int4Scales {
     uint4 s[2], o[2];
 };
-__device__ __forceinline__ Int4Scales load_int4_scales(const GemmArgs& a, const TileInfo& ti, int kb, const DqLane& d) {
-    const size_t so = ((size_t)ti.g * (a.K >> 7) + ((kb * kBK) >> 7)) * a.N + ti.n0 + d.c16 * 16;
+__device__ __forceinline__ Int4Scales load_int4_scales(const GemmArgs& a, int g, int n0, int kb, const DqLane& d) {
+    const size_t so = ((size_t)g * (a.K >> 7) + ((kb * kBK) >> 7)) * a.N + n0 + d.c16 * 16;
     const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.scale) + so);
     Int4Scales r;
     r.s[0] = __ldg(sp);
@@ -277,8 +320,7 @@ __device__ __forceinline__ Int4Scales load_int4_scales(const GemmArgs& a, const 
 }
 
 __device__ __forceinline__ void convert_block_int4(const PackedRegs<B200MOE_CT_INT4>& r, const Int4Scales& sc,
-                                                   uint8_t* bt_hi, uint8_t* bt_lo, const DqLane& d) {
-    const int c16 = d.c16;
+                                                   uint32_t sa_hi, uint32_t sa_lo) {
     const f32x2 kMagic = pack_f32x2(8388616.0f, 8388616.0f);  // 2^23 + 8
 #pragma unroll
     for (int h = 0; h < 2; ++h) {  // columns 8h .. 8h+7: one 16-byte chunk of the bf16 tile per row
@@ -309,9 +351,8 @@ __device__ __forceinline__ void convert_block_int4(const PackedRegs<B200MOE_CT_I
         }
 #pragma unroll
         for (int j = 0; j < kDqRows; ++j) {
-            const uint32_t off = btile_offset(d.row + kDqRowStep * j, 2 * c16 + h);
-            *reinterpret_cast<uint4*>(bt_hi + off) = make_uint4(hi[j][0], hi[j][1], hi[j][2], hi[j][3]);
-            *reinterpret_cast<uint4*>(bt_lo + off) = make_uint4(lo[j][0], lo[j][1], lo[j][2], lo[j][3]);
+            sts128(dq_row_addr(sa_hi, j) ^ (uint32_t)(h << 4), hi[j][0], hi[j][1], hi[j][2], hi[j][3]);
+            sts128(dq_row_addr(sa_lo, j) ^ (uint32_t)(h << 4), lo[j][0], lo[j][1], lo[j][2], lo[j][3]);
         }
     }
 }
@@ -368,8 +409,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         sb->n_tiles = acc;
         sb->abort = 0;
         for (int i = 0; i < NS; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->full[i]), 1 + kDqGroupWarps); ptx::mbar_init(ptx::smem_u32(&sb->empty[i]), 1); }
-        ptx::mbar_init(ptx::smem_u32(&sb->t_full), 1);
-        ptx::mbar_init(ptx::smem_u32(&sb->t_empty), kEpiWarps);
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(ptx::smem_u32(&sb->t_full[i]), 1);
+            ptx::mbar_init(ptx::smem_u32(&sb->t_empty[i]), kEpiWarps / 2);
+        }
         ptx::mbar_init(ptx::smem_u32(&sb->drain), 1);
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_x);
@@ -394,6 +437,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         if (lane == 0) {
             uint32_t ia = 0;
             bool ok = true;
+            const bool dbg = (a.tune & 64) && blockIdx.x == 0;
+            long long pT[3] = {0, 0, 0};
             StageIter far;
             iter_start(far, n_tiles, tile_prefix, row_start, a.G, n_nt);
             for (int i = 0; i < kL2Ahead && far.valid; ++i) {
@@ -404,21 +449,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
                 for (int kt = 0; kt < n_kt; ++kt, ++ia) {
                     const uint32_t s = ia % NS, ph = (ia / NS) & 1;
+                    long long c0 = clock64();
                     if (ia >= NS && !gm_wait(&sb->empty[s], ph ^ 1, sb, a.status, 10 + (int)s)) { ok = false; break; }
+                    long long c1 = clock64();
                     const uint32_t bar = ptx::smem_u32(&sb->full[s]);
-                    ptx::mbar_arrive_expect_tx(bar, ti.halves * kAHalfBytes);
                     const int kx = kt * kBK;
+                    if (a.tune & 4) { ptx::mbar_arrive(bar); } else {
+                    ptx::mbar_arrive_expect_tx(bar, ti.halves * kAHalfBytes);
                     ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes), &tmap_x, bar, kx, ti.row0);
                     if (ti.halves == 2)
                         ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes + kAHalfBytes), &tmap_x, bar, kx,
                                          ti.row0 + kBM);
-                    if (far.valid) {
+                    }
+                    if (far.valid && !(a.tune & 16)) {
                         ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0,
                                                 far.ti.g * a.K + far.kt * kBK);
                         iter_next(far, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
                     }
+                    if (dbg) { long long c2 = clock64(); pT[0] += c1 - c0; pT[1] += c2 - c1; pT[2] += 1; }
                 }
             }
+            if (dbg) for (int i = 0; i < 3; ++i) a.status[28 + i] = (int)(pT[i] >> 4);
             if (!ok)
                 for (uint32_t j = (ia > NS ? ia - NS : 0); j < ia; ++j)
                     (void)ptx::mbar_wait(ptx::smem_u32(&sb->full[j % NS]), (j / NS) & 1);
@@ -434,55 +485,83 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             const uint64_t da0 = ptx::umma_desc_sw128(ptx::smem_u32(a_ring), 0, 1024);
             // B: MN-major, 64-column blocks kBK*128 B apart (LBO), 8-k groups 1024 B apart (SBO)
             const uint64_t db0 = ptx::umma_desc_sw128(ptx::smem_u32(b_ring), kBK * 128, 1024);
-            uint32_t sa = 0, pha = 0, it = 0;
+            uint32_t sa = 0, pha = 0;
+            uint32_t uses[2] = {0, 0}, next1 = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++it) {
+            const bool dbg = (a.tune & 64) && blockIdx.x == 0;
+            long long mT[4] = {0, 0, 0, 0};
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
-                // the accumulators are single-buffered: the previous tile's epilogue must have drained them
-                if (it >= 1 && !gm_wait(&sb->t_empty, (it - 1) & 1, sb, a.status, 30)) { ok = false; break; }
+                // accumulators of this tile: both for two halves, else the one used less recently;
+                // the epilogue of their previous tile must have drained them
+                const uint32_t b0 = ti.halves == 2 ? 0u : next1, b1 = ti.halves == 2 ? 2u : next1 + 1u;
+                if (ti.halves == 1 && !(a.tune & 1)) next1 ^= 1u;
+                for (uint32_t b = b0; b < b1 && ok; ++b)
+                    if (uses[b] >= 1 && !gm_wait(&sb->t_empty[b], (uses[b] - 1) & 1, sb, a.status, 30 + (int)b)) ok = false;
+                if (!ok) break;
+                const uint32_t acc0 = tmem_base + b0 * kBN;
                 ptx::tc_fence_after();
                 uint32_t accumulate = 0;
                 for (int kt = 0; kt < n_kt; ++kt) {
+                    long long c0 = clock64();
                     if (!gm_wait(&sb->full[sa], pha, sb, a.status, 40 + (int)sa)) { ok = false; break; }
+                    long long c1 = clock64();
                     ptx::tc_fence_after();
                     const uint64_t da = da0 + (uint64_t)(sa * (kATileBytes >> 4));
+                    if (!(a.tune & 8))
 #pragma unroll
                     for (int p = 0; p < P; ++p) {  // int4: the hi tile, then the lo tile, against the same x stage
                         const uint64_t db = db0 + (uint64_t)((sa * P + p) * (kBTileBytes >> 4));
 #pragma unroll
                         for (int k16 = 0; k16 < kBK / 16; ++k16)
-                            ptx::umma_bf16(tmem_base, da + (uint64_t)(k16 * 2), db + (uint64_t)(k16 * 128), idesc,
+                            ptx::umma_bf16(acc0, da + (uint64_t)(k16 * 2), db + (uint64_t)(k16 * 128), idesc,
                                            accumulate | (uint32_t)(k16 + p));
                         if (ti.halves == 2) {
 #pragma unroll
                             for (int k16 = 0; k16 < kBK / 16; ++k16)
-                                ptx::umma_bf16(tmem_base + kBN, da + (uint64_t)((kAHalfBytes >> 4) + k16 * 2),
+                                ptx::umma_bf16(acc0 + kBN, da + (uint64_t)((kAHalfBytes >> 4) + k16 * 2),
                                                db + (uint64_t)(k16 * 128), idesc, accumulate | (uint32_t)(k16 + p));
                         }
                     }
                     accumulate = 1;
                     ptx::umma_commit(ptx::smem_u32(&sb->empty[sa]));
                     if (++sa == NS) { sa = 0; pha ^= 1; }
+                    if (dbg) { long long c2 = clock64(); mT[0] += c1 - c0; mT[1] += c2 - c1; mT[2] += 1; }
                 }
-                if (ok) ptx::umma_commit(ptx::smem_u32(&sb->t_full));
+                if (ok)
+                    for (uint32_t b = b0; b < b1; ++b) {
+                        ptx::umma_commit(ptx::smem_u32(&sb->t_full[b]));
+                        ++uses[b];
+                    }
             }
             // drain: every issued MMA must have completed before TMEM is released
             ptx::umma_commit(ptx::smem_u32(&sb->drain));
             (void)ptx::mbar_wait(ptx::smem_u32(&sb->drain), 0);
+            if (dbg) for (int i = 0; i < 3; ++i) a.status[24 + i] = (int)(mT[i] >> 4);
         }
         __syncwarp();
     } else if (warp >= kWarpEpi0 && warp < kWarpEpi0 + kEpiWarps) {
         // ------------------------------ epilogue ------------------------------
         const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31 are the ones this warp may read
-        const int half = (warp - kWarpEpi0) >> 2;     // which accumulator / row half of the tile
+        const int grp = (warp - kWarpEpi0) >> 2;      // which accumulator this warp drains
         const bool per_channel = (MODE == B200MOE_CT_INT8);
         const bool has_offset = per_channel && a.offset != nullptr;
-        uint32_t it = 0;
-        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++it) {
+        uint32_t use = 0, next1 = 0;
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
             const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
-            if (!__all_sync(0xffffffffu, gm_wait(&sb->t_full, it & 1, sb, a.status, 60))) break;
+            // a two-half tile: this group takes row half `grp`; a one-half tile sits in one accumulator
+            bool mine = true;
+            int half = grp;
+            if (ti.halves == 1) {
+                mine = (int)next1 == grp;
+                half = 0;
+                if (!(a.tune & 1)) next1 ^= 1u;
+            }
+            if (!mine) continue;
+            if (!__all_sync(0xffffffffu, gm_wait(&sb->t_full[grp], use & 1, sb, a.status, 60 + grp))) break;
+            ++use;
             ptx::tc_fence_after();
-            if (half < ti.halves) {
+            {
                 const int row = ti.row0 + half * kBM + quarter * 32 + lane;
                 const bool row_ok = row < ti.row_end;
                 const float rs = (has_offset && row_ok) ? __ldg(a.rowsum + row) : 0.f;
@@ -490,7 +569,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 #pragma unroll 1
                 for (int c = 0; c < kBN / 32; ++c) {
                     uint32_t r[32];
-                    ptx::tmem_ld_32x32(tmem_base + half * kBN + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
+                    ptx::tmem_ld_32x32(tmem_base + grp * kBN + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
                     float sv = 1.f, sov = 0.f;
                     if (per_channel) {
                         const size_t ci = (size_t)ti.g * a.N + ti.n0 + c * 32 + lane;
@@ -524,55 +603,63 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             }
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->t_empty));
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->t_empty[grp]));
         }
     } else if (warp >= kWarpDq0) {
         // ------------------------------ dequant ------------------------------
-        // A unit of work is one stage (one k block); for int4 it holds the hi and the lo tile.
+        // A unit of work is one stage (one k block); for int4 it holds the hi and the lo tile.  These
+        // warps bound the kernel when tiles are small, so the loop carries as little bookkeeping as it
+        // can: a stage counter, one iterator (for the loads, kPrefetch units ahead) whose global address
+        // advances by a constant inside a tile, and shared addresses derived from one per-thread offset.
         const int dq_tid = threadIdx.x - kWarpDq0 * 32;
         const int grp = dq_tid / (kDqGroupWarps * 32);
         const DqLane d = dq_lane(dq_tid % (kDqGroupWarps * 32));
-        StageIter cur, pf;
-        iter_start(cur, n_tiles, tile_prefix, row_start, a.G, n_nt);
-        for (int i = 0; i < grp && cur.valid; ++i) iter_next(cur, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
-        pf = cur;
+        const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+        const long long total = (long long)my_tiles * n_kt;  // stages of this CTA
+        const uint32_t units = total > grp ? (uint32_t)((total - grp + kDqGroups - 1) / kDqGroups) : 0u;
+        DqIter pf;
+        pf.t = blockIdx.x;
+        pf.kt = 0;
+        dq_locate<MODE>(pf, weight, a, d, n_tiles, tile_prefix, row_start, n_nt);
+        if (grp > 0 && pf.valid) dq_advance<MODE>(pf, grp, weight, a, d, n_kt, n_tiles, tile_prefix, row_start, n_nt);
+        DqIter cur = pf;  // int4 only: the stage being converted (its scales are loaded late)
         PackedRegs<MODE> regs[kPrefetch];
 #pragma unroll
         for (int u = 0; u < kPrefetch; ++u) {
             if (pf.valid) {
-                load_packed<MODE>(regs[u], weight, a, pf.ti, pf.kt, d);
-#pragma unroll
-                for (int i = 0; i < kDqGroups; ++i)
-                    if (pf.valid) iter_next(pf, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
+                load_packed<MODE>(regs[u], pf, a, d);
+                dq_advance<MODE>(pf, kDqGroups, weight, a, d, n_kt, n_tiles, tile_prefix, row_start, n_nt);
             }
         }
-        uint32_t ib = grp;
+        const uint32_t sa0 = ptx::smem_u32(b_ring) + btile_offset(d.row, 2 * d.c16);
+        uint32_t ib = grp, n = 0;
         bool ok = true;
-        while (cur.valid && ok) {
+        while (n < units && ok) {
 #pragma unroll
             for (int u = 0; u < kPrefetch; ++u) {
-                if (!cur.valid) break;
+                if (n >= units) break;
                 const uint32_t slot = ib % NS;
                 Int4Scales sc4;
-                if constexpr (MODE == B200MOE_CT_INT4) sc4 = load_int4_scales(a, cur.ti, cur.kt, d);
+                if constexpr (MODE == B200MOE_CT_INT4) sc4 = load_int4_scales(a, cur.g, cur.n0, cur.kt, d);
                 bool got = true;
                 if (ib >= NS) got = gm_wait(&sb->empty[slot], ((ib / NS) & 1) ^ 1, sb, a.status, 80 + (int)slot);
                 if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-                uint8_t* bt = b_ring + slot * P * kBTileBytes;
+                const uint32_t sa = sa0 + slot * (uint32_t)(P * kBTileBytes);
                 if constexpr (MODE == B200MOE_CT_INT4)
-                    convert_block_int4(regs[u], sc4, bt, bt + kBTileBytes, d);
+                    convert_block_int4(regs[u], sc4, sa, sa + kBTileBytes);
                 else
-                    convert_stage<MODE>(regs[u], bt, a, cur.ti, cur.kt, d);
+                    convert_stage<MODE>(regs[u], sa);
                 ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->full[slot]));
-                if (pf.valid) load_packed<MODE>(regs[u], weight, a, pf.ti, pf.kt, d);
-#pragma unroll
-                for (int i = 0; i < kDqGroups; ++i) {
-                    if (pf.valid) iter_next(pf, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
-                    if (cur.valid) iter_next(cur, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
+                if (pf.valid) {
+                    load_packed<MODE>(regs[u], pf, a, d);
+                    dq_advance<MODE>(pf, kDqGroups, weight, a, d, n_kt, n_tiles, tile_prefix, row_start, n_nt);
                 }
+                if constexpr (MODE == B200MOE_CT_INT4)
+                    dq_advance<MODE>(cur, kDqGroups, weight, a, d, n_kt, n_tiles, tile_prefix, row_start, n_nt);
                 ib += kDqGroups;
+                ++n;
             }
         }
     }
@@ -697,6 +784,7 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
     a.y = static_cast<__nv_bfloat16*>(y);
     a.M = (int)M; a.K = (int)K; a.N = (int)N; a.G = (int)G;
     a.gl_type = group_list_type;
+    { static const int tune = [] { const char* e = getenv("B200MOE_TUNE"); return e ? atoi(e) : 0; }(); a.tune = tune; }
     a.status = static_cast<int*>(workspace);
 
     if (compute_type == B200MOE_CT_INT8) {
@@ -799,6 +887,7 @@ extern "C" int b200moe_grouped_gemm_int8_noalloc(const void* x, const void* weig
     a.y = static_cast<__nv_bfloat16*>(y);
     a.M = (int)M; a.K = (int)K; a.N = (int)N; a.G = (int)G;
     a.gl_type = group_list_type;
+    { static const int tune = [] { const char* e = getenv("B200MOE_TUNE"); return e ? atoi(e) : 0; }(); a.tune = tune; }
     a.status = static_cast<int*>(scratch);
     if (offset != nullptr) {
         float* rowsum = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + B200MOE_STATUS_BYTES);
