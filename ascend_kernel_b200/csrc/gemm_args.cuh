@@ -13,7 +13,6 @@ struct GemmArgs {
     __nv_bfloat16* y;
     int M, K, N, G, gl_type;
     int* status;
-    int tune;  // experiment switches (B200MOE_TUNE), 0 in production
 };
 
 // CTA-pair (cta_group::2) kernel, grouped_gemm_pair.cu.  mode is a B200MOE_CT_* value.

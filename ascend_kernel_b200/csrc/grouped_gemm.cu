@@ -437,8 +437,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         if (lane == 0) {
             uint32_t ia = 0;
             bool ok = true;
-            const bool dbg = (a.tune & 64) && blockIdx.x == 0;
-            long long pT[3] = {0, 0, 0};
             StageIter far;
             iter_start(far, n_tiles, tile_prefix, row_start, a.G, n_nt);
             for (int i = 0; i < kL2Ahead && far.valid; ++i) {
@@ -449,27 +447,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
                 for (int kt = 0; kt < n_kt; ++kt, ++ia) {
                     const uint32_t s = ia % NS, ph = (ia / NS) & 1;
-                    long long c0 = clock64();
                     if (ia >= NS && !gm_wait(&sb->empty[s], ph ^ 1, sb, a.status, 10 + (int)s)) { ok = false; break; }
-                    long long c1 = clock64();
                     const uint32_t bar = ptx::smem_u32(&sb->full[s]);
                     const int kx = kt * kBK;
-                    if (a.tune & 4) { ptx::mbar_arrive(bar); } else {
                     ptx::mbar_arrive_expect_tx(bar, ti.halves * kAHalfBytes);
                     ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes), &tmap_x, bar, kx, ti.row0);
                     if (ti.halves == 2)
                         ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes + kAHalfBytes), &tmap_x, bar, kx,
                                          ti.row0 + kBM);
-                    }
-                    if (far.valid && !(a.tune & 16)) {
+                    if (far.valid) {
                         ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0,
                                                 far.ti.g * a.K + far.kt * kBK);
                         iter_next(far, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
                     }
-                    if (dbg) { long long c2 = clock64(); pT[0] += c1 - c0; pT[1] += c2 - c1; pT[2] += 1; }
                 }
             }
-            if (dbg) for (int i = 0; i < 3; ++i) a.status[28 + i] = (int)(pT[i] >> 4);
             if (!ok)
                 for (uint32_t j = (ia > NS ? ia - NS : 0); j < ia; ++j)
                     (void)ptx::mbar_wait(ptx::smem_u32(&sb->full[j % NS]), (j / NS) & 1);
@@ -488,14 +480,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             uint32_t sa = 0, pha = 0;
             uint32_t uses[2] = {0, 0}, next1 = 0;
             bool ok = true;
-            const bool dbg = (a.tune & 64) && blockIdx.x == 0;
-            long long mT[4] = {0, 0, 0, 0};
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
                 // accumulators of this tile: both for two halves, else the one used less recently;
                 // the epilogue of their previous tile must have drained them
                 const uint32_t b0 = ti.halves == 2 ? 0u : next1, b1 = ti.halves == 2 ? 2u : next1 + 1u;
-                if (ti.halves == 1 && !(a.tune & 1)) next1 ^= 1u;
+                if (ti.halves == 1) next1 ^= 1u;
                 for (uint32_t b = b0; b < b1 && ok; ++b)
                     if (uses[b] >= 1 && !gm_wait(&sb->t_empty[b], (uses[b] - 1) & 1, sb, a.status, 30 + (int)b)) ok = false;
                 if (!ok) break;
@@ -503,12 +493,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 ptx::tc_fence_after();
                 uint32_t accumulate = 0;
                 for (int kt = 0; kt < n_kt; ++kt) {
-                    long long c0 = clock64();
                     if (!gm_wait(&sb->full[sa], pha, sb, a.status, 40 + (int)sa)) { ok = false; break; }
-                    long long c1 = clock64();
                     ptx::tc_fence_after();
                     const uint64_t da = da0 + (uint64_t)(sa * (kATileBytes >> 4));
-                    if (!(a.tune & 8))
 #pragma unroll
                     for (int p = 0; p < P; ++p) {  // int4: the hi tile, then the lo tile, against the same x stage
                         const uint64_t db = db0 + (uint64_t)((sa * P + p) * (kBTileBytes >> 4));
@@ -526,7 +513,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     accumulate = 1;
                     ptx::umma_commit(ptx::smem_u32(&sb->empty[sa]));
                     if (++sa == NS) { sa = 0; pha ^= 1; }
-                    if (dbg) { long long c2 = clock64(); mT[0] += c1 - c0; mT[1] += c2 - c1; mT[2] += 1; }
                 }
                 if (ok)
                     for (uint32_t b = b0; b < b1; ++b) {
@@ -537,7 +523,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             // drain: every issued MMA must have completed before TMEM is released
             ptx::umma_commit(ptx::smem_u32(&sb->drain));
             (void)ptx::mbar_wait(ptx::smem_u32(&sb->drain), 0);
-            if (dbg) for (int i = 0; i < 3; ++i) a.status[24 + i] = (int)(mT[i] >> 4);
         }
         __syncwarp();
     } else if (warp >= kWarpEpi0 && warp < kWarpEpi0 + kEpiWarps) {
@@ -555,7 +540,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             if (ti.halves == 1) {
                 mine = (int)next1 == grp;
                 half = 0;
-                if (!(a.tune & 1)) next1 ^= 1u;
+                next1 ^= 1u;
             }
             if (!mine) continue;
             if (!__all_sync(0xffffffffu, gm_wait(&sb->t_full[grp], use & 1, sb, a.status, 60 + grp))) break;
@@ -784,7 +769,6 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
     a.y = static_cast<__nv_bfloat16*>(y);
     a.M = (int)M; a.K = (int)K; a.N = (int)N; a.G = (int)G;
     a.gl_type = group_list_type;
-    { static const int tune = [] { const char* e = getenv("B200MOE_TUNE"); return e ? atoi(e) : 0; }(); a.tune = tune; }
     a.status = static_cast<int*>(workspace);
 
     if (compute_type == B200MOE_CT_INT8) {
@@ -887,7 +871,6 @@ extern "C" int b200moe_grouped_gemm_int8_noalloc(const void* x, const void* weig
     a.y = static_cast<__nv_bfloat16*>(y);
     a.M = (int)M; a.K = (int)K; a.N = (int)N; a.G = (int)G;
     a.gl_type = group_list_type;
-    { static const int tune = [] { const char* e = getenv("B200MOE_TUNE"); return e ? atoi(e) : 0; }(); a.tune = tune; }
     a.status = static_cast<int*>(scratch);
     if (offset != nullptr) {
         float* rowsum = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + B200MOE_STATUS_BYTES);
