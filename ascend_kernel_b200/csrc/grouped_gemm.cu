@@ -675,19 +675,28 @@ __global__ void rowsum_kernel(const __nv_bfloat16* __restrict__ x, float* __rest
         if (v) atomicMax(&s_used, v);
     }
     __syncthreads();
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= M || row >= s_used) return;
-    const uint4* p = reinterpret_cast<const uint4*>(x + (size_t)row * K);
-    float s = 0.f;
-    for (int i = threadIdx.x & 31; i < K / 8; i += 32) {
-        const uint4 q = __ldg(p + i);
-        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    const int used = (int)(s_used < M ? s_used : M);
+    const int wpb = blockDim.x >> 5;
+    for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < used; row += gridDim.x * wpb) {
+        const uint4* p = reinterpret_cast<const uint4*>(x + (size_t)row * K);
+        float s = 0.f;
+        for (int i = threadIdx.x & 31; i < K / 8; i += 32) {
+            const uint4 q = __ldg(p + i);
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) s += __uint_as_float(w[j] << 16) + __uint_as_float(w[j] & 0xFFFF0000u);
+            for (int j = 0; j < 4; ++j) s += __uint_as_float(w[j] << 16) + __uint_as_float(w[j] & 0xFFFF0000u);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if ((threadIdx.x & 31) == 0) out[row] = s;
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if ((threadIdx.x & 31) == 0) out[row] = s;
+}
+
+// Grid of the row-sum kernel: one warp per row up to a few CTAs per multiprocessor, then a stride
+// (every CTA first reduces the group list, which should not be repeated thousands of times).
+static unsigned rowsum_blocks(int64_t M) {
+    const int64_t want = (M + 7) / 8, cap = 16LL * sm_count();
+    return (unsigned)(want < 1 ? 1 : (want < cap ? want : cap));
 }
 
 static size_t gm_smem_bytes(int G) {
@@ -775,7 +784,7 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
         float* rowsum = reinterpret_cast<float*>(ws);
         ws += align256((size_t)M * sizeof(float));
         if (offset != nullptr) {
-            rowsum_kernel<<<(unsigned)((M + 7) / 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rowsum, (int)M,
+            rowsum_kernel<<<rowsum_blocks(M), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rowsum, (int)M,
                                                                    (int)K, reinterpret_cast<const long long*>(group_list),
                                                                    (int)G, group_list_type);
             B200MOE_CUDA_TRY(cudaGetLastError());
@@ -874,7 +883,7 @@ extern "C" int b200moe_grouped_gemm_int8_noalloc(const void* x, const void* weig
     a.status = static_cast<int*>(scratch);
     if (offset != nullptr) {
         float* rowsum = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + B200MOE_STATUS_BYTES);
-        rowsum_kernel<<<(unsigned)((M + 7) / 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rowsum, (int)M, (int)K,
+        rowsum_kernel<<<rowsum_blocks(M), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rowsum, (int)M, (int)K,
                                                               reinterpret_cast<const long long*>(group_list), (int)G,
                                                               group_list_type);
         B200MOE_CUDA_TRY(cudaGetLastError());
