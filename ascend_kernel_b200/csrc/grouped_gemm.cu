@@ -661,7 +661,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 // last group are skipped (a caller may pass a buffer sized for the worst case as x).
 __global__ void rowsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int M, int K,
                               const long long* __restrict__ group_list, int G, int gl_type) {
-    __shared__ long long s_used;
+    // rows in use = end of the last group (clamped to M): a warp-level reduction, then one shared
+    // atomic per warp
+    __shared__ int s_used;
     if (threadIdx.x == 0) s_used = 0;
     __syncthreads();
     long long v = 0;
@@ -669,13 +671,18 @@ __global__ void rowsum_kernel(const __nv_bfloat16* __restrict__ x, float* __rest
         const long long c = group_list[g];
         if (gl_type == B200MOE_GROUP_LIST_COUNTS) v += c > 0 ? c : 0; else v = c > v ? c : v;
     }
-    if (gl_type == B200MOE_GROUP_LIST_COUNTS) {
-        if (v) atomicAdd(reinterpret_cast<unsigned long long*>(&s_used), (unsigned long long)v);
-    } else {
-        if (v) atomicMax(&s_used, v);
+    v = v > M ? M : v;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const long long other = __shfl_xor_sync(0xffffffffu, v, o);
+        if (gl_type == B200MOE_GROUP_LIST_COUNTS) v += other; else v = other > v ? other : v;
+    }
+    v = v > M ? M : v;
+    if ((threadIdx.x & 31) == 0 && v > 0) {
+        if (gl_type == B200MOE_GROUP_LIST_COUNTS) atomicAdd(&s_used, (int)v); else atomicMax(&s_used, (int)v);
     }
     __syncthreads();
-    const int used = (int)(s_used < M ? s_used : M);
+    const int used = (s_used < 0 || s_used > M) ? M : s_used;  // (a sum of eight clamped parts could wrap)
     const int wpb = blockDim.x >> 5;
     for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < used; row += gridDim.x * wpb) {
         const uint4* p = reinterpret_cast<const uint4*>(x + (size_t)row * K);
