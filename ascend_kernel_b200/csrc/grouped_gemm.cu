@@ -52,6 +52,11 @@ constexpr int kDqRows = kBK / (2 * kDqGroupWarps);  // k rows converted by a thr
 constexpr int kDqRowStep = 2;                        // distance between a thread's rows
 constexpr int kDqWarpRows = 2 * kDqRows;             // a warp owns this many consecutive k rows
 constexpr int kSuperRows = 8;  // m-tiles per L2 super-tile
+// Published tiles a role may lag behind the publisher: the publisher leads the x loads by kL2Ahead
+// stages, those lead the MMAs by the ring depth, the epilogue trails by at most two tiles; with one
+// stage per tile that is kL2Ahead + kNS + 2 tiles.
+constexpr int kTileRing = 32;
+constexpr int kBarrierBytes = 512;  // shared memory reserved for GmBarriers
 constexpr int kAHalfBytes = kBM * kBK * 2;   // one 128-row box
 constexpr int kATileBytes = 2 * kAHalfBytes;  // an x stage holds both row halves
 constexpr int kBTileBytes = kBK * kBN * 2;
@@ -80,6 +85,11 @@ struct GmBarriers {
     uint32_t tmem_base;
     int abort;
     int n_tiles;
+    int pad;
+    // Tile schedule of this CTA: tiles are drawn from a global ticket counter (status word 2) by the
+    // thread that runs furthest ahead and published here, entry i % kTileRing = (i + 1) << 32 | tile.
+    // Every role walks the entries in order, so all see the same sequence.
+    unsigned long long tile_ring[kTileRing];
 };
 
 struct TileInfo {
@@ -115,6 +125,33 @@ __device__ __forceinline__ bool gm_wait(uint64_t* bar, uint32_t parity, GmBarrie
 }
 
 // tile index -> expert, first row, row bound, first column.  tile_prefix has G+1 entries.
+// The seq-th tile of this CTA (seq counts from 0 and is advanced), or n_tiles when the schedule has
+// ended, a wait expired or another role aborted.  The publisher is always far ahead, so outside the
+// first microseconds of the kernel the entry is already there.
+__device__ __forceinline__ int next_tile(GmBarriers* sb, uint32_t& seq, int n_tiles, int* status) {
+    const volatile unsigned long long* e = &sb->tile_ring[seq % kTileRing];
+    const uint32_t want = seq + 1;
+    unsigned long long v = *e;
+    if ((uint32_t)(v >> 32) != want) {
+        volatile int* abort = &sb->abort;
+        const uint64_t t0 = ptx::globaltimer_ns();
+        uint32_t spins = 0;
+        while ((uint32_t)((v = *e) >> 32) != want) {
+            if ((++spins & 0xFF) == 0) {
+                if (*abort) return n_tiles;
+                if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
+                    *abort = 1;
+                    if (status != nullptr && atomicCAS(status, kDevOk, kDevWaitExpired) == kDevOk) status[1] = 90;
+                    return n_tiles;
+                }
+            }
+        }
+    }
+    ++seq;
+    const int t = (int)(uint32_t)v;
+    return t < n_tiles ? t : n_tiles;
+}
+
 __device__ __forceinline__ TileInfo locate_tile(int t, const int* tile_prefix, const int* row_start, int G, int n_nt) {
     int lo = 0, hi = G;  // largest g with tile_prefix[g] <= t
     while (hi - lo > 1) {
@@ -180,6 +217,7 @@ struct PackedRegs {
 // thread's first packed row of that stage carried along (advanced by a constant inside a tile).
 struct DqIter {
     int t, kt, g, n0;
+    uint32_t seq;  // tiles taken from the CTA's schedule so far
     bool valid;
     const uint8_t* wp;
 };
@@ -199,7 +237,7 @@ __device__ __forceinline__ void dq_locate(DqIter& it, const uint8_t* __restrict_
 template <int MODE>
 __device__ __forceinline__ void dq_advance(DqIter& it, int step, const uint8_t* __restrict__ w, const GemmArgs& a,
                                            const DqLane& d, int n_kt, int n_tiles, const int* tile_prefix,
-                                           const int* row_start, int n_nt) {
+                                           const int* row_start, int n_nt, GmBarriers* sb) {
     using T = GmTraits<MODE>;
     it.kt += step;
     if (it.kt < n_kt) {
@@ -208,8 +246,8 @@ __device__ __forceinline__ void dq_advance(DqIter& it, int step, const uint8_t* 
     }
     do {
         it.kt -= n_kt;
-        it.t += gridDim.x;
-    } while (it.kt >= n_kt);
+        it.t = next_tile(sb, it.seq, n_tiles, a.status);
+    } while (it.kt >= n_kt && it.t < n_tiles);
     dq_locate<MODE>(it, w, a, d, n_tiles, tile_prefix, row_start, n_nt);
 }
 
@@ -391,7 +429,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     constexpr int NS = T::kStages, P = T::kParts;
     uint8_t* b_ring = a_ring + NS * kATileBytes;
     GmBarriers* sb = reinterpret_cast<GmBarriers*>(b_ring + NS * P * kBTileBytes);
-    int* row_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sb) + 256);
+    static_assert(sizeof(GmBarriers) <= kBarrierBytes, "barrier block");
+    int* row_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sb) + kBarrierBytes);
     int* tile_prefix = row_start + (a.G + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -408,6 +447,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
         sb->n_tiles = acc;
         sb->abort = 0;
+        for (int i = 0; i < kTileRing; ++i) sb->tile_ring[i] = 0ull;
         for (int i = 0; i < NS; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->full[i]), 1 + kDqGroupWarps); ptx::mbar_init(ptx::smem_u32(&sb->empty[i]), 1); }
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(ptx::smem_u32(&sb->t_full[i]), 1);
@@ -435,15 +475,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         // prefetch has no shared-memory destination), so the dequant warps' register loads, which
         // can only run a stage or two ahead, find their data in L2 instead of waiting on HBM.
         if (lane == 0) {
-            uint32_t ia = 0;
+            uint32_t ia = 0, seq = 0, published = 0;
             bool ok = true;
+            // This thread runs furthest ahead (its L2 prefetch leads everything else), so it draws the
+            // tiles.  One ticket is always held in hand, so the atomic's latency is off the path.
+            int* ticket = a.status + 2;  // zeroed by the host before the launch
+            int held = atomicAdd(ticket, 1);
+            auto publish = [&]() -> int {
+                const int t = held < n_tiles ? held : n_tiles;
+                *reinterpret_cast<volatile unsigned long long*>(&sb->tile_ring[published % kTileRing]) =
+                    ((unsigned long long)(published + 1) << 32) | (uint32_t)t;
+                ++published;
+                if (t < n_tiles) held = atomicAdd(ticket, 1);
+                return t;
+            };
             StageIter far;
-            iter_start(far, n_tiles, tile_prefix, row_start, a.G, n_nt);
-            for (int i = 0; i < kL2Ahead && far.valid; ++i) {
+            far.t = publish();
+            far.kt = 0;
+            far.valid = far.t < n_tiles;
+            if (far.valid) far.ti = locate_tile(far.t, tile_prefix, row_start, a.G, n_nt);
+            auto far_step = [&]() {
                 ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0, far.ti.g * a.K + far.kt * kBK);
-                iter_next(far, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
-            }
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                if (++far.kt < n_kt) return;
+                far.kt = 0;
+                far.t = publish();
+                far.valid = far.t < n_tiles;
+                if (far.valid) far.ti = locate_tile(far.t, tile_prefix, row_start, a.G, n_nt);
+            };
+            for (int i = 0; i < kL2Ahead && far.valid; ++i) far_step();
+            for (;;) {
+                const int t = next_tile(sb, seq, n_tiles, a.status);
+                if (t >= n_tiles || !ok) break;
                 const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
                 for (int kt = 0; kt < n_kt; ++kt, ++ia) {
                     const uint32_t s = ia % NS, ph = (ia / NS) & 1;
@@ -455,11 +517,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     if (ti.halves == 2)
                         ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes + kAHalfBytes), &tmap_x, bar, kx,
                                          ti.row0 + kBM);
-                    if (far.valid) {
-                        ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0,
-                                                far.ti.g * a.K + far.kt * kBK);
-                        iter_next(far, n_kt, n_tiles, tile_prefix, row_start, a.G, n_nt);
-                    }
+                    if (far.valid) far_step();
                 }
             }
             if (!ok)
@@ -480,7 +538,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             uint32_t sa = 0, pha = 0;
             uint32_t uses[2] = {0, 0}, next1 = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            uint32_t seq = 0;
+            for (;;) {
+                const int t = next_tile(sb, seq, n_tiles, a.status);
+                if (t >= n_tiles || !ok) break;
                 const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
                 // accumulators of this tile: both for two halves, else the one used less recently;
                 // the epilogue of their previous tile must have drained them
@@ -531,8 +592,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         const int grp = (warp - kWarpEpi0) >> 2;      // which accumulator this warp drains
         const bool per_channel = (MODE == B200MOE_CT_INT8);
         const bool has_offset = per_channel && a.offset != nullptr;
-        uint32_t use = 0, next1 = 0;
-        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        uint32_t use = 0, next1 = 0, seq = 0;
+        for (;;) {
+            const int t = next_tile(sb, seq, n_tiles, a.status);
+            if (t >= n_tiles) break;
             const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
             // a two-half tile: this group takes row half `grp`; a one-half tile sits in one accumulator
             bool mine = true;
@@ -599,30 +662,30 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         const int dq_tid = threadIdx.x - kWarpDq0 * 32;
         const int grp = dq_tid / (kDqGroupWarps * 32);
         const DqLane d = dq_lane(dq_tid % (kDqGroupWarps * 32));
-        const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-        const long long total = (long long)my_tiles * n_kt;  // stages of this CTA
-        const uint32_t units = total > grp ? (uint32_t)((total - grp + kDqGroups - 1) / kDqGroups) : 0u;
         DqIter pf;
-        pf.t = blockIdx.x;
+        pf.seq = 0;
+        pf.t = next_tile(sb, pf.seq, n_tiles, a.status);
         pf.kt = 0;
         dq_locate<MODE>(pf, weight, a, d, n_tiles, tile_prefix, row_start, n_nt);
-        if (grp > 0 && pf.valid) dq_advance<MODE>(pf, grp, weight, a, d, n_kt, n_tiles, tile_prefix, row_start, n_nt);
+        if (grp > 0 && pf.valid) dq_advance<MODE>(pf, grp, weight, a, d, n_kt, n_tiles, tile_prefix, row_start, n_nt, sb);
         DqIter cur = pf;  // int4 only: the stage being converted (its scales are loaded late)
         PackedRegs<MODE> regs[kPrefetch];
+        bool loaded[kPrefetch];
 #pragma unroll
         for (int u = 0; u < kPrefetch; ++u) {
+            loaded[u] = pf.valid;
             if (pf.valid) {
                 load_packed<MODE>(regs[u], pf, a, d);
-                dq_advance<MODE>(pf, kDqGroups, weight, a, d, n_kt, n_tiles, tile_prefix, row_start, n_nt);
+                dq_advance<MODE>(pf, kDqGroups, weight, a, d, n_kt, n_tiles, tile_prefix, row_start, n_nt, sb);
             }
         }
         const uint32_t sa0 = ptx::smem_u32(b_ring) + btile_offset(d.row, 2 * d.c16);
-        uint32_t ib = grp, n = 0;
+        uint32_t ib = grp;
         bool ok = true;
-        while (n < units && ok) {
+        while (ok) {
 #pragma unroll
             for (int u = 0; u < kPrefetch; ++u) {
-                if (n >= units) break;
+                if (!loaded[u]) { ok = false; break; }  // the schedule has ended
                 const uint32_t slot = ib % NS;
                 Int4Scales sc4;
                 if constexpr (MODE == B200MOE_CT_INT4) sc4 = load_int4_scales(a, cur.g, cur.n0, cur.kt, d);
@@ -637,14 +700,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->full[slot]));
+                loaded[u] = pf.valid;
                 if (pf.valid) {
                     load_packed<MODE>(regs[u], pf, a, d);
-                    dq_advance<MODE>(pf, kDqGroups, weight, a, d, n_kt, n_tiles, tile_prefix, row_start, n_nt);
+                    dq_advance<MODE>(pf, kDqGroups, weight, a, d, n_kt, n_tiles, tile_prefix, row_start, n_nt, sb);
                 }
                 if constexpr (MODE == B200MOE_CT_INT4)
-                    dq_advance<MODE>(cur, kDqGroups, weight, a, d, n_kt, n_tiles, tile_prefix, row_start, n_nt);
+                    dq_advance<MODE>(cur, kDqGroups, weight, a, d, n_kt, n_tiles, tile_prefix, row_start, n_nt, sb);
                 ib += kDqGroups;
-                ++n;
             }
         }
     }
@@ -707,7 +770,7 @@ static unsigned rowsum_blocks(int64_t M) {
 }
 
 static size_t gm_smem_bytes(int G) {
-    return 1024 + (size_t)kNS * (kATileBytes + kBTileBytes) + 256 + sizeof(int) * 2 * (size_t)(G + 1);
+    return 1024 + (size_t)kNS * (kATileBytes + kBTileBytes) + kBarrierBytes + sizeof(int) * 2 * (size_t)(G + 1);
 }
 
 template <int MODE>
