@@ -9,7 +9,7 @@
 // partial sums per column are combined with one shuffle and one pass through shared memory;
 // scale and offset are applied in the fp32 epilogue and the result is rounded to bf16 once.
 // Experts with more than 4 rows are processed 4 rows at a time (the weight slab is then re-read
-// from L2).
+// from L2).  int8 items with 2..4 rows use the tensor core for the multiply-adds (gv_compute_mma).
 #include "common.cuh"
 
 namespace b200moe {
@@ -21,6 +21,8 @@ constexpr int kGvUnroll = 8;                            // row pairs in flight p
 constexpr int kGvWarpRows = 2 * kGvUnroll;              // k rows a warp consumes per step
 constexpr int kGvIterRows = kGvWarps * kGvWarpRows;     // k rows a CTA consumes per step
 constexpr int kGvRows = 4;                              // x rows per pass
+constexpr int kGvXPad = 16;                             // bf16 elements between staged x rows (bank spread)
+constexpr int kGvMmaParts = 4;                          // k groups of the tensor-core path
 
 struct GemvArgs {
     const __nv_bfloat16* x;
@@ -170,7 +172,7 @@ __device__ __forceinline__ void gv_compute(const GemvArgs& a, const __nv_bfloat1
         uint32_t xw[MB][kGvUnroll];
 #pragma unroll
         for (int m = 0; m < MB; ++m) {
-            const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)m * a.K + k0);
+            const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)m * (a.K + kGvXPad) + k0);
             const uint4 x0 = xp[0], x1 = xp[1];
             xw[m][0] = x0.x; xw[m][1] = x0.y; xw[m][2] = x0.z; xw[m][3] = x0.w;
             xw[m][4] = x1.x; xw[m][5] = x1.y; xw[m][6] = x1.z; xw[m][7] = x1.w;
@@ -259,6 +261,108 @@ __device__ __forceinline__ void gv_compute(const GemvArgs& a, const __nv_bfloat1
     __syncthreads();
 }
 
+// ---- 2..4 rows per expert, int8: the multiply-adds go to the tensor core ---------------------
+// With more than one row the scalar path spends most of its issue slots on FMAs.  Here a warp
+// multiplies a 16 (k) x 128 (columns) block of weights with up to four x rows per step using eight
+// mma.sync m16n8k16 instructions, the weights as the 16 x 16 operand:
+//   lane (g, t) = (lane / 4, lane % 4) loads rows k0 + 4t .. 4t+3, columns 16g .. 16g+15 (each load
+//   instruction reads four full 128-byte lines) and feeds instruction j with columns 16g + 2j, +1:
+//   operand row g <-> column 16g + 2j, row g + 8 <-> column 16g + 2j + 1, and the instruction's
+//   k index {2t, 2t+1, 2t+8, 2t+9} <-> weight rows 4t .. 4t+3 (a summation index: any assignment
+//   works as long as the x operand uses the same one).  One byte permute per two rows and two
+//   columns puts (row, row + 1) pairs of a column side by side, then the exact int8 -> bf16
+//   conversion of common.cuh applies; x pairs come from shared memory with one 8-byte load per step.
+// The instruction count per weight byte no longer depends on the number of rows.
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void gv_compute_mma(const GemvArgs& a, const __nv_bfloat16* xs, const float* xsum, float* red,
+                                               int g_expert, int r0, int rows_valid, int n0) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int hc = warp & 1, kg = warp >> 1;  // column half of the slab, k group
+    const size_t row_bytes = (size_t)a.N;
+    const uint8_t* wbase = a.weight + (size_t)g_expert * a.K * row_bytes + n0 + 128 * hc + 16 * g + (size_t)(4 * t) * row_bytes;
+    // x pairs of token g at the lane's four k rows (tokens beyond the valid rows contribute zeros)
+    const __nv_bfloat16* xrow = xs + (size_t)(g < rows_valid ? g : 0) * (a.K + kGvXPad) + 4 * t;
+    const bool x_on = g < rows_valid;
+
+    float c[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) c[j][0] = c[j][1] = c[j][2] = c[j][3] = 0.f;
+
+    constexpr int kStepRows = 16 * kGvMmaParts;  // k rows the CTA consumes per step
+    for (int k0 = kg * 16; k0 < a.K; k0 += 2 * kStepRows) {
+        const bool second = k0 + kStepRows < a.K;
+        uint4 q[2][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (h == 1 && !second) break;
+            const uint8_t* p = wbase + (size_t)(k0 + h * kStepRows) * row_bytes;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) q[h][i] = ldg_stream(p + (size_t)i * row_bytes);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (h == 1 && !second) break;
+            uint2 xb = make_uint2(0u, 0u);
+            if (x_on) xb = *reinterpret_cast<const uint2*>(xrow + k0 + h * kStepRows);
+            const uint32_t r0w[4] = {q[h][0].x, q[h][0].y, q[h][0].z, q[h][0].w};
+            const uint32_t r1w[4] = {q[h][1].x, q[h][1].y, q[h][1].z, q[h][1].w};
+            const uint32_t r2w[4] = {q[h][2].x, q[h][2].y, q[h][2].z, q[h][2].w};
+            const uint32_t r3w[4] = {q[h][3].x, q[h][3].y, q[h][3].z, q[h][3].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                for (int o = 0; o < 2; ++o) {  // byte pairs (0,1) and (2,3) of word i: instruction j = 2i + o
+                    const uint32_t sel = o == 0 ? 0x5410u : 0x7632u;
+                    uint32_t a0, a1, a2, a3;
+                    s8x4_to_bf16_even_odd(prmt(r0w[i], r1w[i], sel), a0, a1);  // (row 4t, 4t+1) at the two columns
+                    s8x4_to_bf16_even_odd(prmt(r2w[i], r3w[i], sel), a2, a3);  // (row 4t+2, 4t+3)
+                    mma_16816(c[2 * i + o], a0, a1, a2, a3, xb.x, xb.y);
+                }
+            }
+        }
+    }
+
+    // ---- partial sums of the four k groups -> shared memory -> per-column epilogue ----------------
+    if (t < 2) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int col = 128 * hc + 16 * g + 2 * j;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {  // tokens 2t, 2t + 1
+                const int tok = 2 * t + e;
+                float* dst = red + (size_t)(kg * kGvRows + tok) * kGvSlabN + col;
+                *reinterpret_cast<float2*>(dst) = make_float2(c[j][e], c[j][2 + e]);
+            }
+        }
+    }
+    __syncthreads();
+    {
+        const int tc = threadIdx.x;  // column inside the slab
+        const int n = n0 + tc;
+        const float s_n = __bfloat162float(static_cast<const __nv_bfloat16*>(a.scale)[(size_t)g_expert * a.N + n]);
+        const float so_n = a.offset != nullptr ? s_n * __bfloat162float(a.offset[(size_t)g_expert * a.N + n]) : 0.f;
+#pragma unroll
+        for (int m = 0; m < kGvRows; ++m) {
+            if (m < rows_valid) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < kGvMmaParts; ++w) v += red[(w * kGvRows + m) * kGvSlabN + tc];
+                v = fmaf(so_n, xsum[m], s_n * v);
+                a.y[(size_t)(r0 + m) * a.N + n] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+    __syncthreads();
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -308,7 +412,7 @@ __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvA
             __syncthreads();
             for (int m = 0; m < rows; ++m) {
                 const uint4* src = reinterpret_cast<const uint4*>(a.x + (size_t)(r + m) * a.K);
-                uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)m * a.K);
+                uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)m * (a.K + kGvXPad));
                 float s = 0.f;
                 for (int i = threadIdx.x; i < kvec; i += kGvThreads) {
                     const uint4 v = __ldg(src + i);
@@ -327,6 +431,7 @@ __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvA
             }
             __syncthreads();
             if (rows == 1) gv_compute<MODE, 1>(a, xs, xsum, red, g, r, rows, n0);
+            else if constexpr (MODE == B200MOE_CT_INT8) gv_compute_mma(a, xs, xsum, red, g, r, rows, n0);
             else if (rows == 2) gv_compute<MODE, 2>(a, xs, xsum, red, g, r, rows, n0);
             else gv_compute<MODE, 4>(a, xs, xsum, red, g, r, rows, n0);
         }
@@ -336,7 +441,7 @@ __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvA
 static size_t gv_smem_bytes(int G, int K) {
     size_t b = sizeof(int) * (size_t)(2 * G + 2) + 16;
     b += sizeof(float) * (4 + kGvWarps * kGvRows * kGvSlabN);
-    b += (size_t)kGvRows * K * 2;
+    b += (size_t)kGvRows * (K + kGvXPad) * 2;
     return b;
 }
 

@@ -38,6 +38,8 @@ def _int8_case(counts, K, N, seed, with_offset):
     ([1, 0, 2, 4, 0, 3], 512, 512, True),
     ([0, 0, 5, 9, 1], 192, 768, True),       # more than 4 rows per expert, K not a multiple of 128
     ([2] * 40, 128, 256, False),             # more work items than resident CTAs per expert slab
+    ([3, 2, 4, 7], 64, 256, True),           # one k block only; 2..4 rows take the tensor-core path
+    ([2, 3, 4, 1, 8, 2], 7168, 512, True),   # benchmark K
 ])
 def test_int8_matches_oracle(counts, K, N, with_offset):
     x, w, scale, offset, cnt = _int8_case(counts, K, N, 7, with_offset)
