@@ -273,6 +273,12 @@ __device__ __forceinline__ void gv_compute(const GemvArgs& a, const __nv_bfloat1
 //   columns puts (row, row + 1) pairs of a column side by side, then the exact int8 -> bf16
 //   conversion of common.cuh applies; x pairs come from shared memory with one 8-byte load per step.
 // The instruction count per weight byte no longer depends on the number of rows.
+// Two e4m3 codes in the high bytes of the two 16-bit lanes (low bytes ignored) -> bf16x2, exact:
+// exponent and mantissa bits go under the bf16 exponent, times 2^120 (subnormals included).
+__device__ __forceinline__ uint32_t e4m3x2_hi_to_bf16(uint32_t t) {
+    return mul_bf16x2(((t >> 4) & 0x07F007F0u) | (t & 0x80008000u), 0x7B807B80u);
+}
+
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                           uint32_t b1) {
     asm volatile(
@@ -281,6 +287,10 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// fp8 (e4m3) follows the same scheme: the bytes of rows (k, k+1) of a column are permuted into the
+// high bytes of the two 16-bit lanes and decoded by bit placement (exact in bf16); the fp32 scale of
+// the 128 x 128 block, uniform for a warp over a 128-row stretch, multiplies the stretch's partial sums.
+template <int MODE>
 __device__ __forceinline__ void gv_compute_mma(const GemvArgs& a, const __nv_bfloat16* xs, const float* xsum, float* red,
                                                int g_expert, int r0, int rows_valid, int n0) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -295,10 +305,20 @@ __device__ __forceinline__ void gv_compute_mma(const GemvArgs& a, const __nv_bfl
     float c[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j) c[j][0] = c[j][1] = c[j][2] = c[j][3] = 0.f;
+    constexpr bool kBlockScale = (MODE == B200MOE_CT_FP8);
+    float ct[kBlockScale ? 8 : 1][4];  // fp8: totals; `c` then holds the current 128-row stretch
+    if constexpr (kBlockScale) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ct[j][0] = ct[j][1] = ct[j][2] = ct[j][3] = 0.f;
+    }
 
     constexpr int kStepRows = 16 * kGvMmaParts;  // k rows the CTA consumes per step
     for (int k0 = kg * 16; k0 < a.K; k0 += 2 * kStepRows) {
         const bool second = k0 + kStepRows < a.K;
+        float sf = 1.f;
+        if constexpr (kBlockScale)  // k0 and k0 + 64 lie in the same 128-row block (K % 128 == 0)
+            sf = __ldg(static_cast<const float*>(a.scale) + ((size_t)g_expert * (a.K >> 7) + (k0 >> 7)) * (a.N >> 7) +
+                       ((n0 + 128 * hc) >> 7));
         uint4 q[2][4];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -320,14 +340,38 @@ __device__ __forceinline__ void gv_compute_mma(const GemvArgs& a, const __nv_bfl
             for (int i = 0; i < 4; ++i) {
 #pragma unroll
                 for (int o = 0; o < 2; ++o) {  // byte pairs (0,1) and (2,3) of word i: instruction j = 2i + o
-                    const uint32_t sel = o == 0 ? 0x5410u : 0x7632u;
                     uint32_t a0, a1, a2, a3;
-                    s8x4_to_bf16_even_odd(prmt(r0w[i], r1w[i], sel), a0, a1);  // (row 4t, 4t+1) at the two columns
-                    s8x4_to_bf16_even_odd(prmt(r2w[i], r3w[i], sel), a2, a3);  // (row 4t+2, 4t+3)
+                    if constexpr (MODE == B200MOE_CT_INT8) {
+                        const uint32_t sel = o == 0 ? 0x5410u : 0x7632u;
+                        s8x4_to_bf16_even_odd(prmt(r0w[i], r1w[i], sel), a0, a1);  // (row 4t, 4t+1) at the two columns
+                        s8x4_to_bf16_even_odd(prmt(r2w[i], r3w[i], sel), a2, a3);  // (row 4t+2, 4t+3)
+                    } else {
+                        // byte b of both rows into the high bytes of the two lanes (the low bytes are masked off)
+                        const uint32_t s0 = o == 0 ? 0x4000u : 0x6020u, s1 = o == 0 ? 0x5010u : 0x7030u;
+                        a0 = e4m3x2_hi_to_bf16(prmt(r0w[i], r1w[i], s0));
+                        a1 = e4m3x2_hi_to_bf16(prmt(r0w[i], r1w[i], s1));
+                        a2 = e4m3x2_hi_to_bf16(prmt(r2w[i], r3w[i], s0));
+                        a3 = e4m3x2_hi_to_bf16(prmt(r2w[i], r3w[i], s1));
+                    }
                     mma_16816(c[2 * i + o], a0, a1, a2, a3, xb.x, xb.y);
                 }
             }
         }
+        if constexpr (kBlockScale) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    ct[j][e] = fmaf(sf, c[j][e], ct[j][e]);
+                    c[j][e] = 0.f;
+                }
+        }
+    }
+    if constexpr (kBlockScale) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) c[j][e] = ct[j][e];
     }
 
     // ---- partial sums of the four k groups -> shared memory -> per-column epilogue ----------------
@@ -347,15 +391,18 @@ __device__ __forceinline__ void gv_compute_mma(const GemvArgs& a, const __nv_bfl
     {
         const int tc = threadIdx.x;  // column inside the slab
         const int n = n0 + tc;
-        const float s_n = __bfloat162float(static_cast<const __nv_bfloat16*>(a.scale)[(size_t)g_expert * a.N + n]);
-        const float so_n = a.offset != nullptr ? s_n * __bfloat162float(a.offset[(size_t)g_expert * a.N + n]) : 0.f;
+        float s_n = 1.f, so_n = 0.f;
+        if constexpr (MODE == B200MOE_CT_INT8) {
+            s_n = __bfloat162float(static_cast<const __nv_bfloat16*>(a.scale)[(size_t)g_expert * a.N + n]);
+            if (a.offset != nullptr) so_n = s_n * __bfloat162float(a.offset[(size_t)g_expert * a.N + n]);
+        }
 #pragma unroll
         for (int m = 0; m < kGvRows; ++m) {
             if (m < rows_valid) {
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < kGvMmaParts; ++w) v += red[(w * kGvRows + m) * kGvSlabN + tc];
-                v = fmaf(so_n, xsum[m], s_n * v);
+                if constexpr (MODE == B200MOE_CT_INT8) v = fmaf(so_n, xsum[m], s_n * v);
                 a.y[(size_t)(r0 + m) * a.N + n] = __float2bfloat16_rn(v);
             }
         }
@@ -430,8 +477,11 @@ __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvA
                 }
             }
             __syncthreads();
-            if (rows == 1) gv_compute<MODE, 1>(a, xs, xsum, red, g, r, rows, n0);
-            else if constexpr (MODE == B200MOE_CT_INT8) gv_compute_mma(a, xs, xsum, red, g, r, rows, n0);
+            // fp8: the tensor-core path also wins with one row (its decode is two-wide); int8 with one
+            // row is faster on the scalar path
+            if constexpr (MODE == B200MOE_CT_FP8) gv_compute_mma<MODE>(a, xs, xsum, red, g, r, rows, n0);
+            else if (rows == 1) gv_compute<MODE, 1>(a, xs, xsum, red, g, r, rows, n0);
+            else if constexpr (MODE == B200MOE_CT_INT8) gv_compute_mma<MODE>(a, xs, xsum, red, g, r, rows, n0);
             else if (rows == 2) gv_compute<MODE, 2>(a, xs, xsum, red, g, r, rows, n0);
             else gv_compute<MODE, 4>(a, xs, xsum, red, g, r, rows, n0);
         }

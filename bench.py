@@ -282,6 +282,32 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
                                                  "shape": {"M": Mv, "K": K2, "N": N2, "G": G, "active_experts": n_act}}
         del w2, s2, x2, y2
         torch.cuda.empty_cache()
+        # the reference's own weight formats at the pass-1 shape (same routing): fp8 with fp32 block
+        # scales, fp4 (canonical layout) with bf16 scales per 16 k rows
+        K1, N1 = 7168, 4096
+        x1 = torch.randn(Mv, K1, generator=gen, device=dev).to(torch.bfloat16)
+        y1 = torch.empty(Mv, N1, dtype=torch.bfloat16, device=dev)
+        for kind in ("fp8", "fp4"):
+            cols = N1 if kind == "fp8" else N1 // 2
+            w1 = torch.empty(G, K1, cols, dtype=torch.uint8, device=dev)
+            for g in range(G):
+                w1[g] = torch.randint(0, 256, (K1, cols), generator=gen, device=dev, dtype=torch.uint8)
+            if kind == "fp8":
+                s1 = torch.randn(G, K1 // 128, N1 // 128, generator=gen, device=dev)
+                sbytes = n_act * (K1 // 128) * (N1 // 128) * 4
+            else:
+                s1 = (torch.rand(G, K1 // 16, N1, generator=gen, device=dev) * 3 + 0.25).to(torch.bfloat16)
+                w1 = w1.view(torch.int8)
+                sbytes = n_act * (K1 // 16) * N1 * 2
+            ms = time_launches(lambda: ak.grouped_soft_gemv(x1, w1, s1, counts, kind, y1, group_list_type=1,
+                                                            weight_layout="canonical"), 3, 10)
+            by = n_act * K1 * cols + sbytes + 2.0 * Mv * K1 + 2.0 * Mv * N1
+            out[f"grouped_gemv_decode_{kind}"] = {"ms": ms, "gbs": by / ms / 1e6,
+                                                  "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
+                                                  "shape": {"M": Mv, "K": K1, "N": N1, "G": G, "active_experts": n_act}}
+            del w1, s1
+            torch.cuda.empty_cache()
+        del x1, y1
     if "dequant" not in which:
         return out
     # ---- FP4 dequant (configuration 2) ----
