@@ -57,6 +57,7 @@ constexpr int kSuperRows = 8;  // m-tiles per L2 super-tile
 // stage per tile that is kL2Ahead + kNS + 2 tiles.
 constexpr int kTileRing = 32;
 constexpr int kBarrierBytes = 512;  // shared memory reserved for GmBarriers
+constexpr int kEpiScaleFloats = 2 * kBN;  // per epilogue warp: the tile's column scales and scale * offset
 constexpr int kAHalfBytes = kBM * kBK * 2;   // one 128-row box
 constexpr int kATileBytes = 2 * kAHalfBytes;  // an x stage holds both row halves
 constexpr int kBTileBytes = kBK * kBN * 2;
@@ -430,7 +431,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     uint8_t* b_ring = a_ring + NS * kATileBytes;
     GmBarriers* sb = reinterpret_cast<GmBarriers*>(b_ring + NS * P * kBTileBytes);
     static_assert(sizeof(GmBarriers) <= kBarrierBytes, "barrier block");
-    int* row_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sb) + kBarrierBytes);
+    float* epi_scale = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sb) + kBarrierBytes);
+    int* row_start = reinterpret_cast<int*>(epi_scale + kEpiWarps * kEpiScaleFloats);
     int* tile_prefix = row_start + (a.G + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -606,6 +608,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 next1 ^= 1u;
             }
             if (!mine) continue;
+            // int8: every thread needs the scale (and scale * offset) of all 256 columns of the tile; the
+            // warp stages them in its own shared-memory strip while the tile is still being accumulated
+            float* es = epi_scale + (warp - kWarpEpi0) * kEpiScaleFloats;
+            if (per_channel) {
+                const size_t c0 = (size_t)ti.g * a.N + ti.n0;
+#pragma unroll
+                for (int i = 0; i < kBN / 32; ++i) {
+                    const int col = i * 32 + lane;
+                    const float sv = __bfloat162float(static_cast<const __nv_bfloat16*>(a.scale)[c0 + col]);
+                    es[col] = sv;
+                    es[kBN + col] = has_offset ? sv * __bfloat162float(a.offset[c0 + col]) : 0.f;
+                }
+                __syncwarp();
+            }
             if (!__all_sync(0xffffffffu, gm_wait(&sb->t_full[grp], use & 1, sb, a.status, 60 + grp))) break;
             ++use;
             ptx::tc_fence_after();
@@ -618,29 +634,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 for (int c = 0; c < kBN / 32; ++c) {
                     uint32_t r[32];
                     ptx::tmem_ld_32x32(tmem_base + grp * kBN + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
-                    float sv = 1.f, sov = 0.f;
-                    if (per_channel) {
-                        const size_t ci = (size_t)ti.g * a.N + ti.n0 + c * 32 + lane;
-                        sv = __bfloat162float(static_cast<const __nv_bfloat16*>(a.scale)[ci]);
-                        if (has_offset) sov = sv * __bfloat162float(a.offset[ci]);
-                    }
                     ptx::tmem_ld_wait();
                     uint32_t o[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        // output columns 2j, 2j+1; the int8 dequant stores columns (0,2,1,3) of every
-                        // group of four, so column c sits at accumulator position pos(c)
-                        constexpr bool kPerm = (MODE == B200MOE_CT_INT8);
-                        const int p0 = kPerm ? ((2 * j) & ~3) + (((2 * j) & 3) == 2 ? 1 : 0) : 2 * j;
-                        const int p1 = kPerm ? ((2 * j) & ~3) + (((2 * j) & 3) == 2 ? 3 : 2) : 2 * j + 1;
-                        float v0 = __uint_as_float(r[p0]), v1 = __uint_as_float(r[p1]);
+                    for (int q = 0; q < 8; ++q) {  // output columns 4q .. 4q+3 of the chunk
+                        float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f), o4 = make_float4(0.f, 0.f, 0.f, 0.f);
                         if (per_channel) {
-                            const float s0 = __shfl_sync(0xffffffffu, sv, 2 * j), s1 = __shfl_sync(0xffffffffu, sv, 2 * j + 1);
-                            const float so0 = __shfl_sync(0xffffffffu, sov, 2 * j), so1 = __shfl_sync(0xffffffffu, sov, 2 * j + 1);
-                            v0 = fmaf(so0, rs, s0 * v0);
-                            v1 = fmaf(so1, rs, s1 * v1);
+                            s4 = *reinterpret_cast<const float4*>(es + c * 32 + 4 * q);
+                            o4 = *reinterpret_cast<const float4*>(es + kBN + c * 32 + 4 * q);
                         }
-                        o[j] = pack_bf16x2(v0, v1);
+                        // the int8 dequant stores columns (0,2,1,3) of every group of four, so output
+                        // column 4q + i sits at accumulator position 4q + (0,2,1,3)[i]
+                        constexpr bool kPerm = (MODE == B200MOE_CT_INT8);
+                        float v0 = __uint_as_float(r[4 * q]), v1 = __uint_as_float(r[4 * q + (kPerm ? 2 : 1)]);
+                        float v2 = __uint_as_float(r[4 * q + (kPerm ? 1 : 2)]), v3 = __uint_as_float(r[4 * q + 3]);
+                        if (per_channel) {
+                            v0 = fmaf(o4.x, rs, s4.x * v0);
+                            v1 = fmaf(o4.y, rs, s4.y * v1);
+                            v2 = fmaf(o4.z, rs, s4.z * v2);
+                            v3 = fmaf(o4.w, rs, s4.w * v3);
+                        }
+                        o[2 * q] = pack_bf16x2(v0, v1);
+                        o[2 * q + 1] = pack_bf16x2(v2, v3);
                     }
                     if (row_ok) {
                         uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
@@ -770,7 +785,8 @@ static unsigned rowsum_blocks(int64_t M) {
 }
 
 static size_t gm_smem_bytes(int G) {
-    return 1024 + (size_t)kNS * (kATileBytes + kBTileBytes) + kBarrierBytes + sizeof(int) * 2 * (size_t)(G + 1);
+    return 1024 + (size_t)kNS * (kATileBytes + kBTileBytes) + kBarrierBytes + sizeof(float) * kEpiWarps * kEpiScaleFloats +
+           sizeof(int) * 2 * (size_t)(G + 1);
 }
 
 template <int MODE>
