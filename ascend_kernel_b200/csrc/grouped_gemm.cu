@@ -419,7 +419,10 @@ __device__ __forceinline__ void iter_next(StageIter& it, int n_kt, int n_tiles, 
     if (it.valid) it.ti = locate_tile(it.t, tile_prefix, row_start, G, n_nt);
 }
 
-template <int MODE>
+// SILU (int8 only): the weight columns come as blocks of 128 gate columns followed by the 128 up
+// columns of the same indices, and the epilogue writes bf16(silu(gate) * up), [M, N/2], instead of
+// the [M, N] product (gate and up are rounded to bf16 first, as the unfused operators would).
+template <int MODE, bool SILU>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                     const uint8_t* __restrict__ weight, const GemmArgs a) {
@@ -629,6 +632,46 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 const int row = ti.row0 + half * kBM + quarter * 32 + lane;
                 const bool row_ok = row < ti.row_end;
                 const float rs = (has_offset && row_ok) ? __ldg(a.rowsum + row) : 0.f;
+                if constexpr (SILU) {
+                    __nv_bfloat16* arow = a.y + (size_t)row * (a.N >> 1) + (ti.n0 >> 1);
+                    const uint32_t acc = tmem_base + grp * kBN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+                    for (int c = 0; c < kBN / 32; ++c) {  // 16 activation columns per step
+                        uint32_t rg[16], ru[16];
+                        ptx::tmem_ld_32x16(acc + c * 16, rg);
+                        ptx::tmem_ld_32x16(acc + kBN / 2 + c * 16, ru);
+                        ptx::tmem_ld_wait();
+                        uint32_t o[8];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float4 sg = *reinterpret_cast<const float4*>(es + c * 16 + 4 * q);
+                            const float4 og = *reinterpret_cast<const float4*>(es + kBN + c * 16 + 4 * q);
+                            const float4 su = *reinterpret_cast<const float4*>(es + kBN / 2 + c * 16 + 4 * q);
+                            const float4 ou = *reinterpret_cast<const float4*>(es + kBN + kBN / 2 + c * 16 + 4 * q);
+                            // accumulator positions (0,2,1,3) of a group of four hold columns 0..3
+                            const uint32_t g01 = pack_bf16x2(fmaf(og.x, rs, sg.x * __uint_as_float(rg[4 * q])),
+                                                             fmaf(og.y, rs, sg.y * __uint_as_float(rg[4 * q + 2])));
+                            const uint32_t g23 = pack_bf16x2(fmaf(og.z, rs, sg.z * __uint_as_float(rg[4 * q + 1])),
+                                                             fmaf(og.w, rs, sg.w * __uint_as_float(rg[4 * q + 3])));
+                            const uint32_t u01 = pack_bf16x2(fmaf(ou.x, rs, su.x * __uint_as_float(ru[4 * q])),
+                                                             fmaf(ou.y, rs, su.y * __uint_as_float(ru[4 * q + 2])));
+                            const uint32_t u23 = pack_bf16x2(fmaf(ou.z, rs, su.z * __uint_as_float(ru[4 * q + 1])),
+                                                             fmaf(ou.w, rs, su.w * __uint_as_float(ru[4 * q + 3])));
+                            const uint32_t gw[2] = {g01, g23}, uw[2] = {u01, u23};
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                const float g0 = __uint_as_float(gw[i] << 16), g1 = __uint_as_float(gw[i] & 0xFFFF0000u);
+                                const float u0 = __uint_as_float(uw[i] << 16), u1 = __uint_as_float(uw[i] & 0xFFFF0000u);
+                                o[2 * q + i] = pack_bf16x2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+                            }
+                        }
+                        if (row_ok) {
+                            uint4* dst = reinterpret_cast<uint4*>(arow + c * 16);
+                            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                        }
+                    }
+                } else {
                 __nv_bfloat16* yrow = a.y + (size_t)row * a.N + ti.n0;
 #pragma unroll 1
                 for (int c = 0; c < kBN / 32; ++c) {
@@ -662,6 +705,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 #pragma unroll
                         for (int q = 0; q < 4; ++q) dst[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
                     }
+                }
                 }
             }
             ptx::tc_fence_before();
@@ -789,7 +833,7 @@ static size_t gm_smem_bytes(int G) {
            sizeof(int) * 2 * (size_t)(G + 1);
 }
 
-template <int MODE>
+template <int MODE, bool SILU = false>
 static int gm_launch(const void* x, const void* w, const GemmArgs& a, cudaStream_t stream) {
     using T = GmTraits<MODE>;
     CUtensorMap tx, tw;
@@ -798,9 +842,9 @@ static int gm_launch(const void* x, const void* w, const GemmArgs& a, cudaStream
     rc = make_tensor_map_2d(&tw, w, 1, (uint64_t)a.G * a.K, T::kNibbles ? a.N / 2 : a.N, kBK, T::kPRowBytes, false);
     if (rc != B200MOE_OK) return rc;
     const size_t smem = gm_smem_bytes(a.G);
-    B200MOE_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200MOE_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_kernel<MODE, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem));
-    grouped_gemm_kernel<MODE><<<sm_count(), kGemmThreads, smem, stream>>>(tx, tw, static_cast<const uint8_t*>(w), a);
+    grouped_gemm_kernel<MODE, SILU><<<sm_count(), kGemmThreads, smem, stream>>>(tx, tw, static_cast<const uint8_t*>(w), a);
     B200MOE_CUDA_TRY(cudaGetLastError());
     return B200MOE_OK;
 }
@@ -896,6 +940,45 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
     }
     if (use_pair_kernel()) return launch_grouped_gemm_pair(B200MOE_CT_FP4, x, w, a, s);
     return gm_launch<B200MOE_CT_FP4>(x, w, a, s);
+}
+
+extern "C" int b200moe_grouped_gemm_int8_silu(const void* x, const void* weight, const void* scale, const void* offset,
+                                              const int64_t* group_list, void* out, int64_t M, int64_t K, int64_t N,
+                                              int64_t G, int group_list_type, void* workspace, size_t workspace_bytes,
+                                              void* stream) {
+    if (group_list_type != B200MOE_GROUP_LIST_CUMSUM && group_list_type != B200MOE_GROUP_LIST_COUNTS)
+        return B200MOE_ERR_ARGUMENT;
+    if (M < 0 || K <= 0 || N <= 0 || G <= 0 || G > kMaxExperts || M > 0x7FFFFFF0LL || K > 0x7FFFFFF0LL ||
+        N > 0x7FFFFFF0LL || G * K > 0x7FFFFFF0LL)
+        return B200MOE_ERR_SHAPE;
+    if ((K % kBK) != 0 || (N % kBN) != 0) return B200MOE_ERR_SHAPE;
+    if (M == 0) return B200MOE_OK;
+    if (!x || !weight || !scale || !group_list || !out) return B200MOE_ERR_NULL_POINTER;
+    if (!aligned16(x) || !aligned16(weight) || !aligned16(scale) || !aligned16(out) || (offset && !aligned16(offset)))
+        return B200MOE_ERR_ALIGNMENT;
+    const size_t need = b200moe_grouped_gemm_workspace_bytes(M, K, N, G, B200MOE_CT_INT8, B200MOE_LAYOUT_CANONICAL);
+    if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return B200MOE_ERR_WORKSPACE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    B200MOE_CUDA_TRY(cudaMemsetAsync(workspace, 0, 16, s));
+    GemmArgs a;
+    a.scale = scale;
+    a.offset = nullptr;
+    a.rowsum = nullptr;
+    a.group_list = group_list;
+    a.y = static_cast<__nv_bfloat16*>(out);
+    a.M = (int)M; a.K = (int)K; a.N = (int)N; a.G = (int)G;
+    a.gl_type = group_list_type;
+    a.status = static_cast<int*>(workspace);
+    if (offset != nullptr) {
+        float* rowsum = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + B200MOE_STATUS_BYTES);
+        rowsum_kernel<<<rowsum_blocks(M), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rowsum, (int)M, (int)K,
+                                                       reinterpret_cast<const long long*>(group_list), (int)G,
+                                                       group_list_type);
+        B200MOE_CUDA_TRY(cudaGetLastError());
+        a.offset = static_cast<const __nv_bfloat16*>(offset);
+        a.rowsum = rowsum;
+    }
+    return gm_launch<B200MOE_CT_INT8, true>(x, weight, a, s);
 }
 
 // ---------------------------------------------------------------------------------------------

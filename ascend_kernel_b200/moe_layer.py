@@ -44,14 +44,17 @@ class CudaRowOps:
 
 class MoELayer:
     def __init__(self, w13, s13, o13, w2, s2, o2, n_experts: int, top_k: int, group=None, row_ops=CudaRowOps,
-                 exchange: str = "nccl", max_tokens: int = 0):
+                 exchange: str = "nccl", max_tokens: int = 0, fuse_silu: bool = None):
         """w13 int8 [E_local, H, 2I] (gate columns first), w2 int8 [E_local, I, H]; per-channel bf16
         scales/offsets [E_local, N].  ``group``: a torch.distributed process group or None.
         ``row_ops`` exists so the dispatch / regroup / combine index logic can be exercised by CPU
         ranks in the test-suite with stand-in row operations; the product always uses CudaRowOps.
         ``exchange``: "nccl" (all-to-all collectives) or "p2p" (this package's peer-memory kernels;
         needs ``max_tokens`` = the largest number of tokens a rank passes to forward, which sizes the
-        receive buffers for the worst case max_tokens x world x top_k rows)."""
+        receive buffers for the worst case max_tokens x world x top_k rows).
+        ``fuse_silu`` (default: on with the CUDA row operations): SiLU(gate) * up runs in the epilogue
+        of the first grouped GEMM; the layer then keeps w13 / s13 / o13 in the interleaved column
+        order that kernel takes (a one-time copy made here) instead of the tensors passed in."""
         self.ops = row_ops
         self.w13, self.s13, self.o13, self.w2, self.s2, self.o2 = w13, s13, o13, w2, s2, o2
         self.n_experts, self.top_k = n_experts, top_k
@@ -66,6 +69,11 @@ class MoELayer:
         assert self.e_local * self.world == n_experts
         self.hidden, self.inter = w13.shape[1], w2.shape[1]
         self.device = w13.device
+        self.fuse_silu = (row_ops is CudaRowOps) if fuse_silu is None else bool(fuse_silu)
+        if self.fuse_silu:
+            self.w13 = ops.interleave_gate_up(w13)
+            self.s13 = ops.interleave_gate_up(s13)
+            self.o13 = None if o13 is None else ops.interleave_gate_up(o13)
         self.px = None
         if exchange == "p2p":
             from .ep_exchange import PeerExchange
@@ -82,7 +90,6 @@ class MoELayer:
         """rows [R, H] expert-major with per-local-expert counts -> [R, H] (into ``y`` when given).
         ``n_rows``: int64 device tensor with the number of rows in use when R is only a capacity."""
         R = rows.shape[0]
-        h = torch.empty(R, 2 * self.inter, dtype=torch.bfloat16, device=self.device)
         if y is None:
             y = torch.empty(R, self.hidden, dtype=torch.bfloat16, device=self.device)
         if R == 0:
@@ -91,10 +98,17 @@ class MoELayer:
         self.timing = None
         if ev:
             ev[0].record()
-        self.ops.grouped_gemm(rows, self.w13, self.s13, self.o13, counts, "int8", h, group_list_type=1)
-        if ev:
-            ev[1].record()
-        act = self.ops.silu_mul(h) if n_rows is None else ops.silu_mul_dyn(h, n_rows)
+        if self.fuse_silu:
+            act = torch.empty(R, self.inter, dtype=torch.bfloat16, device=self.device)
+            ops.grouped_gemm_silu(rows, self.w13, self.s13, self.o13, counts, act, group_list_type=1)
+            if ev:
+                ev[1].record()
+        else:
+            h = torch.empty(R, 2 * self.inter, dtype=torch.bfloat16, device=self.device)
+            self.ops.grouped_gemm(rows, self.w13, self.s13, self.o13, counts, "int8", h, group_list_type=1)
+            if ev:
+                ev[1].record()
+            act = self.ops.silu_mul(h) if n_rows is None else ops.silu_mul_dyn(h, n_rows)
         if ev:
             ev[2].record()
         self.ops.grouped_gemm(act, self.w2, self.s2, self.o2, counts, "int8", y, group_list_type=1)

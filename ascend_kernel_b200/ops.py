@@ -105,6 +105,47 @@ def grouped_gemm(x, weight, antiquantScaleOptional, antiquantOffsetOptional, gro
     return ws if return_workspace else None
 
 
+def interleave_gate_up(t, block: int = 128):
+    """[..., 2I] with the gate columns first and the up columns after them -> the order
+    grouped_gemm_silu takes: blocks of `block` gate columns followed by the up columns of the same
+    indices.  Applies to the weight [G, K, 2I] and to its per-channel scale / offset [G, 2I]."""
+    two_i = t.shape[-1]
+    inter = two_i // 2
+    if two_i % (2 * block) != 0:
+        raise RuntimeError("2I must be a multiple of 256")
+    j = torch.arange(two_i, device=t.device)
+    b, r = j // (2 * block), j % (2 * block)
+    src = torch.where(r < block, b * block + r, inter + b * block + (r - block))
+    return t.index_select(t.dim() - 1, src).contiguous()
+
+
+def grouped_gemm_silu(x, weight, scale, offset, group_list, output, group_list_type: int = 0,
+                      return_workspace: bool = False):
+    """output [M, I] = bf16(silu(gate) * up) of the int8 gate/up projection; ``weight`` / ``scale`` /
+    ``offset`` in the interleaved column order of :func:`interleave_gate_up`."""
+    _need_cuda(x=x, weight=weight, scale=scale, offset=offset, group_list=group_list, output=output)
+    if x.dtype != torch.bfloat16 or output.dtype != torch.bfloat16 or group_list.dtype != torch.int64:
+        raise RuntimeError("x and output must be bfloat16, group_list int64")
+    if weight.dim() != 3 or weight.element_size() != 1:
+        raise RuntimeError("weight must be int8 [G, K, 2I]")
+    G, K, N = weight.shape
+    M = x.shape[0]
+    if x.shape[1] != K or tuple(output.shape) != (M, N // 2) or group_list.numel() != G:
+        raise RuntimeError(f"shape mismatch: x {tuple(x.shape)}, weight {tuple(weight.shape)}, output {tuple(output.shape)}")
+    _check_scale(scale, CT["int8"], G, K, N, "scale")
+    if offset is not None:
+        _check_scale(offset, CT["int8"], G, K, N, "offset")
+    need = _lib.b200moe_grouped_gemm_workspace_bytes(M, K, N, G, CT["int8"], LAYOUT["canonical"])
+    ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.b200moe_grouped_gemm_int8_silu(_ptr(x), _ptr(weight), _ptr(scale), _ptr(offset), _ptr(group_list),
+                                                 _ptr(output), M, K, N, G, group_list_type, _ptr(ws), need, _stream())
+    _abi.check(rc, "grouped_gemm_silu")
+    if M > 0:
+        _count(1 + (offset is not None))
+    return ws if return_workspace else None
+
+
 def grouped_soft_gemv(x, weight, scale, groupList, computeType, output, group_list_type: int = 0,
                       weight_layout: str = "ascend", offset=None, return_workspace: bool = False):
     ct = _compute_type(computeType)

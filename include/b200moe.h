@@ -83,6 +83,19 @@ int b200moe_grouped_gemm(const void* x, const void* weight, const void* scale, c
 size_t b200moe_grouped_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t G, int compute_type,
                                             int weight_layout);
 
+/* Gate / up projection of a gated FFN with SiLU(gate) * up fused into the epilogue (int8 weights;
+ * no reference counterpart: the reference ships the GEMM only and chitu applies the activation in a
+ * separate operator).  weight int8 [G, K, N] with N = 2 * I and the gate and up columns interleaved
+ * in blocks of 128: columns [256 b, 256 b + 128) are gate columns [128 b, 128 b + 128) and columns
+ * [256 b + 128, 256 b + 256) the up columns of the same indices; scale / offset [G, N] in the same
+ * order.  out bf16 [M, I]: out[m, j] = bf16(silu(g) * u) with g, u the bf16-rounded products
+ * b200moe_grouped_gemm would have written for gate column j and up column j, so the result equals
+ * b200moe_grouped_gemm followed by b200moe_silu_mul bit for bit.  Workspace as for
+ * b200moe_grouped_gemm with compute_type int8. */
+int b200moe_grouped_gemm_int8_silu(const void* x, const void* weight, const void* scale, const void* offset,
+                                   const int64_t* group_list, void* out, int64_t M, int64_t K, int64_t N, int64_t G,
+                                   int group_list_type, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Allocation-free int8 grouped GEMM.  (No counterpart in the reference: its host binding always
  * obtains a workspace with aclrtMalloc.)  For callers that must not allocate device memory -- a
  * plug-in running inside another framework's step whose allocator owns all device memory, or a

@@ -239,6 +239,48 @@ def test_graphed_layer_replays_match_eager_calls():
 
 
 @pytest.mark.gpu
+def test_fused_silu_gemm_equals_gemm_then_silu_bit_for_bit():
+    """b200moe_grouped_gemm_int8_silu on interleaved weights = b200moe_grouped_gemm + b200moe_silu_mul
+    on the plain ones, on ragged groups (empty expert, one row, more than one tile, rows of nobody)."""
+    import ascend_kernel_b200 as ak
+    from ascend_kernel_b200 import ops
+
+    gen = torch.Generator().manual_seed(5)
+    G, K, I = 5, 192, 384
+    counts = torch.tensor([3, 0, 300, 1, 129], dtype=torch.int64)
+    M = int(counts.sum()) + 2
+    x = torch.randn(M, K, generator=gen).to(torch.bfloat16).cuda()
+    w = torch.randint(-128, 128, (G, K, 2 * I), generator=gen, dtype=torch.int8).cuda()
+    s = (torch.rand(G, 2 * I, generator=gen) * 0.009 + 0.001).to(torch.bfloat16).cuda()
+    o = (torch.rand(G, 2 * I, generator=gen) * 8 - 4).to(torch.bfloat16).cuda()
+    for off in (o, None):
+        h = torch.zeros(M, 2 * I, dtype=torch.bfloat16, device="cuda")
+        ak.grouped_gemm(x, w, s, off, counts.cuda(), "int8", h, group_list_type=1)
+        want = ak.silu_mul(h)
+        got = torch.full((M, I), -768.0, dtype=torch.bfloat16, device="cuda")
+        ws = ops.grouped_gemm_silu(x, ops.interleave_gate_up(w), ops.interleave_gate_up(s),
+                                   None if off is None else ops.interleave_gate_up(off), counts.cuda(), got,
+                                   group_list_type=1, return_workspace=True)
+        torch.cuda.synchronize()
+        assert ak.read_status(ws) == (0, 0)
+        assert torch.equal(got[:M - 2].view(torch.int16), want[:M - 2].view(torch.int16))
+        assert bool((got[M - 2:] == -768.0).all())
+
+
+@pytest.mark.gpu
+def test_layer_with_and_without_fused_silu_agree_bit_for_bit():
+    from ascend_kernel_b200.moe_layer import MoELayer
+
+    c = small_case(T=200, H=256, E=8, I=256, k=2)
+    d = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
+    w = [d[k] for k in ("w13", "s13", "o13", "w2", "s2", "o2")]
+    a = MoELayer(*w, c["E"], c["top_k"], fuse_silu=True).forward(d["x"], d["logits"])
+    b = MoELayer(*w, c["E"], c["top_k"], fuse_silu=False).forward(d["x"], d["logits"])
+    torch.cuda.synchronize()
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+@pytest.mark.gpu
 def test_aux_kernels_match_torch():
     import ascend_kernel_b200 as ak
 
