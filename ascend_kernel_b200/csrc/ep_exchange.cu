@@ -183,7 +183,16 @@ ep_dispatch_kernel(EpComm c, const uint4* __restrict__ x, const int32_t* __restr
         }
         const uint4* src = x + (long long)token_of[i] * c.width16;
         uint4* dst = c.recv_x[d] + pos * c.width16;
-        for (int v = lane; v < c.width16; v += 32) dst[v] = __ldg(src + v);
+        // four loads in flight per lane, then four stores into the owner's memory
+        int v = lane;
+        for (; v + 96 < c.width16; v += 128) {
+            const uint4 q0 = __ldg(src + v), q1 = __ldg(src + v + 32), q2 = __ldg(src + v + 64), q3 = __ldg(src + v + 96);
+            dst[v] = q0;
+            dst[v + 32] = q1;
+            dst[v + 64] = q2;
+            dst[v + 96] = q3;
+        }
+        for (; v < c.width16; v += 32) dst[v] = __ldg(src + v);
     }
     // completion: the last CTA to finish signals every rank
     __threadfence_system();
@@ -213,15 +222,23 @@ __global__ void ep_combine_kernel(EpComm c, const int32_t* __restrict__ remote_p
     __syncthreads();
     for (int v = threadIdx.x; v < c.width16; v += blockDim.x) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int j = 0; j < top_k; ++j) {
-            if (s_row[j] == nullptr) continue;
-            const float w = s_w[j];
-            const uint4 q = s_row[j][v];
-            const uint32_t vw[4] = {q.x, q.y, q.z, q.w};
+        // the loads cross NVLink: eight are issued before the first is consumed
+        for (int j0 = 0; j0 < top_k; j0 += 8) {
+            uint4 q[8];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                acc[2 * k] = fmaf(w, __uint_as_float(vw[k] << 16), acc[2 * k]);
-                acc[2 * k + 1] = fmaf(w, __uint_as_float(vw[k] & 0xFFFF0000u), acc[2 * k + 1]);
+            for (int j = 0; j < 8; ++j) {
+                q[j] = make_uint4(0u, 0u, 0u, 0u);
+                if (j0 + j < top_k && s_row[j0 + j] != nullptr) q[j] = s_row[j0 + j][v];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float w = j0 + j < top_k ? s_w[j0 + j] : 0.f;
+                const uint32_t vw[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    acc[2 * k] = fmaf(w, __uint_as_float(vw[k] << 16), acc[2 * k]);
+                    acc[2 * k + 1] = fmaf(w, __uint_as_float(vw[k] & 0xFFFF0000u), acc[2 * k + 1]);
+                }
             }
         }
         out[t * c.width16 + v] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
