@@ -183,16 +183,7 @@ ep_dispatch_kernel(EpComm c, const uint4* __restrict__ x, const int32_t* __restr
         }
         const uint4* src = x + (long long)token_of[i] * c.width16;
         uint4* dst = c.recv_x[d] + pos * c.width16;
-        // four loads in flight per lane, then four stores into the owner's memory
-        int v = lane;
-        for (; v + 96 < c.width16; v += 128) {
-            const uint4 q0 = __ldg(src + v), q1 = __ldg(src + v + 32), q2 = __ldg(src + v + 64), q3 = __ldg(src + v + 96);
-            dst[v] = q0;
-            dst[v + 32] = q1;
-            dst[v + 64] = q2;
-            dst[v + 96] = q3;
-        }
-        for (; v < c.width16; v += 32) dst[v] = __ldg(src + v);
+        for (int v = lane; v < c.width16; v += 32) dst[v] = __ldg(src + v);
     }
     // completion: the last CTA to finish signals every rank
     __threadfence_system();
