@@ -61,6 +61,21 @@ def test_int8_matches_oracle(counts, K, N, with_offset):
     assert same_bits(out, out2)
 
 
+def test_largest_expert_count_and_all_empty_groups():
+    """1024 experts (the limit of the in-kernel schedule, and the largest shared-memory footprint) with
+    0..3 rows each; then a group list that gives every expert zero rows: nothing is written."""
+    gen = torch.Generator().manual_seed(23)
+    counts = torch.randint(0, 4, (1024,), generator=gen).tolist()
+    x, w, scale, offset, cnt = _int8_case(counts, 64, 256, 29, True)
+    gold = O.golden_f32(x, w, scale, offset, cnt, "int8", O.GROUP_LIST_COUNTS)
+    out, st = run_gemm(x, w, scale, offset, cnt, "int8", gl_type=1)
+    assert st == (0, 0)
+    assert_close_to_golden(out, gold)
+    out0, st0 = run_gemm(x, w, scale, offset, torch.zeros_like(cnt), "int8", gl_type=1)
+    assert st0 == (0, 0)
+    assert (out0.float() == SENTINEL).all()
+
+
 def test_rows_past_last_boundary_untouched():
     x, w, scale, offset, cnt = _int8_case([100, 30], 128, 256, 17, True, extra_rows=50)
     out, st = run_gemm(x, w, scale, offset, torch.cumsum(cnt, 0), "int8")
