@@ -63,9 +63,17 @@ constexpr int kATileBytes = 2 * kAHalfBytes;  // an x stage holds both row halve
 constexpr int kBTileBytes = kBK * kBN * 2;
 constexpr uint32_t kTmemCols = 512;
 
+// Internal kernel mode: fp4 weights in the stored ("ascend") order, read as they are.  In that order a
+// 64-row x 128-byte tile of the canonical matrix is still a 64 x 128-byte box of the same 2-D array
+// (row = (b*4 + a)*8 + p, 128 bytes = [q (4)][c8 (8)][4 bytes], for canonical row 16a + 8b + c8 and
+// byte column 128j + 16p + 4q + s), so tensor maps and strides are those of the canonical layout
+// and only the thread -> data assignment of the dequant warps changes: a thread takes 8 rows x 8
+// columns (two 16-byte loads) instead of 4 rows x 16 columns.
+constexpr int kCtFp4Ascend = 16;
+
 template <int MODE>
 struct GmTraits {
-    static constexpr bool kNibbles = (MODE == B200MOE_CT_FP4 || MODE == B200MOE_CT_INT4);
+    static constexpr bool kNibbles = (MODE == B200MOE_CT_FP4 || MODE == B200MOE_CT_INT4 || MODE == kCtFp4Ascend);
     // int4 with per-128-k scale/offset: (w + o) * s does not fit bf16, so every k block is fed to
     // the tensor core twice -- a stage carries two weight tiles, hi = bf16(v) and lo = bf16(v - hi),
     // multiplied with the same x block; the fp32 accumulator then holds x @ v to about 2^-16 relative.
@@ -196,13 +204,27 @@ __device__ __forceinline__ uint32_t btile_offset(int k, int nchunk16) {  // nchu
 struct DqLane {
     int row;  // the thread converts k = row + kDqRowStep * j, j < kDqRows, of its stages
     int c16;  // 16-column chunk 0..15
+    // stored-order fp4 only: the thread converts canonical rows k0 .. k0 + 7, columns 8 * chunk .. + 7
+    int k0, chunk, src_row, src_byte;  // where its 32 bytes start inside the 64 x 128-byte box
 };
+template <int MODE>
 __device__ __forceinline__ DqLane dq_lane(int tid) {
     const int w = tid >> 5, l = tid & 31;
-    const int p = l >> 3, q = l & 7, odd = q >> 2;
     DqLane d;
-    d.row = kDqWarpRows * w + odd;
-    d.c16 = 4 * (p ^ odd) + (q & 3);
+    if constexpr (MODE == kCtFp4Ascend) {
+        const int a = w >> 1, b = w & 1;      // warp <-> rows 16a + 8b .. + 7 (one 16-row scale group)
+        d.k0 = 16 * a + 8 * b;
+        d.chunk = l;                          // lane <-> 16-byte chunk of the bf16 tile row (8 columns)
+        d.src_row = (b * 4 + a) * 8 + (l >> 2);
+        d.src_byte = (l & 3) * 32;
+        d.row = d.src_row;                    // what dq_locate adds to the stage's first row
+        d.c16 = 0;
+    } else {
+        const int p = l >> 3, q = l & 7, odd = q >> 2;
+        d.row = kDqWarpRows * w + odd;
+        d.c16 = 4 * (p ^ odd) + (q & 3);
+        d.k0 = d.chunk = d.src_row = d.src_byte = 0;
+    }
     return d;
 }
 
@@ -233,7 +255,9 @@ __device__ __forceinline__ void dq_locate(DqIter& it, const uint8_t* __restrict_
     it.n0 = ti.n0;
     const size_t row_bytes = T::kNibbles ? (size_t)a.N / 2 : (size_t)a.N;
     it.wp = w + ((size_t)ti.g * a.K + (size_t)it.kt * kBK + d.row) * row_bytes +
-            (T::kNibbles ? (ti.n0 >> 1) + d.c16 * 8 : ti.n0 + d.c16 * 16);
+            (MODE == kCtFp4Ascend ? (ti.n0 >> 1) + d.src_byte
+             : T::kNibbles        ? (ti.n0 >> 1) + d.c16 * 8
+                                  : ti.n0 + d.c16 * 16);
 }
 template <int MODE>
 __device__ __forceinline__ void dq_advance(DqIter& it, int step, const uint8_t* __restrict__ w, const GemmArgs& a,
@@ -255,6 +279,16 @@ __device__ __forceinline__ void dq_advance(DqIter& it, int step, const uint8_t* 
 template <int MODE>
 __device__ __forceinline__ void load_packed(PackedRegs<MODE>& r, const DqIter& it, const GemmArgs& a, const DqLane& d) {
     using T = GmTraits<MODE>;
+    if constexpr (MODE == kCtFp4Ascend) {
+        // 32 consecutive bytes = rows c8 = 0..7 of the thread's 8 columns, 4 bytes each; one scale
+        // vector (8 columns of the rows' 16-row group)
+        r.q[0] = __ldg(reinterpret_cast<const uint4*>(it.wp));
+        r.q[1] = __ldg(reinterpret_cast<const uint4*>(it.wp + 16));
+        r.s[0] = __ldg(reinterpret_cast<const uint4*>(
+            static_cast<const __nv_bfloat16*>(a.scale) +
+            ((size_t)it.g * (a.K >> 4) + ((it.kt * kBK + d.k0) >> 4)) * a.N + it.n0 + d.chunk * 8));
+        return;
+    }
     const size_t row_bytes = T::kNibbles ? (size_t)a.N / 2 : (size_t)a.N;
 #pragma unroll
     for (int j = 0; j < kDqRows; ++j) {
@@ -288,6 +322,20 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t x, uint32_t y, ui
 // XOR with 2j (bits 5..6 of the address) and the row offset by j * 256 bytes.  The second chunk of
 // the pair is at the returned address ^ 16.
 __device__ __forceinline__ uint32_t dq_row_addr(uint32_t sa, int j) { return (sa ^ (uint32_t)(j << 5)) + (uint32_t)(j * 256); }
+
+// Stored-order fp4: eight rows of eight columns; `sa` is the shared address of the thread's chunk in
+// its first row (a multiple of 8, so row i flips the chunk's swizzle bits by i and adds i * 128).
+__device__ __forceinline__ void convert_stage_fp4_ascend(const PackedRegs<kCtFp4Ascend>& r, uint32_t sa) {
+    const uint4 sc = r.s[0];
+    const uint32_t w8[8] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w, r.q[1].x, r.q[1].y, r.q[1].z, r.q[1].w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        uint32_t v[4];
+        e2m1x8_to_bf16(w8[i], v);
+        sts128((sa ^ (uint32_t)(i << 4)) + (uint32_t)(i * 128), mul_bf16x2(v[0], sc.x), mul_bf16x2(v[1], sc.y),
+               mul_bf16x2(v[2], sc.z), mul_bf16x2(v[3], sc.w));
+    }
+}
 
 template <int MODE>
 __device__ __forceinline__ void convert_stage(const PackedRegs<MODE>& r, uint32_t sa) {
@@ -720,7 +768,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         // advances by a constant inside a tile, and shared addresses derived from one per-thread offset.
         const int dq_tid = threadIdx.x - kWarpDq0 * 32;
         const int grp = dq_tid / (kDqGroupWarps * 32);
-        const DqLane d = dq_lane(dq_tid % (kDqGroupWarps * 32));
+        const DqLane d = dq_lane<MODE>(dq_tid % (kDqGroupWarps * 32));
         DqIter pf;
         pf.seq = 0;
         pf.t = next_tile(sb, pf.seq, n_tiles, a.status);
@@ -738,7 +786,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 dq_advance<MODE>(pf, kDqGroups, weight, a, d, n_kt, n_tiles, tile_prefix, row_start, n_nt, sb);
             }
         }
-        const uint32_t sa0 = ptx::smem_u32(b_ring) + btile_offset(d.row, 2 * d.c16);
+        const uint32_t sa0 = ptx::smem_u32(b_ring) + (MODE == kCtFp4Ascend ? btile_offset(d.k0, d.chunk)
+                                                                            : btile_offset(d.row, 2 * d.c16));
         uint32_t ib = grp;
         bool ok = true;
         while (ok) {
@@ -754,6 +803,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 const uint32_t sa = sa0 + slot * (uint32_t)(P * kBTileBytes);
                 if constexpr (MODE == B200MOE_CT_INT4)
                     convert_block_int4(regs[u], sc4, sa, sa + kBTileBytes);
+                else if constexpr (MODE == kCtFp4Ascend)
+                    convert_stage_fp4_ascend(regs[u], sa);
                 else
                     convert_stage<MODE>(regs[u], sa);
                 ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core (async proxy)
@@ -870,7 +921,8 @@ extern "C" size_t b200moe_grouped_gemm_workspace_bytes(int64_t M, int64_t K, int
                                                        int weight_layout) {
     size_t b = B200MOE_STATUS_BYTES;
     if (compute_type == B200MOE_CT_INT8) b += align256((size_t)M * sizeof(float));
-    if (compute_type == B200MOE_CT_FP4 && weight_layout == B200MOE_LAYOUT_ASCEND)
+    // (only the CTA-pair variant still converts stored-order fp4 weights into a canonical copy)
+    if (compute_type == B200MOE_CT_FP4 && weight_layout == B200MOE_LAYOUT_ASCEND && use_pair_kernel())
         b += (size_t)G * (size_t)K * (size_t)(N / 2);
     return b;
 }
@@ -932,14 +984,18 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
         if (use_pair_kernel()) return launch_grouped_gemm_pair(B200MOE_CT_FP8, x, weight, a, s);
         return gm_launch<B200MOE_CT_FP8>(x, weight, a, s);
     }
-    const void* w = weight;
-    if (weight_layout == B200MOE_LAYOUT_ASCEND) {
-        int rc = b200moe_fp4_layout(weight, ws, G, K, N, 0, stream);
-        if (rc != B200MOE_OK) return rc;
-        w = ws;
+    if (use_pair_kernel()) {
+        const void* w = weight;
+        if (weight_layout == B200MOE_LAYOUT_ASCEND) {
+            int rc = b200moe_fp4_layout(weight, ws, G, K, N, 0, stream);
+            if (rc != B200MOE_OK) return rc;
+            w = ws;
+        }
+        return launch_grouped_gemm_pair(B200MOE_CT_FP4, x, w, a, s);
     }
-    if (use_pair_kernel()) return launch_grouped_gemm_pair(B200MOE_CT_FP4, x, w, a, s);
-    return gm_launch<B200MOE_CT_FP4>(x, w, a, s);
+    // the stored ("ascend") order is read in place by the dequant warps
+    if (weight_layout == B200MOE_LAYOUT_ASCEND) return gm_launch<kCtFp4Ascend>(x, weight, a, s);
+    return gm_launch<B200MOE_CT_FP4>(x, weight, a, s);
 }
 
 extern "C" int b200moe_grouped_gemm_int8_silu(const void* x, const void* weight, const void* scale, const void* offset,

@@ -251,9 +251,12 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
     del c, y, xv, yv
     torch.cuda.empty_cache()
     # ---- the other weight formats at the prefill shape (int4 = configuration 3 variant B; fp8 / fp4 = the
-    # reference's own formats, cumulative group_list, canonical fp4 layout) ----
+    # reference's own formats, cumulative group_list; fp4 in the canonical order and in the reference's
+    # stored order, which the kernel reads in place) ----
     if "gemm" in which:
-        for kind in ("int4", "fp8", "fp4"):
+        for name in ("int4", "fp8", "fp4", "fp4_stored_order"):
+            kind = "fp4" if name.startswith("fp4") else name
+            layout = "ascend" if name == "fp4_stored_order" else "canonical"
             c = (inputs.config3_variants(dev, kind) if not quick
                  else inputs.config3_variants(dev, kind, n_rows=8192, n_experts=32))
             M, K = c["x"].shape
@@ -261,10 +264,10 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
             gl = c["counts"] if kind == "int4" else torch.cumsum(c["counts"], 0)
             off = c["offset"] if kind == "int4" else torch.zeros(1, device=dev)
             fn = (lambda: ak.grouped_gemm(c["x"], c["weight"], c["scale"], off, gl, kind, y,
-                                          group_list_type=1 if kind == "int4" else 0, weight_layout="canonical"))
+                                          group_list_type=1 if kind == "int4" else 0, weight_layout=layout))
             ms = time_launches(fn, 2, 5)
             flops = 2.0 * M * K * N
-            out[f"grouped_gemm_prefill_{kind}"] = {"ms": ms, "tflops": flops / ms / 1e9,
+            out[f"grouped_gemm_prefill_{name}"] = {"ms": ms, "tflops": flops / ms / 1e9,
                                                    "frac_of_measured_sustained": flops / ms / 1e9 / peaks["bf16_tflops_sustained"]}
             del c, y
             torch.cuda.empty_cache()
