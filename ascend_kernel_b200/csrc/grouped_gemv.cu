@@ -33,6 +33,7 @@ struct GemvArgs {
     __nv_bfloat16* y;
     int M, K, N, G, gl_type;
     int* status;
+    int fp4_stored;  // fp4 weights in the reference's pre-shuffled order, read in place
 };
 
 typedef unsigned long long f32x2;  // two packed fp32 (sm_100 two-wide FP32 instructions)
@@ -410,6 +411,100 @@ __device__ __forceinline__ void gv_compute_mma(const GemvArgs& a, const __nv_bfl
     __syncthreads();
 }
 
+// ---- fp4 weights in the reference's stored (pre-shuffled) order, read in place -----------------
+// Canonical row 16a + 8b + c8 of 64-row block R, byte column 128j + 16p + 4q + s lives at
+//   ((((((2R + b) * 4 + a) * 8 + p) * J + j) * 4 + q) * 8 + c8) * 4 + s,        J = N / 256,
+// so 16 consecutive bytes are four consecutive rows of eight columns.  A lane therefore owns eight
+// columns of the 256-column slab (lane = 16-byte chunk of the output row) and, per step, the 16 rows
+// of one scale group: four 16-byte loads, one scale vector.  Same arithmetic as the canonical path
+// (fp32 dequantised weights, fp32 accumulation); no conversion pass over the weights.
+template <int MB>
+__device__ __forceinline__ void gv_compute_fp4_stored(const GemvArgs& a, const __nv_bfloat16* xs, float* red, int g,
+                                                      int r0, int rows_valid, int n0) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int J = a.N >> 8, j = n0 >> 8, p = lane >> 2, q = lane & 3;
+    const uint8_t* wbase = a.weight + (size_t)g * a.K * ((size_t)a.N >> 1) + (size_t)j * 128 + q * 32;
+    const size_t p_stride = (size_t)J * 128;  // bytes between consecutive (b, a, p) rows of the stored array
+    const int col0 = n0 + lane * 8;
+
+    f32x2 acc[MB][4];
+#pragma unroll
+    for (int m = 0; m < MB; ++m)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[m][c] = 0ull;
+
+    for (int k0 = warp * 16; k0 < a.K; k0 += kGvWarps * 16) {
+        const int R = k0 >> 6, aa = (k0 >> 4) & 3;
+        uint4 wq[4];  // [2b + h]: rows k0 + 8b + 4h .. + 3
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            const uint8_t* ptr = wbase + ((size_t)((2 * R + b) * 4 + aa) * 8 + p) * p_stride;
+            wq[2 * b] = ldg_stream(ptr);
+            wq[2 * b + 1] = ldg_stream(ptr + 16);
+        }
+        const uint4 s4 = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.scale) +
+                                                              ((size_t)g * (a.K >> 4) + (k0 >> 4)) * a.N + col0));
+        const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
+        f32x2 sc[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sc[c] = pack2(__uint_as_float(sw[c] << 16), __uint_as_float(sw[c] & 0xFFFF0000u));
+        uint32_t xw[MB][8];  // x of the 16 rows, two per word
+#pragma unroll
+        for (int m = 0; m < MB; ++m) {
+            const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)m * (a.K + kGvXPad) + k0);
+            const uint4 x0 = xp[0], x1 = xp[1];
+            xw[m][0] = x0.x; xw[m][1] = x0.y; xw[m][2] = x0.z; xw[m][3] = x0.w;
+            xw[m][4] = x1.x; xw[m][5] = x1.y; xw[m][6] = x1.z; xw[m][7] = x1.w;
+        }
+#pragma unroll
+        for (int piece = 0; piece < 4; ++piece) {
+            const uint32_t w4[4] = {wq[piece].x, wq[piece].y, wq[piece].z, wq[piece].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int row = 4 * piece + i;  // 8b + 4h + i within the step
+                uint32_t v[4];
+                e2m1x8_to_bf16(w4[i], v);
+                f32x2 wv[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    wv[c] = mul2(pack2(__uint_as_float(v[c] << 16), __uint_as_float(v[c] & 0xFFFF0000u)), sc[c]);
+#pragma unroll
+                for (int m = 0; m < MB; ++m) {
+                    const uint32_t xx = xw[m][row >> 1];
+                    const float xv = __uint_as_float((row & 1) ? (xx & 0xFFFF0000u) : (xx << 16));
+                    const f32x2 x2 = pack2(xv, xv);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[m][c] = fma2(x2, wv[c], acc[m][c]);
+                }
+            }
+        }
+    }
+    // partial sums of the eight warps -> shared memory -> one thread per column
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+        float v[8];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) unpack2(acc[m][c], v[2 * c], v[2 * c + 1]);
+        float4* dst = reinterpret_cast<float4*>(red + ((warp * kGvRows + m) * kGvSlabN) + lane * 8);
+        dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+        dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    __syncthreads();
+    {
+        const int t = threadIdx.x;
+#pragma unroll
+        for (int m = 0; m < MB; ++m) {
+            if (m < rows_valid) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < kGvWarps; ++w) v += red[(w * kGvRows + m) * kGvSlabN + t];
+                a.y[(size_t)(r0 + m) * a.N + n0 + t] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+    __syncthreads();
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -479,7 +574,11 @@ __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvA
             __syncthreads();
             // fp8: the tensor-core path also wins with one row (its decode is two-wide); int8 with one
             // row is faster on the scalar path
-            if constexpr (MODE == B200MOE_CT_FP8) gv_compute_mma<MODE>(a, xs, xsum, red, g, r, rows, n0);
+            if (MODE == B200MOE_CT_FP4 && a.fp4_stored) {
+                if (rows == 1) gv_compute_fp4_stored<1>(a, xs, red, g, r, rows, n0);
+                else if (rows == 2) gv_compute_fp4_stored<2>(a, xs, red, g, r, rows, n0);
+                else gv_compute_fp4_stored<4>(a, xs, red, g, r, rows, n0);
+            } else if constexpr (MODE == B200MOE_CT_FP8) gv_compute_mma<MODE>(a, xs, xsum, red, g, r, rows, n0);
             else if (rows == 1) gv_compute<MODE, 1>(a, xs, xsum, red, g, r, rows, n0);
             else if constexpr (MODE == B200MOE_CT_INT8) gv_compute_mma<MODE>(a, xs, xsum, red, g, r, rows, n0);
             else if (rows == 2) gv_compute<MODE, 2>(a, xs, xsum, red, g, r, rows, n0);
@@ -513,10 +612,8 @@ using namespace b200moe;
 
 extern "C" size_t b200moe_grouped_gemv_workspace_bytes(int64_t, int64_t K, int64_t N, int64_t G, int compute_type,
                                                        int weight_layout) {
-    size_t b = B200MOE_STATUS_BYTES;
-    if (compute_type == B200MOE_CT_FP4 && weight_layout == B200MOE_LAYOUT_ASCEND)
-        b += (size_t)G * (size_t)K * (size_t)(N / 2);  // canonical copy of the pre-shuffled weights
-    return b;
+    (void)K; (void)N; (void)G; (void)compute_type; (void)weight_layout;
+    return B200MOE_STATUS_BYTES;  // status words and the work-item ticket; no mode needs more
 }
 
 extern "C" int b200moe_grouped_gemv(const void* x, const void* weight, const void* scale, const void* offset,
@@ -555,12 +652,8 @@ extern "C" int b200moe_grouped_gemv(const void* x, const void* weight, const voi
     a.gl_type = group_list_type;
     a.status = static_cast<int*>(workspace);
 
-    if (compute_type == B200MOE_CT_FP4 && weight_layout == B200MOE_LAYOUT_ASCEND) {
-        void* canon = static_cast<uint8_t*>(workspace) + B200MOE_STATUS_BYTES;
-        int rc = b200moe_fp4_layout(weight, canon, G, K, N, 0, stream);
-        if (rc != B200MOE_OK) return rc;
-        a.weight = static_cast<const uint8_t*>(canon);
-    }
+    // fp4 in the stored (pre-shuffled) order is read in place
+    a.fp4_stored = (compute_type == B200MOE_CT_FP4 && weight_layout == B200MOE_LAYOUT_ASCEND) ? 1 : 0;
     switch (compute_type) {
         case B200MOE_CT_INT8: return gv_launch<B200MOE_CT_INT8>(a, s);
         case B200MOE_CT_FP8: return gv_launch<B200MOE_CT_FP8>(a, s);

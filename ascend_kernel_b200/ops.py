@@ -100,8 +100,8 @@ def grouped_gemm(x, weight, antiquantScaleOptional, antiquantOffsetOptional, gro
     ws = _run(_lib.b200moe_grouped_gemm, _lib.b200moe_grouped_gemm_workspace_bytes, "grouped_gemm", x, weight,
               antiquantScaleOptional, offset, groupListOptional, output, ct, group_list_type,
               LAYOUT[weight_layout], M, K, N, G)
-    if M > 0:  # GEMM + row sums for the int8 offset term + layout conversion of pre-shuffled fp4 weights
-        _count(1 + (offset is not None and ct == CT["int8"]) + (ct == CT["fp4"] and weight_layout == "ascend"))
+    if M > 0:  # GEMM + row sums for the int8 offset term (pre-shuffled fp4 weights are read in place)
+        _count(1 + (offset is not None and ct == CT["int8"]))
     return ws if return_workspace else None
 
 
@@ -159,7 +159,7 @@ def grouped_soft_gemv(x, weight, scale, groupList, computeType, output, group_li
     ws = _run(_lib.b200moe_grouped_gemv, _lib.b200moe_grouped_gemv_workspace_bytes, "grouped_soft_gemv", x, weight,
               scale, offset, groupList, output, ct, group_list_type, LAYOUT[weight_layout], M, K, N, G)
     if M > 0:
-        _count(1 + (ct == CT["fp4"] and weight_layout == "ascend"))
+        _count(1)
     return ws if return_workspace else None
 
 

@@ -290,7 +290,8 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
         K1, N1 = 7168, 4096
         x1 = torch.randn(Mv, K1, generator=gen, device=dev).to(torch.bfloat16)
         y1 = torch.empty(Mv, N1, dtype=torch.bfloat16, device=dev)
-        for kind in ("fp8", "fp4"):
+        for name in ("fp8", "fp4", "fp4_stored_order"):
+            kind = "fp4" if name.startswith("fp4") else name
             cols = N1 if kind == "fp8" else N1 // 2
             w1 = torch.empty(G, K1, cols, dtype=torch.uint8, device=dev)
             for g in range(G):
@@ -302,10 +303,11 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
                 s1 = (torch.rand(G, K1 // 16, N1, generator=gen, device=dev) * 3 + 0.25).to(torch.bfloat16)
                 w1 = w1.view(torch.int8)
                 sbytes = n_act * (K1 // 16) * N1 * 2
+            layout = "ascend" if name == "fp4_stored_order" else "canonical"
             ms = time_launches(lambda: ak.grouped_soft_gemv(x1, w1, s1, counts, kind, y1, group_list_type=1,
-                                                            weight_layout="canonical"), 3, 10)
+                                                            weight_layout=layout), 3, 10)
             by = n_act * K1 * cols + sbytes + 2.0 * Mv * K1 + 2.0 * Mv * N1
-            out[f"grouped_gemv_decode_{kind}"] = {"ms": ms, "gbs": by / ms / 1e6,
+            out[f"grouped_gemv_decode_{name}"] = {"ms": ms, "gbs": by / ms / 1e6,
                                                   "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
                                                   "shape": {"M": Mv, "K": K1, "N": N1, "G": G, "active_experts": n_act}}
             del w1, s1

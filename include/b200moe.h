@@ -59,7 +59,9 @@ enum {
 };
 
 enum { B200MOE_GROUP_LIST_CUMSUM = 0, B200MOE_GROUP_LIST_COUNTS = 1 };
-enum { B200MOE_LAYOUT_CANONICAL = 0, B200MOE_LAYOUT_ASCEND = 1 }; /* fp4 weights only */
+/* fp4 weights only: CANONICAL = [G,K,N/2], low nibble = even column; ASCEND = the reference's
+ * pre-shuffled stored order (b200moe_fp4_layout converts).  Both kernels read either in place. */
+enum { B200MOE_LAYOUT_CANONICAL = 0, B200MOE_LAYOUT_ASCEND = 1 };
 enum { B200MOE_FP4_SCALE_NONE = 0, B200MOE_FP4_SCALE_E8M0_PER32 = 1 };
 
 /* Device-side status words live in the first 16 bytes of every workspace:
