@@ -81,5 +81,7 @@ def test_workspace_sizes():
     abi = _lib()
     assert abi.lib.b200moe_grouped_gemm_workspace_bytes(1000, 256, 512, 4, 2, 0) == 256 + 4096
     assert abi.lib.b200moe_grouped_gemm_workspace_bytes(1000, 256, 512, 4, 0, 0) == 256
-    assert abi.lib.b200moe_grouped_gemm_workspace_bytes(8, 256, 512, 4, 1, 1) == 256 + 4 * 256 * 256
+    # pre-shuffled fp4 weights are read in place: no canonical copy in the workspace
+    assert abi.lib.b200moe_grouped_gemm_workspace_bytes(8, 256, 512, 4, 1, 1) == 256
     assert abi.lib.b200moe_grouped_gemv_workspace_bytes(8, 256, 512, 4, 2, 0) == 256
+    assert abi.lib.b200moe_grouped_gemv_workspace_bytes(8, 256, 512, 4, 1, 1) == 256
