@@ -444,28 +444,12 @@ __device__ __forceinline__ void convert_block_int4(const PackedRegs<B200MOE_CT_I
     }
 }
 
-// Walks the (tile, k-stage) sequence of this CTA; the dequant warps run two of these, one for
-// the stage being converted and one kPrefetch stages ahead for the loads.
+// Position of the x producer's L2 prefetch in the (tile, k-stage) sequence of its CTA.
 struct StageIter {
     int t, kt;
     TileInfo ti;
     bool valid;
 };
-__device__ __forceinline__ void iter_start(StageIter& it, int n_tiles, const int* tile_prefix, const int* row_start,
-                                           int G, int n_nt) {
-    it.t = blockIdx.x;
-    it.kt = 0;
-    it.valid = it.t < n_tiles;
-    if (it.valid) it.ti = locate_tile(it.t, tile_prefix, row_start, G, n_nt);
-}
-__device__ __forceinline__ void iter_next(StageIter& it, int n_kt, int n_tiles, const int* tile_prefix,
-                                          const int* row_start, int G, int n_nt) {
-    if (++it.kt < n_kt) return;
-    it.kt = 0;
-    it.t += gridDim.x;
-    it.valid = it.t < n_tiles;
-    if (it.valid) it.ti = locate_tile(it.t, tile_prefix, row_start, G, n_nt);
-}
 
 // SILU (int8 only): the weight columns come as blocks of 128 gate columns followed by the 128 up
 // columns of the same indices, and the epilogue writes bf16(silu(gate) * up), [M, N/2], instead of
