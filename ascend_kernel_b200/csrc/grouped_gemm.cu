@@ -161,30 +161,44 @@ __device__ __forceinline__ int next_tile(GmBarriers* sb, uint32_t& seq, int n_ti
     return t < n_tiles ? t : n_tiles;
 }
 
+// Tile numbering: first every tile with two row halves (more than 128 rows), expert by expert in
+// super-tiles, then every tile with one row half (the last, short m-tile of an expert).  tile_prefix
+// holds two prefix arrays of G + 1 entries each: two-half tiles before expert g, one-half tiles
+// before expert g.
 __device__ __forceinline__ TileInfo locate_tile(int t, const int* tile_prefix, const int* row_start, int G, int n_nt) {
-    int lo = 0, hi = G;  // largest g with tile_prefix[g] <= t
+    const int n_two = tile_prefix[G];
+    const bool two = t < n_two;
+    const int* pref = two ? tile_prefix : tile_prefix + (G + 1);
+    const int tt = two ? t : t - n_two;
+    int lo = 0, hi = G;  // largest g with pref[g] <= tt
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
-        if (tile_prefix[mid] <= t) lo = mid;
+        if (pref[mid] <= tt) lo = mid;
         else hi = mid;
     }
     const int g = lo;
-    const int j = t - tile_prefix[g];
+    const int j = tt - pref[g];
     const int r0 = row_start[g], r1 = row_start[g + 1];
-    const int mt = (r1 - r0 + kTileM - 1) / kTileM;
-    // super-tiles of up to kSuperRows m-tiles x all n-tiles keep x rows and the expert's weights
-    // L2-resident while they are shared by concurrently running CTAs
-    const int per_super = kSuperRows * n_nt;
-    const int st = j / per_super;
-    const int base = st * kSuperRows;
-    const int h = min(kSuperRows, mt - base);
-    const int jj = j - st * per_super;
     TileInfo ti;
     ti.g = g;
-    ti.n0 = (jj / h) * kBN;
-    ti.row0 = r0 + (base + jj % h) * kTileM;
     ti.row_end = r1;
-    ti.halves = (r1 - ti.row0) > kBM ? 2 : 1;
+    if (two) {
+        const int mt = (pref[g + 1] - pref[g]) / n_nt;
+        // super-tiles of up to kSuperRows m-tiles x all n-tiles keep x rows and the expert's weights
+        // L2-resident while they are shared by concurrently running CTAs
+        const int per_super = kSuperRows * n_nt;
+        const int st = j / per_super;
+        const int base = st * kSuperRows;
+        const int h = min(kSuperRows, mt - base);
+        const int jj = j - st * per_super;
+        ti.n0 = (jj / h) * kBN;
+        ti.row0 = r0 + (base + jj % h) * kTileM;
+        ti.halves = 2;
+    } else {
+        ti.n0 = j * kBN;
+        ti.row0 = r0 + ((r1 - r0) / kTileM) * kTileM;
+        ti.halves = 1;
+    }
     return ti;
 }
 
@@ -476,12 +490,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
     load_row_starts(a.group_list, a.G, a.M, a.gl_type, row_start, a.status);
     if (threadIdx.x == 0) {
-        int acc = 0;
+        int acc = 0, acc1 = 0;
+        int* pref1 = tile_prefix + (a.G + 1);
         tile_prefix[0] = 0;
+        pref1[0] = 0;
         for (int g = 0; g < a.G; ++g) {
-            acc += ((row_start[g + 1] - row_start[g] + kTileM - 1) / kTileM) * n_nt;
+            const int rows = row_start[g + 1] - row_start[g], tail = rows % kTileM;
+            acc += (rows / kTileM + (tail > kBM ? 1 : 0)) * n_nt;    // tiles with two row halves
+            acc1 += ((tail >= 1 && tail <= kBM) ? 1 : 0) * n_nt;      // the short last m-tile, if any
             tile_prefix[g + 1] = acc;
+            pref1[g + 1] = acc1;
         }
+        acc += acc1;
         sb->n_tiles = acc;
         sb->abort = 0;
         for (int i = 0; i < kTileRing; ++i) sb->tile_ring[i] = 0ull;
@@ -865,7 +885,7 @@ static unsigned rowsum_blocks(int64_t M) {
 
 static size_t gm_smem_bytes(int G) {
     return 1024 + (size_t)kNS * (kATileBytes + kBTileBytes) + kBarrierBytes + sizeof(float) * kEpiWarps * kEpiScaleFloats +
-           sizeof(int) * 2 * (size_t)(G + 1);
+           sizeof(int) * 3 * (size_t)(G + 1);
 }
 
 template <int MODE, bool SILU = false>
