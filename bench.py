@@ -149,13 +149,27 @@ def cpu_moe_sample(every: int, prepared=None):
     return tok_s, t_total, rows_total, desc
 
 
+def use_all_host_cores():
+    """Give torch's CPU kernels every core this process may run on, and return the count.  A launcher
+    that starts one process per GPU sets OMP_NUM_THREADS=1 for its children, which would leave the
+    CPU arm with a single thread."""
+    import torch
+
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    torch.set_num_threads(max(1, cores))
+    return torch.get_num_threads()
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     import torch
 
-    threads = torch.get_num_threads()
+    threads = use_all_host_cores()
     every = 32
     prepared = cpu_sample_inputs(every)
     for _ in range(args.warmup):
@@ -483,6 +497,7 @@ def run_ours(args):
             line["kernels"]["peaks"] = {**peaks, "kind": peak_kind}
         if not args.no_cpu:
             # a bounded sample: 32 of the 256 experts, passes repeated until about ten seconds are timed
+            use_all_host_cores()
             prepared = cpu_sample_inputs(8)
             cpu_moe_sample(8, prepared)  # warm-up (thread pool, allocator)
             rows_sum, secs, passes = 0, 0.0, 0
