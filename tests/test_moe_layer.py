@@ -197,11 +197,19 @@ def test_host_pipeline_matches_single_calls():
     want = [layer.forward_host(x, lg).clone() for x, lg in zip(xs, lgs)]
     pipe = HostPipeline(layer, depth=2)
     outs = [torch.empty(c["x"].shape, dtype=torch.bfloat16).pin_memory() for _ in range(5)]
-    for x, lg, o in zip(xs, lgs, outs):
-        pipe.submit(x, lg, o)
+    handles = [pipe.submit(x, lg, o) for x, lg, o in zip(xs, lgs, outs)]
+    # a result is in its host buffer once its handle has been waited for: the first because the next
+    # submit enqueued its copy, the last because the wait itself does
+    handles[0].synchronize()
+    assert torch.equal(outs[0].view(torch.int16), want[0].view(torch.int16))
+    assert handles[-1].event is None
+    handles[-1].synchronize()
+    assert torch.equal(outs[-1].view(torch.int16), want[-1].view(torch.int16))
     pipe.drain()
     for o, w in zip(outs, want):
         assert torch.equal(o.view(torch.int16), w.view(torch.int16))
+    with pytest.raises(ValueError):
+        HostPipeline(layer, depth=1)
 
 
 @pytest.mark.gpu
