@@ -14,7 +14,7 @@ scaling): each of the N ranks holds 4096/N tokens and 256/N experts.
 Rank 0 prints ONE JSON line.  `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is
 the same metric through the public host-buffer call (`HostPipeline.submit`: pinned host -> device
 copies of every step's inputs and the device -> host read of every step's result inside the timed
-region, two steps in flight so that the copies of neighbouring steps overlap the kernels;
+region, two steps in flight so that the copies of neighbouring steps overlap the expert GEMMs;
 `single_step_latency_ms` is the unpipelined `MoELayer.forward_host`); `roofline` covers the
 dominant kernel of the step (the tcgen05 grouped GEMM, both launches); `kernels` (N=1 only) holds
 the three hot-path kernels at their own benchmark configurations (prefill grouped GEMM, decode
