@@ -10,13 +10,14 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(*args):
+def _run(*args, env=None):
     return subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), *args], capture_output=True, text=True,
-                          timeout=900, cwd=ROOT)
+                          timeout=900, cwd=ROOT, env=env)
 
 
 def test_reference_arm_prints_one_json_line_with_the_contract_keys():
-    r = _run("--impl", "reference", "--steps", "1", "--warmup", "0")
+    # a one-process-per-GPU launcher hands its children OMP_NUM_THREADS=1; the arm must still use the host's cores
+    r = _run("--impl", "reference", "--steps", "1", "--warmup", "0", env={**os.environ, "OMP_NUM_THREADS": "1"})
     assert r.returncode == 0, r.stderr[-2000:]
     lines = [l for l in r.stdout.splitlines() if l.strip().startswith("{")]
     assert len(lines) == 1
@@ -26,7 +27,7 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
                 "data", "config", "cpu_baseline", "e2e"):
         assert key in d, key
     assert d["value"] > 0 and d["config"]["workload"].startswith("moe_ffn_layer")
-    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
 
 
