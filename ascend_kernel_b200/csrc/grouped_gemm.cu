@@ -60,6 +60,8 @@ constexpr int kBarrierBytes = 512;  // shared memory reserved for GmBarriers
 constexpr int kEpiScaleFloats = 2 * kBN;  // per epilogue warp: the tile's column scales and scale * offset
 constexpr int kAHalfBytes = kBM * kBK * 2;   // one 128-row box
 constexpr int kATileBytes = 2 * kAHalfBytes;  // an x stage holds both row halves
+constexpr int kSmallRows = 32;                 // rows of the small x box (a nearly empty last row half)
+constexpr int kSmallBytes = kSmallRows * kBK * 2;
 constexpr int kBTileBytes = kBK * kBN * 2;
 constexpr uint32_t kTmemCols = 512;
 
@@ -470,8 +472,8 @@ struct StageIter {
 // the [M, N] product (gate and up are rounded to bf16 first, as the unfused operators would).
 template <int MODE, bool SILU>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                    const uint8_t* __restrict__ weight, const GemmArgs a) {
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_xs,
+                    const __grid_constant__ CUtensorMap tmap_w, const uint8_t* __restrict__ weight, const GemmArgs a) {
     using T = GmTraits<MODE>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -513,6 +515,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         ptx::mbar_init(ptx::smem_u32(&sb->drain), 1);
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_x);
+        ptx::prefetch_tensormap(&tmap_xs);
         ptx::prefetch_tensormap(&tmap_w);
     }
     if (warp == kWarpMma) {
@@ -564,16 +567,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 const int t = next_tile(sb, seq, n_tiles, a.status);
                 if (t >= n_tiles || !ok) break;
                 const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
+                // The last row half of a tile often holds only a few rows of the expert (a second half
+                // of a dozen rows when an expert has a little over 128): a box of kSmallRows rows then
+                // replaces the 128-row box.  The MMA still reads 128 rows; what the rows beyond the box
+                // hold is left over from earlier stages and lands in accumulator rows that are never
+                // stored.
+                const int last_rows = ti.row_end - (ti.row0 + (ti.halves - 1) * kBM);
+                const bool small_last = last_rows <= kSmallRows;
+                const uint32_t stage_bytes = (uint32_t)((ti.halves - 1) * kAHalfBytes + (small_last ? kSmallBytes : kAHalfBytes));
+                const CUtensorMap* last_map = small_last ? &tmap_xs : &tmap_x;
                 for (int kt = 0; kt < n_kt; ++kt, ++ia) {
                     const uint32_t s = ia % NS, ph = (ia / NS) & 1;
                     if (ia >= NS && !gm_wait(&sb->empty[s], ph ^ 1, sb, a.status, 10 + (int)s)) { ok = false; break; }
                     const uint32_t bar = ptx::smem_u32(&sb->full[s]);
                     const int kx = kt * kBK;
-                    ptx::mbar_arrive_expect_tx(bar, ti.halves * kAHalfBytes);
-                    ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes), &tmap_x, bar, kx, ti.row0);
-                    if (ti.halves == 2)
-                        ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes + kAHalfBytes), &tmap_x, bar, kx,
+                    ptx::mbar_arrive_expect_tx(bar, stage_bytes);
+                    if (ti.halves == 2) {
+                        ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes), &tmap_x, bar, kx, ti.row0);
+                        ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes + kAHalfBytes), last_map, bar, kx,
                                          ti.row0 + kBM);
+                    } else {
+                        ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes), last_map, bar, kx, ti.row0);
+                    }
                     if (far.valid) far_step();
                 }
             }
@@ -891,15 +906,17 @@ static size_t gm_smem_bytes(int G) {
 template <int MODE, bool SILU = false>
 static int gm_launch(const void* x, const void* w, const GemmArgs& a, cudaStream_t stream) {
     using T = GmTraits<MODE>;
-    CUtensorMap tx, tw;
+    CUtensorMap tx, txs, tw;
     int rc = make_tensor_map_2d(&tx, x, 2, (uint64_t)a.M, a.K, kBM, kBK, true);
+    if (rc != B200MOE_OK) return rc;
+    rc = make_tensor_map_2d(&txs, x, 2, (uint64_t)a.M, a.K, kSmallRows, kBK, true);
     if (rc != B200MOE_OK) return rc;
     rc = make_tensor_map_2d(&tw, w, 1, (uint64_t)a.G * a.K, T::kNibbles ? a.N / 2 : a.N, kBK, T::kPRowBytes, false);
     if (rc != B200MOE_OK) return rc;
     const size_t smem = gm_smem_bytes(a.G);
     B200MOE_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_kernel<MODE, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem));
-    grouped_gemm_kernel<MODE, SILU><<<sm_count(), kGemmThreads, smem, stream>>>(tx, tw, static_cast<const uint8_t*>(w), a);
+    grouped_gemm_kernel<MODE, SILU><<<sm_count(), kGemmThreads, smem, stream>>>(tx, txs, tw, static_cast<const uint8_t*>(w), a);
     B200MOE_CUDA_TRY(cudaGetLastError());
     return B200MOE_OK;
 }
