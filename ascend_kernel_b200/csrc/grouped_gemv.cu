@@ -416,8 +416,9 @@ __device__ __forceinline__ void gv_compute_mma(const GemvArgs& a, const __nv_bfl
 //   ((((((2R + b) * 4 + a) * 8 + p) * J + j) * 4 + q) * 8 + c8) * 4 + s,        J = N / 256,
 // so 16 consecutive bytes are four consecutive rows of eight columns.  A lane therefore owns eight
 // columns of the 256-column slab (lane = 16-byte chunk of the output row) and, per step, the 16 rows
-// of one scale group: four 16-byte loads, one scale vector.  Same arithmetic as the canonical path
-// (fp32 dequantised weights, fp32 accumulation); no conversion pass over the weights.
+// of one scale group: four 16-byte loads, one scale vector.  fp32 throughout; the scale of a group
+// multiplies the fp32 sum of its 16 products (x * e2m1 is exact in fp32) instead of every weight.
+// No conversion pass over the weights.
 template <int MB>
 __device__ __forceinline__ void gv_compute_fp4_stored(const GemvArgs& a, const __nv_bfloat16* xs, float* red, int g,
                                                       int r0, int rows_valid, int n0) {
@@ -456,6 +457,12 @@ __device__ __forceinline__ void gv_compute_fp4_stored(const GemvArgs& a, const _
             xw[m][0] = x0.x; xw[m][1] = x0.y; xw[m][2] = x0.z; xw[m][3] = x0.w;
             xw[m][4] = x1.x; xw[m][5] = x1.y; xw[m][6] = x1.z; xw[m][7] = x1.w;
         }
+        // the 16 rows of the step share one scale per column: sum x * e2m1 first (fp32), scale once
+        f32x2 part[MB][4];
+#pragma unroll
+        for (int m = 0; m < MB; ++m)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) part[m][c] = 0ull;
 #pragma unroll
         for (int piece = 0; piece < 4; ++piece) {
             const uint32_t w4[4] = {wq[piece].x, wq[piece].y, wq[piece].z, wq[piece].w};
@@ -466,18 +473,21 @@ __device__ __forceinline__ void gv_compute_fp4_stored(const GemvArgs& a, const _
                 e2m1x8_to_bf16(w4[i], v);
                 f32x2 wv[4];
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    wv[c] = mul2(pack2(__uint_as_float(v[c] << 16), __uint_as_float(v[c] & 0xFFFF0000u)), sc[c]);
+                for (int c = 0; c < 4; ++c) wv[c] = pack2(__uint_as_float(v[c] << 16), __uint_as_float(v[c] & 0xFFFF0000u));
 #pragma unroll
                 for (int m = 0; m < MB; ++m) {
                     const uint32_t xx = xw[m][row >> 1];
                     const float xv = __uint_as_float((row & 1) ? (xx & 0xFFFF0000u) : (xx << 16));
                     const f32x2 x2 = pack2(xv, xv);
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) acc[m][c] = fma2(x2, wv[c], acc[m][c]);
+                    for (int c = 0; c < 4; ++c) part[m][c] = fma2(x2, wv[c], part[m][c]);
                 }
             }
         }
+#pragma unroll
+        for (int m = 0; m < MB; ++m)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[m][c] = fma2(part[m][c], sc[c], acc[m][c]);
     }
     // partial sums of the eight warps -> shared memory -> one thread per column
 #pragma unroll
