@@ -82,7 +82,7 @@ struct GvTraits {
 };
 
 // Decode the lane's 16 columns of one weight row into eight fp32 pairs.
-template <int MODE>
+template <int MODE, bool kScaleFp4 = true>
 __device__ __forceinline__ void gv_decode(const uint4& q, f32x2 (&w)[8], const f32x2 (&sc)[8], const f32x2 (&tc)[8]) {
     if constexpr (MODE == B200MOE_CT_INT8) {
         const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
@@ -131,7 +131,10 @@ __device__ __forceinline__ void gv_decode(const uint4& q, f32x2 (&w)[8], const f
             e2m1x8_to_bf16(w2[i], o);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-                w[4 * i + j] = mul2(pack2(__uint_as_float(o[j] << 16), __uint_as_float(o[j] & 0xFFFF0000u)), sc[4 * i + j]);
+                if constexpr (kScaleFp4)
+                    w[4 * i + j] = mul2(pack2(__uint_as_float(o[j] << 16), __uint_as_float(o[j] & 0xFFFF0000u)), sc[4 * i + j]);
+                else
+                    w[4 * i + j] = pack2(__uint_as_float(o[j] << 16), __uint_as_float(o[j] & 0xFFFF0000u));
         }
     }
 }
@@ -208,18 +211,37 @@ __device__ __forceinline__ void gv_compute(const GemvArgs& a, const __nv_bfloat1
                 tc[c] = mul2(pack2(__uint_as_float(ow[c] << 16), __uint_as_float(ow[c] & 0xFFFF0000u)), sc[c]);
             }
         }
+        // fp4 with one or two rows: the step's rows are one scale group, so the scale multiplies the fp32
+        // sum of the step's products (x * e2m1 is exact in fp32) instead of every weight
+        constexpr bool kGroupScale = (MODE == B200MOE_CT_FP4) && MB <= 2;
+        f32x2 part[kGroupScale ? MB : 1][8];
+        if constexpr (kGroupScale) {
+#pragma unroll
+            for (int m = 0; m < MB; ++m)
+#pragma unroll
+                for (int c = 0; c < 8; ++c) part[m][c] = 0ull;
+        }
 #pragma unroll
         for (int u = 0; u < kGvUnroll; ++u) {
             f32x2 w[8];
-            gv_decode<MODE>(q[u], w, sc, tc);
+            gv_decode<MODE, !kGroupScale>(q[u], w, sc, tc);
 #pragma unroll
             for (int m = 0; m < MB; ++m) {
                 float xv = __uint_as_float(half ? (xw[m][u] & 0xFFFF0000u) : (xw[m][u] << 16));
                 if constexpr (MODE == B200MOE_CT_FP8) xv *= sf;
                 const f32x2 xx = pack2(xv, xv);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) acc[m][c] = fma2(xx, w[c], acc[m][c]);
+                for (int c = 0; c < 8; ++c) {
+                    if constexpr (kGroupScale) part[m][c] = fma2(xx, w[c], part[m][c]);
+                    else acc[m][c] = fma2(xx, w[c], acc[m][c]);
+                }
             }
+        }
+        if constexpr (kGroupScale) {
+#pragma unroll
+            for (int m = 0; m < MB; ++m)
+#pragma unroll
+                for (int c = 0; c < 8; ++c) acc[m][c] = fma2(part[m][c], sc[c], acc[m][c]);
         }
     }
 
