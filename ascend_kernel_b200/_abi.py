@@ -25,7 +25,7 @@ EXPORTS = [
     "b200moe_gather_rows", "b200moe_combine", "b200moe_read_status", "b200moe_strerror", "b200moe_version",
     "b200moe_moe_route", "b200moe_moe_regroup_index", "b200moe_grouped_gemm_int8_noalloc", "b200moe_grouped_gemm_int8_noalloc_max_rows", "b200moe_noalloc_read_status",
     "b200moe_ep_post_counts", "b200moe_ep_dispatch", "b200moe_ep_wait", "b200moe_ep_post", "b200moe_ep_combine",
-    "b200moe_silu_mul_dyn", "b200moe_grouped_gemm_int8_silu", "b200moe_ipc_alloc", "b200moe_ipc_open", "b200moe_ipc_close", "b200moe_ipc_free",
+    "b200moe_silu_mul_dyn", "b200moe_grouped_gemm_int8_silu", "b200moe_pack_weight_int8", "b200moe_grouped_gemm_int8_packed", "b200moe_ipc_alloc", "b200moe_ipc_open", "b200moe_ipc_close", "b200moe_ipc_free",
 ]
 
 EP_MAX_WORLD = 8
@@ -65,6 +65,10 @@ def _load() -> ctypes.CDLL:
         f.restype = sz
     lib.b200moe_grouped_gemm_int8_silu.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, vp, sz, vp]
     lib.b200moe_grouped_gemm_int8_silu.restype = i32
+    lib.b200moe_pack_weight_int8.argtypes = [vp, vp, i64, i64, i64, i32, vp]
+    lib.b200moe_pack_weight_int8.restype = i32
+    lib.b200moe_grouped_gemm_int8_packed.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp, sz, vp]
+    lib.b200moe_grouped_gemm_int8_packed.restype = i32
     lib.b200moe_grouped_gemm_int8_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, vp]
     lib.b200moe_grouped_gemm_int8_noalloc.restype = i32
     lib.b200moe_grouped_gemm_int8_noalloc_max_rows.argtypes = []

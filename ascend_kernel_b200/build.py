@@ -21,7 +21,7 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libb200moe.so")
 EXT = os.path.join(HERE, "cinfer_ascendc" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
 
-CU_SOURCES = ["host_util.cu", "fp4_dequant.cu", "grouped_gemv.cu", "grouped_gemm.cu", "grouped_gemm_pair.cu", "moe_aux.cu",
+CU_SOURCES = ["host_util.cu", "fp4_dequant.cu", "grouped_gemv.cu", "grouped_gemm.cu", "grouped_gemm_packed.cu", "moe_aux.cu",
               "ep_exchange.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]

@@ -1,4 +1,4 @@
-// Arguments shared by the grouped-GEMM kernels and the launcher of the CTA-pair variant.
+// Arguments shared by the grouped-GEMM kernels.
 #pragma once
 
 #include "common.cuh"
@@ -15,7 +15,8 @@ struct GemmArgs {
     int* status;
 };
 
-// CTA-pair (cta_group::2) kernel, grouped_gemm_pair.cu.  mode is a B200MOE_CT_* value.
-int launch_grouped_gemm_pair(int mode, const void* x, const void* w, const GemmArgs& a, cudaStream_t stream);
+// out[m] = sum_k x[m, k] in fp32 for the rows the group list uses (grouped_gemm.cu).
+void launch_rowsum(const void* x, float* out, int64_t M, int64_t K, const int64_t* group_list, int64_t G, int gl_type,
+                   cudaStream_t stream);
 
 }  // namespace b200moe

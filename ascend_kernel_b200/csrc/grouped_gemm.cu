@@ -3,7 +3,7 @@
 //
 //   y[rows of expert g] = bf16( x[rows of expert g] @ dequant(W[g]) ),  fp32 accumulation in TMEM.
 //
-// One CTA per SM walks a static round-robin over output tiles of up to 256 rows x 256 columns:
+// One CTA per SM draws output tiles of up to 256 rows x 256 columns from a global ticket counter:
 // two UMMA 128x256x16 instructions (rows 0-127 and 128-255 of the tile, one TMEM accumulator of
 // 256 columns each) share every dequantised weight stage, so the CUDA-core dequant work per
 // tensor-core flop is half that of a 128-row tile; tiles with at most 128 rows issue one.  The
@@ -26,8 +26,6 @@
 // Weights never make a round trip through global memory.  Every wait is bounded; on expiry the
 // kernel records an error status, all roles wind down, copies in flight are given time to land
 // and TMEM is released.
-#include <cstdlib>
-#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -898,6 +896,12 @@ static unsigned rowsum_blocks(int64_t M) {
     return (unsigned)(want < 1 ? 1 : (want < cap ? want : cap));
 }
 
+void launch_rowsum(const void* x, float* out, int64_t M, int64_t K, const int64_t* group_list, int64_t G, int gl_type,
+                   cudaStream_t stream) {
+    rowsum_kernel<<<rowsum_blocks(M), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), out, (int)M, (int)K,
+                                                        reinterpret_cast<const long long*>(group_list), (int)G, gl_type);
+}
+
 static size_t gm_smem_bytes(int G) {
     return 1024 + (size_t)kNS * (kATileBytes + kBTileBytes) + kBarrierBytes + sizeof(float) * kEpiWarps * kEpiScaleFloats +
            sizeof(int) * 3 * (size_t)(G + 1);
@@ -923,17 +927,6 @@ static int gm_launch(const void* x, const void* w, const GemmArgs& a, cudaStream
 
 static size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
-// Kernel variant: the single-CTA kernel of this file (default; the faster one on B200 as measured)
-// or the CTA-pair (cta_group::2) kernel of grouped_gemm_pair.cu, selected with the environment
-// variable B200MOE_GEMM_KERNEL=pair (read once per process).
-static bool use_pair_kernel() {
-    static const bool pair = [] {
-        const char* e = getenv("B200MOE_GEMM_KERNEL");
-        return e != nullptr && strcmp(e, "pair") == 0;
-    }();
-    return pair;
-}
-
 }  // namespace b200moe
 
 using namespace b200moe;
@@ -942,9 +935,7 @@ extern "C" size_t b200moe_grouped_gemm_workspace_bytes(int64_t M, int64_t K, int
                                                        int weight_layout) {
     size_t b = B200MOE_STATUS_BYTES;
     if (compute_type == B200MOE_CT_INT8) b += align256((size_t)M * sizeof(float));
-    // (only the CTA-pair variant still converts stored-order fp4 weights into a canonical copy)
-    if (compute_type == B200MOE_CT_FP4 && weight_layout == B200MOE_LAYOUT_ASCEND && use_pair_kernel())
-        b += (size_t)G * (size_t)K * (size_t)(N / 2);
+    (void)K; (void)N; (void)G; (void)weight_layout;  // stored-order fp4 weights are read in place
     return b;
 }
 
@@ -994,7 +985,6 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
             a.offset = static_cast<const __nv_bfloat16*>(offset);
             a.rowsum = rowsum;
         }
-        if (use_pair_kernel()) return launch_grouped_gemm_pair(B200MOE_CT_INT8, x, weight, a, s);
         return gm_launch<B200MOE_CT_INT8>(x, weight, a, s);
     }
     if (compute_type == B200MOE_CT_INT4) {
@@ -1002,17 +992,7 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
         return gm_launch<B200MOE_CT_INT4>(x, weight, a, s);
     }
     if (compute_type == B200MOE_CT_FP8) {
-        if (use_pair_kernel()) return launch_grouped_gemm_pair(B200MOE_CT_FP8, x, weight, a, s);
         return gm_launch<B200MOE_CT_FP8>(x, weight, a, s);
-    }
-    if (use_pair_kernel()) {
-        const void* w = weight;
-        if (weight_layout == B200MOE_LAYOUT_ASCEND) {
-            int rc = b200moe_fp4_layout(weight, ws, G, K, N, 0, stream);
-            if (rc != B200MOE_OK) return rc;
-            w = ws;
-        }
-        return launch_grouped_gemm_pair(B200MOE_CT_FP4, x, w, a, s);
     }
     // the stored ("ascend") order is read in place by the dequant warps
     if (weight_layout == B200MOE_LAYOUT_ASCEND) return gm_launch<kCtFp4Ascend>(x, weight, a, s);

@@ -8,9 +8,9 @@ e // (E / world)).  Per step:
   gather rows into expert order                      b200moe_gather_rows
   all-to-all of per-expert counts, then of rows      NCCL (torch.distributed), world > 1 only
   regroup received rows expert-major                 b200moe_moe_regroup_index + b200moe_gather_rows, world > 1 only
-  grouped GEMM gate|up  [H -> 2I], int8 antiquant    b200moe_grouped_gemm  (tcgen05)
-  SiLU(gate) * up                                    b200moe_silu_mul
-  grouped GEMM down     [I -> H], int8 antiquant     b200moe_grouped_gemm
+  grouped GEMM gate|up  [H -> 2I], int8 antiquant,   b200moe_grouped_gemm_int8_packed  (tcgen05; weights
+  SiLU(gate) * up in its epilogue                    repacked once at construction)
+  grouped GEMM down     [I -> H], int8 antiquant     b200moe_grouped_gemm_int8_packed
   inverse regroup, all-to-all back                   world > 1 only
   weighted sum over each token's k results           b200moe_combine
 
@@ -44,7 +44,7 @@ class CudaRowOps:
 
 class MoELayer:
     def __init__(self, w13, s13, o13, w2, s2, o2, n_experts: int, top_k: int, group=None, row_ops=CudaRowOps,
-                 exchange: str = "nccl", max_tokens: int = 0, fuse_silu: bool = None):
+                 exchange: str = "nccl", max_tokens: int = 0, fuse_silu: bool = None, gemm: str = None):
         """w13 int8 [E_local, H, 2I] (gate columns first), w2 int8 [E_local, I, H]; per-channel bf16
         scales/offsets [E_local, N].  ``group``: a torch.distributed process group or None.
         ``row_ops`` exists so the dispatch / regroup / combine index logic can be exercised by CPU
@@ -54,7 +54,11 @@ class MoELayer:
         receive buffers for the worst case max_tokens x world x top_k rows).
         ``fuse_silu`` (default: on with the CUDA row operations): SiLU(gate) * up runs in the epilogue
         of the first grouped GEMM; the layer then keeps w13 / s13 / o13 in the interleaved column
-        order that kernel takes (a one-time copy made here) instead of the tensors passed in."""
+        order that kernel takes (a one-time copy made here) instead of the tensors passed in.
+        ``gemm``: "packed" (default with the CUDA row operations) repacks both weight tensors once
+        into the tile order of ``ops.grouped_gemm_packed`` and keeps only those copies -- the expert
+        GEMMs then dequantise straight into tensor memory and SiLU(gate) * up runs in the first
+        one's epilogue; "generic" calls the drop-in operator on the [G, K, N] tensors."""
         self.ops = row_ops
         self.w13, self.s13, self.o13, self.w2, self.s2, self.o2 = w13, s13, o13, w2, s2, o2
         self.n_experts, self.top_k = n_experts, top_k
@@ -70,7 +74,15 @@ class MoELayer:
         self.hidden, self.inter = w13.shape[1], w2.shape[1]
         self.device = w13.device
         self.fuse_silu = (row_ops is CudaRowOps) if fuse_silu is None else bool(fuse_silu)
-        if self.fuse_silu:
+        if gemm is None:
+            gemm = "packed" if (row_ops is CudaRowOps and self.fuse_silu) else "generic"
+        if gemm not in ("packed", "generic"):
+            raise ValueError("gemm must be 'packed' or 'generic'")
+        self.gemm = gemm
+        if gemm == "packed":
+            self.w13 = ops.pack_weight_int8(w13, gate_up=True)
+            self.w2 = ops.pack_weight_int8(w2, gate_up=False)
+        elif self.fuse_silu:
             self.w13 = ops.interleave_gate_up(w13)
             self.s13 = ops.interleave_gate_up(s13)
             self.o13 = None if o13 is None else ops.interleave_gate_up(o13)
@@ -105,6 +117,18 @@ class MoELayer:
         self.timing = None
         if ev:
             ev[0].record()
+        if self.gemm == "packed":
+            act = torch.empty(R, self.inter, dtype=torch.bfloat16, device=self.device)
+            ops.grouped_gemm_packed(rows, self.w13, self.s13, self.o13, counts, act, group_list_type=1,
+                                    gate_up_silu=True)
+            if ev:
+                ev[1].record()
+                ev[2].record()
+            ops.grouped_gemm_packed(act, self.w2, self.s2, self.o2, counts, y, group_list_type=1)
+            if ev:
+                ev[3].record()
+                self.timing = ev
+            return y
         if self.fuse_silu:
             act = torch.empty(R, self.inter, dtype=torch.bfloat16, device=self.device)
             ops.grouped_gemm_silu(rows, self.w13, self.s13, self.o13, counts, act, group_list_type=1)

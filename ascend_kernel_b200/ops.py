@@ -75,9 +75,13 @@ def _check_scale(scale, ct, G, K, N, what):
         raise RuntimeError(f"{what} must be {want[1]} of shape {want[0]}, got {scale.dtype} {tuple(scale.shape)}")
 
 
+def _workspace(need, device):
+    return torch.empty(need, dtype=torch.uint8, device=device)
+
+
 def _run(fn, ws_fn, what, x, weight, scale, offset, group_list, output, ct, group_list_type, layout, M, K, N, G):
     need = ws_fn(M, K, N, G, ct, layout)
-    ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+    ws = _workspace(need, x.device)
     with torch.cuda.device(x.device):
         rc = fn(_ptr(x), _ptr(weight), _ptr(scale), _ptr(offset), _ptr(group_list), _ptr(output), M, K, N, G, ct,
                 group_list_type, layout, _ptr(ws), need, _stream())
@@ -141,6 +145,50 @@ def grouped_gemm_silu(x, weight, scale, offset, group_list, output, group_list_t
         rc = _lib.b200moe_grouped_gemm_int8_silu(_ptr(x), _ptr(weight), _ptr(scale), _ptr(offset), _ptr(group_list),
                                                  _ptr(output), M, K, N, G, group_list_type, _ptr(ws), need, _stream())
     _abi.check(rc, "grouped_gemm_silu")
+    if M > 0:
+        _count(1 + (offset is not None))
+    return ws if return_workspace else None
+
+
+def pack_weight_int8(weight, gate_up: bool = False):
+    """int8 [G, K, N] -> the tile-packed order grouped_gemm_packed reads (same shape, opaque contents).
+    ``gate_up``: N = 2I with the gate columns first; tiles then pair gate and up columns."""
+    _need_cuda(weight=weight)
+    if weight.dim() != 3 or weight.element_size() != 1:
+        raise RuntimeError("weight must be int8 [G, K, N]")
+    G, K, N = weight.shape
+    out = torch.empty_like(weight)
+    with torch.cuda.device(weight.device):
+        rc = _lib.b200moe_pack_weight_int8(_ptr(weight), _ptr(out), G, K, N, int(bool(gate_up)), _stream())
+    _abi.check(rc, "pack_weight_int8")
+    _count(1)
+    return out
+
+
+def grouped_gemm_packed(x, packed, scale, offset, group_list, output, group_list_type: int = 0,
+                        gate_up_silu: bool = False, return_workspace: bool = False):
+    """int8 grouped GEMM on weights from :func:`pack_weight_int8`; ``scale`` / ``offset`` bf16 [G, N] in
+    the original column order.  ``gate_up_silu``: output [M, N/2] = bf16(silu(gate) * up)."""
+    _need_cuda(x=x, packed=packed, scale=scale, offset=offset, group_list=group_list, output=output)
+    if x.dtype != torch.bfloat16 or output.dtype != torch.bfloat16 or group_list.dtype != torch.int64:
+        raise RuntimeError("x and output must be bfloat16, group_list int64")
+    if packed.dim() != 3 or packed.element_size() != 1:
+        raise RuntimeError("packed must be the [G, K, N] tensor pack_weight_int8 returned")
+    G, K, N = packed.shape
+    M = x.shape[0]
+    n_out = N // 2 if gate_up_silu else N
+    if x.shape[1] != K or tuple(output.shape) != (M, n_out) or group_list.numel() != G:
+        raise RuntimeError(f"shape mismatch: x {tuple(x.shape)}, packed {tuple(packed.shape)}, output {tuple(output.shape)}")
+    _check_scale(scale, CT["int8"], G, K, N, "scale")
+    if offset is not None:
+        _check_scale(offset, CT["int8"], G, K, N, "offset")
+    need = _lib.b200moe_grouped_gemm_workspace_bytes(M, K, N, G, CT["int8"], LAYOUT["canonical"])
+    ws = _workspace(need, x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.b200moe_grouped_gemm_int8_packed(_ptr(x), _ptr(packed), _ptr(scale), _ptr(offset), _ptr(group_list),
+                                                   _ptr(output), M, K, N, G, group_list_type, int(bool(gate_up_silu)),
+                                                   _ptr(ws), need, _stream())
+    _abi.check(rc, "grouped_gemm_packed")
     if M > 0:
         _count(1 + (offset is not None))
     return ws if return_workspace else None

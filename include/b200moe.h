@@ -98,6 +98,27 @@ int b200moe_grouped_gemm_int8_silu(const void* x, const void* weight, const void
                                    const int64_t* group_list, void* out, int64_t M, int64_t K, int64_t N, int64_t G,
                                    int group_list_type, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Int8 grouped GEMM on weights repacked once into a tile order (no reference counterpart: the
+ * reference reads [G, K, N] on every call; a caller that keeps expert weights resident, like the MoE
+ * layer, repacks them at load time).  In the packed order every dequantised weight tile is written by
+ * the kernel straight into tensor memory as the MMA's A operand (lanes = weight columns), the token
+ * rows of an expert are the MMA's N extent (rounded up to 16, at most 160 per tile), and shared memory
+ * carries only the x tiles.
+ *   b200moe_pack_weight_int8: weight int8 [G, K, N] -> packed, G*K*N bytes, K % 64 == 0,
+ *     N % 256 == 0.  gate_up != 0: N = 2 * I with the gate columns first; a tile then pairs 128 gate
+ *     columns with the up columns of the same indices.  src and dst must not overlap.
+ *   b200moe_grouped_gemm_int8_packed: same results as b200moe_grouped_gemm with compute_type int8
+ *     (gate_up_silu == 0, packed with gate_up == 0; y bf16 [M, N]) or as b200moe_grouped_gemm
+ *     followed by b200moe_silu_mul (gate_up_silu != 0, packed with gate_up != 0; y bf16 [M, N / 2]).
+ *     scale / offset bf16 [G, N] in the ORIGINAL column order.  Workspace as for
+ *     b200moe_grouped_gemm with compute_type int8. */
+int b200moe_pack_weight_int8(const void* weight, void* packed, int64_t G, int64_t K, int64_t N, int gate_up,
+                             void* stream);
+int b200moe_grouped_gemm_int8_packed(const void* x, const void* packed, const void* scale, const void* offset,
+                                     const int64_t* group_list, void* y, int64_t M, int64_t K, int64_t N, int64_t G,
+                                     int group_list_type, int gate_up_silu, void* workspace, size_t workspace_bytes,
+                                     void* stream);
+
 /* Allocation-free int8 grouped GEMM.  (No counterpart in the reference: its host binding always
  * obtains a workspace with aclrtMalloc.)  For callers that must not allocate device memory -- a
  * plug-in running inside another framework's step whose allocator owns all device memory, or a

@@ -301,9 +301,12 @@ def max_abs(a: torch.Tensor, b: torch.Tensor) -> float:
 # expert-parallel MoE FFN layer (single-process golden of the benchmark's layer configuration)
 # --------------------------------------------------------------------------------------------
 def route_topk(logits: torch.Tensor, top_k: int):
-    """softmax over experts -> top-k -> weights renormalised to sum 1 (float32)."""
+    """softmax over experts -> top-k -> weights renormalised to sum 1 (float32).  Equal probabilities
+    (equal bf16 logits) go to the lower expert index: a stable descending sort, not torch.topk, whose
+    choice among ties is unspecified."""
     p = torch.softmax(logits.float(), dim=-1)
-    w, idx = torch.topk(p, top_k, dim=-1)
+    ws, order = torch.sort(p, dim=-1, descending=True, stable=True)
+    w, idx = ws[..., :top_k].contiguous(), order[..., :top_k].contiguous()
     return w / w.sum(dim=-1, keepdim=True), idx
 
 

@@ -282,10 +282,30 @@ def test_layer_with_and_without_fused_silu_agree_bit_for_bit():
     c = small_case(T=200, H=256, E=8, I=256, k=2)
     d = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
     w = [d[k] for k in ("w13", "s13", "o13", "w2", "s2", "o2")]
-    a = MoELayer(*w, c["E"], c["top_k"], fuse_silu=True).forward(d["x"], d["logits"])
-    b = MoELayer(*w, c["E"], c["top_k"], fuse_silu=False).forward(d["x"], d["logits"])
+    a = MoELayer(*w, c["E"], c["top_k"], fuse_silu=True, gemm="generic").forward(d["x"], d["logits"])
+    b = MoELayer(*w, c["E"], c["top_k"], fuse_silu=False, gemm="generic").forward(d["x"], d["logits"])
     torch.cuda.synchronize()
     assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+@pytest.mark.gpu
+def test_layer_on_packed_weights_agrees_with_the_drop_in_operator_path():
+    """The layer's default (weights repacked once, dequantised into tensor memory) against the same
+    layer on the [G, K, N] tensors through the drop-in grouped GEMM, and both against the oracle."""
+    from ascend_kernel_b200.moe_layer import MoELayer
+
+    c = small_case(T=400, H=256, E=8, I=256, k=4)
+    d = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
+    w = [d[k] for k in ("w13", "s13", "o13", "w2", "s2", "o2")]
+    packed = MoELayer(*w, c["E"], c["top_k"])
+    assert packed.gemm == "packed"
+    a = packed.forward(d["x"], d["logits"])
+    b = MoELayer(*w, c["E"], c["top_k"], gemm="generic").forward(d["x"], d["logits"])
+    torch.cuda.synchronize()
+    gold = O.moe_layer(c["x"], c["logits"], c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], c["top_k"])
+    close(a.cpu(), gold)
+    close(b.cpu(), gold)
+    assert O.rel_l2(a.float().cpu(), b.float().cpu()) < 2e-3
 
 
 @pytest.mark.gpu
