@@ -26,7 +26,12 @@
 // scale and offset are per-thread scalars, a warp stores 64 contiguous bytes of one output row
 // per instruction); warps 12-27 dequant in two groups on alternate stages.  TMEM: accumulators of
 // the two halves at columns 0 and 160, the A ring (3 stages x 2 halves x 32 columns) from column
-// 320.  Every wait is bounded.
+// 320.  The x ring has its own barriers and twice the depth: an x box takes 700 to 800 cycles from
+// issue to arrival, more than a stage lasts, and shared memory has the room that tensor memory lacks.
+// The MMA warp's loop is serial and every step of it costs tens of cycles, so it sees ONE barrier
+// pair: a relay lane of the dequant group (which has slack) waits for the stage's x tile before the
+// group reports the stage full, and hands the x slot back to the producer when it observes the
+// completion of the MMAs that read it.  Every wait is bounded.
 #include "common.cuh"
 #include "gemm_args.cuh"
 #include "ptx.cuh"
@@ -37,7 +42,8 @@ namespace pk {
 constexpr int kBK = 64;        // k per stage
 constexpr int kTileN = 256;    // weight columns per tile: two MMA halves of 128
 constexpr int kMaxR = 160;     // token rows per tile (the MMA's N extent), a multiple of 32
-constexpr int kStages = 3;
+constexpr int kStages = 3;     // A ring (tensor memory), 64 k per stage
+constexpr int kXStages = 6;    // x ring (shared memory), 64 k per stage
 constexpr int kThreads = 896;
 constexpr int kWarpProd = 0, kWarpMma = 2, kWarpEpi0 = 4, kEpiWarps = 8, kWarpDq0 = 12;
 constexpr int kDqGroups = 2, kDqGroupWarps = 8;
@@ -56,7 +62,9 @@ constexpr int kEpiStripBytes = kMaxR * 4;  // per epilogue warp: the row sums of
 static_assert(kACol + kStages * kAStageCols <= kTmemCols, "tensor memory budget");
 
 struct Barriers {
-    uint64_t full[kStages];   // TMA bytes of the x boxes + the 8 dequant warps of the stage's group
+    uint64_t x_full[kXStages];   // x ring: TMA bytes; waited for by the relay lane of the stage's dequant group
+    uint64_t x_empty[kXStages];  // x ring: one arrive by the relay lane once the stage's MMAs have completed
+    uint64_t full[kStages];   // the 8 dequant warps of the stage's group: A slot written AND x tile landed
     uint64_t empty[kStages];  // one tcgen05.commit per stage
     uint64_t t_full, t_empty; // accumulator hand-off with the epilogue
     uint64_t drain;
@@ -199,7 +207,7 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* x_ring = base;
-    Barriers* sb = reinterpret_cast<Barriers*>(x_ring + kStages * kXSlotBytes);
+    Barriers* sb = reinterpret_cast<Barriers*>(x_ring + kXStages * kXSlotBytes);
     float* epi_rowsum = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sb) + kBarrierBytes);
     int* row_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(epi_rowsum) + kEpiWarps * kEpiStripBytes);
     int* tile_prefix = row_start + (a.G + 1);
@@ -220,8 +228,12 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         sb->n_tiles = acc;
         sb->abort = 0;
         for (int i = 0; i < kTileRing; ++i) sb->tile_ring[i] = 0ull;
+        for (int i = 0; i < kXStages; ++i) {
+            ptx::mbar_init(ptx::smem_u32(&sb->x_full[i]), 1);
+            ptx::mbar_init(ptx::smem_u32(&sb->x_empty[i]), 1);
+        }
         for (int i = 0; i < kStages; ++i) {
-            ptx::mbar_init(ptx::smem_u32(&sb->full[i]), 1 + kDqGroupWarps);
+            ptx::mbar_init(ptx::smem_u32(&sb->full[i]), kDqGroupWarps);
             ptx::mbar_init(ptx::smem_u32(&sb->empty[i]), 1);
         }
         ptx::mbar_init(ptx::smem_u32(&sb->t_full), 1);
@@ -284,9 +296,9 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 const int n_big = r32 / kBigBox, n_small = (r32 % kBigBox) / kSmallBox;
                 const uint32_t stage_bytes = (uint32_t)(r32 * kBK * 2);
                 for (int kt = 0; kt < n_kt; ++kt, ++ia) {
-                    const uint32_t s = ia % kStages, ph = (ia / kStages) & 1;
-                    if (ia >= kStages && !pk_wait(&sb->empty[s], ph ^ 1, sb, a.status, 10 + (int)s)) { ok = false; break; }
-                    const uint32_t bar = ptx::smem_u32(&sb->full[s]);
+                    const uint32_t s = ia % kXStages, ph = (ia / kXStages) & 1;
+                    if (ia >= kXStages && !pk_wait(&sb->x_empty[s], ph ^ 1, sb, a.status, 10 + (int)s)) { ok = false; break; }
+                    const uint32_t bar = ptx::smem_u32(&sb->x_full[s]);
                     const uint32_t dst = ptx::smem_u32(x_ring + s * kXSlotBytes);
                     const int kx = kt * kBK;
                     ptx::mbar_arrive_expect_tx(bar, stage_bytes);
@@ -298,8 +310,8 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 }
             }
             if (!ok)
-                for (uint32_t j = (ia > kStages ? ia - kStages : 0); j < ia; ++j)
-                    (void)ptx::mbar_wait(ptx::smem_u32(&sb->full[j % kStages]), (j / kStages) & 1);
+                for (uint32_t j = (ia > kXStages ? ia - kXStages : 0); j < ia; ++j)
+                    (void)ptx::mbar_wait(ptx::smem_u32(&sb->x_full[j % kXStages]), (j / kXStages) & 1);
         }
     } else if (warp == kWarpMma) {
         // ------------------------------ MMA issuer ------------------------------
@@ -312,8 +324,11 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             // B: the x tile, K-major, 8-row groups 1024 B apart, 32 B per 16 k inside the swizzle atom
             const uint64_t db0 = ptx::umma_desc_sw128(ptx::smem_u32(x_ring), 0, 1024);
             const uint32_t ta0 = tmem_base + kACol;
-            uint32_t s = 0, ph = 0, tiles_done = 0, seq = 0;
+            uint32_t s = 0, ph = 0, xs = 0, tiles_done = 0, seq = 0;
             bool ok = true;
+            // whether the next stage's barrier has been seen complete already: polled (non-blocking) right
+            // after a stage's MMAs are issued, so that the poll's latency runs beside the commit's
+            bool ready = false;
             for (;;) {
                 const int t = next_tile(sb, seq, n_tiles, a.status);
                 if (t >= n_tiles || !ok) break;
@@ -324,10 +339,11 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 ptx::tc_fence_after();
                 uint32_t accumulate = 0;
                 for (int kt = 0; kt < n_kt; ++kt) {
-                    if (!pk_wait(&sb->full[s], ph, sb, a.status, 40 + (int)s)) { ok = false; break; }
+                    if (!ready && !pk_wait(&sb->full[s], ph, sb, a.status, 40 + (int)s)) { ok = false; break; }
                     ptx::tc_fence_after();
-                    const uint64_t db = db0 + (uint64_t)(s * (kXSlotBytes >> 4));
+                    const uint64_t db = db0 + (uint64_t)(xs * (kXSlotBytes >> 4));
                     const uint32_t ta = ta0 + s * kAStageCols;
+                    const uint32_t s_next = (s + 1 == kStages) ? 0u : s + 1, ph_next = (s + 1 == kStages) ? ph ^ 1u : ph;
                     if (leader) {
 #pragma unroll
                         for (int h = 0; h < 2; ++h)
@@ -335,11 +351,14 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                             for (int k16 = 0; k16 < kBK / 16; ++k16)
                                 ptx::umma_bf16_ta(tmem_base + h * kMaxR, ta + h * 32 + k16 * 8, db + (uint64_t)(k16 * 2), idesc,
                                                   accumulate | (uint32_t)k16);
-                        ptx::umma_commit(ptx::smem_u32(&sb->empty[s]));
                     }
-                    __syncwarp();
+                    ready = ptx::mbar_test_wait(ptx::smem_u32(&sb->full[s_next]), ph_next);
+                    if (leader) ptx::umma_commit(ptx::smem_u32(&sb->empty[s]));
+                    ready = __all_sync(0xffffffffu, ready);
                     accumulate = 1;
-                    if (++s == kStages) { s = 0; ph ^= 1; }
+                    s = s_next;
+                    ph = ph_next;
+                    if (++xs == kXStages) xs = 0;
                 }
                 if (!ok) break;
                 if (leader) ptx::umma_commit(ptx::smem_u32(&sb->t_full));
@@ -440,6 +459,7 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         const int grp = dq_tid / (kDqGroupWarps * 32);
         const int wb = (dq_tid / 32) % kDqGroupWarps;  // warp block 4 h + q; q equals warp index % 4
         const int thread_off = wb * 2048 + lane * 16;
+        const bool relay = (dq_tid % (kDqGroupWarps * 32)) == 0;  // lane 0 of the group's first warp
         const uint32_t ta0 = tmem_base + kACol + (uint32_t)((wb >> 2) * 32) + ((uint32_t)((wb & 3) * 32) << 16);
         DqIter pf;
         pf.seq = 0;
@@ -466,9 +486,18 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 if (!loaded[u]) { ok = false; break; }  // the schedule has ended
                 const uint32_t slot = ib % kStages;
                 bool got = true;
-                if (ib >= kStages) got = pk_wait(&sb->empty[slot], ((ib / kStages) & 1) ^ 1, sb, a.status, 80 + (int)slot);
+                if (ib >= kStages) {
+                    got = pk_wait(&sb->empty[slot], ((ib / kStages) & 1) ^ 1, sb, a.status, 80 + (int)slot);
+                    // the MMAs of stage ib - kStages have completed: their x slot goes back to the producer
+                    if (relay && got) ptx::mbar_arrive(ptx::smem_u32(&sb->x_empty[(ib - kStages) % kXStages]));
+                }
                 if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
                 ptx::tc_fence_after();
+                // The relay lane will report the stage full only when its x tile has landed as well.  The tile
+                // was requested kXStages stages ago, so this wait is over before the conversion is; its
+                // result is consumed after the stores.
+                bool x_ok = true;
+                if (relay) x_ok = pk_wait(&sb->x_full[ib % kXStages], (ib / kXStages) & 1, sb, a.status, 50);
                 const uint32_t ta = ta0 + slot * kAStageCols;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {  // 16 k = 8 columns per chunk
@@ -482,7 +511,7 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 }
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
-                __syncwarp();
+                if (!__all_sync(0xffffffffu, x_ok)) { ok = false; break; }
                 if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->full[slot]));
                 loaded[u] = pf.valid;
                 if (pf.valid) {
@@ -588,7 +617,7 @@ extern "C" int b200moe_grouped_gemm_int8_packed(const void* x, const void* packe
     if (rc != B200MOE_OK) return rc;
     rc = make_tensor_map_2d(&txs, x, 2, (uint64_t)M, (uint64_t)K, pk::kSmallBox, pk::kBK, true);
     if (rc != B200MOE_OK) return rc;
-    const size_t smem = 1024 + (size_t)pk::kStages * pk::kXSlotBytes + pk::kBarrierBytes +
+    const size_t smem = 1024 + (size_t)pk::kXStages * pk::kXSlotBytes + pk::kBarrierBytes +
                         (size_t)pk::kEpiWarps * pk::kEpiStripBytes + sizeof(int) * 2 * (size_t)(G + 1);
     if (gate_up_silu) {
         B200MOE_CUDA_TRY(cudaFuncSetAttribute(pk::grouped_gemm_packed_kernel<true>,
