@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200moe.so")
 
 # enums of include/b200moe.h
-CT = {"fp8": 0, "fp4": 1, "int8": 2, "int4": 3}
+CT = {"fp8": 0, "fp4": 1, "int8": 2, "int4": 3, "bf16": 4}
 GROUP_LIST_CUMSUM, GROUP_LIST_COUNTS = 0, 1
 LAYOUT = {"canonical": 0, "ascend": 1}
 FP4_SCALE_NONE, FP4_SCALE_E8M0_PER32 = 0, 1
@@ -22,9 +22,10 @@ STATUS_BYTES = 256
 EXPORTS = [
     "b200moe_grouped_gemm", "b200moe_grouped_gemm_workspace_bytes", "b200moe_grouped_gemv",
     "b200moe_grouped_gemv_workspace_bytes", "b200moe_fp4_dequant", "b200moe_fp4_layout", "b200moe_silu_mul",
-    "b200moe_gather_rows", "b200moe_combine", "b200moe_read_status", "b200moe_strerror", "b200moe_version",
+    "b200moe_gather_rows", "b200moe_combine", "b200moe_read_status", "b200moe_read_sticky_status", "b200moe_strerror", "b200moe_version",
     "b200moe_moe_route", "b200moe_moe_regroup_index", "b200moe_grouped_gemm_int8_noalloc", "b200moe_grouped_gemm_int8_noalloc_max_rows", "b200moe_noalloc_read_status",
     "b200moe_ep_post_counts", "b200moe_ep_dispatch", "b200moe_ep_wait", "b200moe_ep_post", "b200moe_ep_combine",
+    "b200moe_fp4_dequant_bf16_scale", "b200moe_fp8_dequant", "b200moe_fp4_scale_fold",
     "b200moe_silu_mul_dyn", "b200moe_grouped_gemm_int8_silu", "b200moe_pack_weight_int8", "b200moe_grouped_gemm_int8_packed", "b200moe_ipc_alloc", "b200moe_ipc_open", "b200moe_ipc_close", "b200moe_ipc_free",
 ]
 
@@ -77,6 +78,12 @@ def _load() -> ctypes.CDLL:
     lib.b200moe_noalloc_read_status.restype = i32
     lib.b200moe_fp4_dequant.argtypes = [vp, vp, vp, i64, i32, vp]
     lib.b200moe_fp4_dequant.restype = i32
+    lib.b200moe_fp4_dequant_bf16_scale.argtypes = [vp, vp, vp, i64, i64, i64, i32, vp]
+    lib.b200moe_fp4_dequant_bf16_scale.restype = i32
+    lib.b200moe_fp8_dequant.argtypes = [vp, vp, vp, i64, i64, i64, vp]
+    lib.b200moe_fp8_dequant.restype = i32
+    lib.b200moe_fp4_scale_fold.argtypes = [vp, vp, vp, i64, i64, i64, i64, vp]
+    lib.b200moe_fp4_scale_fold.restype = i32
     lib.b200moe_fp4_layout.argtypes = [vp, vp, i64, i64, i64, i32, vp]
     lib.b200moe_fp4_layout.restype = i32
     lib.b200moe_silu_mul.argtypes = [vp, vp, i64, i64, vp]
@@ -106,6 +113,8 @@ def _load() -> ctypes.CDLL:
         f.restype = i32
     lib.b200moe_read_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
     lib.b200moe_read_status.restype = i32
+    lib.b200moe_read_sticky_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), i32, vp]
+    lib.b200moe_read_sticky_status.restype = i32
     lib.b200moe_strerror.argtypes = [i32]
     lib.b200moe_strerror.restype = ctypes.c_char_p
     lib.b200moe_version.argtypes = []

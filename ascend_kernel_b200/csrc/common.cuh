@@ -19,6 +19,16 @@ constexpr int kDevOk = 0;
 constexpr int kDevBadGroupList = 1;
 constexpr int kDevWaitExpired = 2;
 
+// Records a device-side finding in the status words of a workspace: words 0 / 1 (zeroed by every
+// entry point before its launch) hold the code and detail of the current call, words 4 / 5 keep the
+// first finding of ANY call that used this workspace since the caller last zeroed them -- a binding
+// that reuses one workspace can check them at its own synchronisation points.
+__device__ __forceinline__ void report_status(int* status, int code, int detail) {
+    if (status == nullptr) return;
+    if (atomicCAS(status, 0, code) == 0) status[1] = detail;
+    if (atomicCAS(status + 4, 0, code) == 0) status[5] = detail;
+}
+
 // Largest expert count the kernels keep in shared memory.
 constexpr int kMaxExperts = 1024;
 
@@ -182,10 +192,7 @@ __device__ __forceinline__ void load_row_starts(const int64_t* __restrict__ gl, 
             row_start[g + 1] = end;
             prev = end;
         }
-        if (bad && status != nullptr) {
-            atomicCAS(status, kDevOk, kDevBadGroupList);
-            status[1] = bad_at;
-        }
+        if (bad) report_status(status, kDevBadGroupList, bad_at);
     }
     __syncthreads();
 }

@@ -82,6 +82,10 @@ struct GmTraits {
     static constexpr int kStages = (kParts == 1) ? kNS : 2;
     static constexpr int kPRowBytes = kNibbles ? kBN / 2 : kBN;
     static constexpr int kPTileBytes = kPRowBytes * kBK;
+    // bf16 weights need no conversion: TMA writes the 64-column blocks of the weight tile straight
+    // into the B ring (a 64 k x 128-byte box with the 128-byte swizzle is exactly one block of the
+    // MN-major operand layout) and the dequant warps have nothing to do
+    static constexpr bool kDirect = (MODE == B200MOE_CT_BF16);
 };
 
 struct GmBarriers {
@@ -117,10 +121,7 @@ __device__ __noinline__ bool gm_wait_slow(uint32_t bar, uint32_t parity, GmBarri
             if (*abort) return false;
             if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
                 *abort = 1;
-                if (status != nullptr) {
-                    atomicCAS(status, kDevOk, kDevWaitExpired);
-                    status[1] = id;
-                }
+                report_status(status, kDevWaitExpired, id);
                 return false;
             }
         }
@@ -150,7 +151,7 @@ __device__ __forceinline__ int next_tile(GmBarriers* sb, uint32_t& seq, int n_ti
                 if (*abort) return n_tiles;
                 if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
                     *abort = 1;
-                    if (status != nullptr && atomicCAS(status, kDevOk, kDevWaitExpired) == kDevOk) status[1] = 90;
+                    report_status(status, kDevWaitExpired, 90);
                     return n_tiles;
                 }
             }
@@ -310,13 +311,17 @@ __device__ __forceinline__ void load_packed(PackedRegs<MODE>& r, const DqIter& i
         if constexpr (T::kNibbles) {
             const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
             r.q[j] = make_uint4(v.x, v.y, 0u, 0u);
-        } else {
+        } else if (MODE != B200MOE_CT_FP8 || it.n0 + d.c16 * 16 < a.N) {
             r.q[j] = __ldg(reinterpret_cast<const uint4*>(p));
+        } else {
+            r.q[j] = make_uint4(0u, 0u, 0u, 0u);  // columns past N in the 128-column last tile of an fp8 matrix
         }
     }
     if constexpr (MODE == B200MOE_CT_FP8) {
-        r.sf = __ldg(static_cast<const float*>(a.scale) +
-                     ((size_t)it.g * (a.K >> 7) + ((it.kt * kBK) >> 7)) * (a.N >> 7) + ((it.n0 + d.c16 * 16) >> 7));
+        r.sf = it.n0 + d.c16 * 16 < a.N
+                   ? __ldg(static_cast<const float*>(a.scale) + ((size_t)it.g * (a.K >> 7) + ((it.kt * kBK) >> 7)) * (a.N >> 7) +
+                           ((it.n0 + d.c16 * 16) >> 7))
+                   : 0.f;
     }
     if constexpr (MODE == B200MOE_CT_FP4) {
         const uint4* sp = reinterpret_cast<const uint4*>(
@@ -485,7 +490,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     int* tile_prefix = row_start + (a.G + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_nt = a.N / kBN;
+    const int n_nt = (a.N + kBN - 1) / kBN;  // (fp8 only: the last tile may hold 128 columns)
     const int n_kt = a.K / kBK;  // stages per tile
 
     load_row_starts(a.group_list, a.G, a.M, a.gl_type, row_start, a.status);
@@ -505,7 +510,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         sb->n_tiles = acc;
         sb->abort = 0;
         for (int i = 0; i < kTileRing; ++i) sb->tile_ring[i] = 0ull;
-        for (int i = 0; i < NS; ++i) { ptx::mbar_init(ptx::smem_u32(&sb->full[i]), 1 + kDqGroupWarps); ptx::mbar_init(ptx::smem_u32(&sb->empty[i]), 1); }
+        for (int i = 0; i < NS; ++i) {
+            ptx::mbar_init(ptx::smem_u32(&sb->full[i]), T::kDirect ? 1 : 1 + kDqGroupWarps);
+            ptx::mbar_init(ptx::smem_u32(&sb->empty[i]), 1);
+        }
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(ptx::smem_u32(&sb->t_full[i]), 1);
             ptx::mbar_init(ptx::smem_u32(&sb->t_empty[i]), kEpiWarps / 2);
@@ -553,7 +561,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             far.valid = far.t < n_tiles;
             if (far.valid) far.ti = locate_tile(far.t, tile_prefix, row_start, a.G, n_nt);
             auto far_step = [&]() {
-                ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0, far.ti.g * a.K + far.kt * kBK);
+                if constexpr (!T::kDirect)
+                    ptx::tma_prefetch_l2_2d(&tmap_w, T::kNibbles ? far.ti.n0 / 2 : far.ti.n0, far.ti.g * a.K + far.kt * kBK);
                 if (++far.kt < n_kt) return;
                 far.kt = 0;
                 far.t = publish();
@@ -579,7 +588,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     if (ia >= NS && !gm_wait(&sb->empty[s], ph ^ 1, sb, a.status, 10 + (int)s)) { ok = false; break; }
                     const uint32_t bar = ptx::smem_u32(&sb->full[s]);
                     const int kx = kt * kBK;
-                    ptx::mbar_arrive_expect_tx(bar, stage_bytes);
+                    ptx::mbar_arrive_expect_tx(bar, stage_bytes + (T::kDirect ? (uint32_t)kBTileBytes : 0u));
+                    if constexpr (T::kDirect) {
+#pragma unroll
+                        for (int blk = 0; blk < kBN / 64; ++blk)
+                            ptx::tma_load_2d(ptx::smem_u32(b_ring + s * kBTileBytes + blk * (kBK * 128)), &tmap_w, bar,
+                                             ti.n0 + blk * 64, ti.g * a.K + kx);
+                    }
                     if (ti.halves == 2) {
                         ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes), &tmap_x, bar, kx, ti.row0);
                         ptx::tma_load_2d(ptx::smem_u32(a_ring + s * kATileBytes + kAHalfBytes), last_map, bar, kx,
@@ -740,6 +755,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 __nv_bfloat16* yrow = a.y + (size_t)row * a.N + ti.n0;
 #pragma unroll 1
                 for (int c = 0; c < kBN / 32; ++c) {
+                    if (MODE == B200MOE_CT_FP8 && ti.n0 + c * 32 >= a.N) break;  // 128-column last tile
                     uint32_t r[32];
                     ptx::tmem_ld_32x32(tmem_base + grp * kBN + c * 32 + ((uint32_t)(quarter * 32) << 16), r);
                     ptx::tmem_ld_wait();
@@ -777,7 +793,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->t_empty[grp]));
         }
-    } else if (warp >= kWarpDq0) {
+    } else if (warp >= kWarpDq0 && !T::kDirect) {
         // ------------------------------ dequant ------------------------------
         // A unit of work is one stage (one k block); for int4 it holds the hi and the lo tile.  These
         // warps bound the kernel when tiles are small, so the loop carries as little bookkeeping as it
@@ -915,7 +931,11 @@ static int gm_launch(const void* x, const void* w, const GemmArgs& a, cudaStream
     if (rc != B200MOE_OK) return rc;
     rc = make_tensor_map_2d(&txs, x, 2, (uint64_t)a.M, a.K, kSmallRows, kBK, true);
     if (rc != B200MOE_OK) return rc;
-    rc = make_tensor_map_2d(&tw, w, 1, (uint64_t)a.G * a.K, T::kNibbles ? a.N / 2 : a.N, kBK, T::kPRowBytes, false);
+    if (T::kDirect)
+        rc = make_tensor_map_2d(&tw, w, 2, (uint64_t)a.G * a.K, a.N, kBK, 64, true);
+    else
+        rc = make_tensor_map_2d(&tw, w, 1, (uint64_t)a.G * a.K, T::kNibbles ? a.N / 2 : a.N, kBK,
+                                a.N < kBN ? (uint32_t)(T::kNibbles ? a.N / 2 : a.N) : (uint32_t)T::kPRowBytes, false);
     if (rc != B200MOE_OK) return rc;
     const size_t smem = gm_smem_bytes(a.G);
     B200MOE_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_kernel<MODE, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -943,7 +963,7 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
                                     const int64_t* group_list, void* y, int64_t M, int64_t K, int64_t N, int64_t G,
                                     int compute_type, int group_list_type, int weight_layout, void* workspace,
                                     size_t workspace_bytes, void* stream) {
-    if (compute_type < B200MOE_CT_FP8 || compute_type > B200MOE_CT_INT4) return B200MOE_ERR_COMPUTE_TYPE;
+    if (compute_type < B200MOE_CT_FP8 || compute_type > B200MOE_CT_BF16) return B200MOE_ERR_COMPUTE_TYPE;
     if (group_list_type != B200MOE_GROUP_LIST_CUMSUM && group_list_type != B200MOE_GROUP_LIST_COUNTS)
         return B200MOE_ERR_ARGUMENT;
     if (weight_layout != B200MOE_LAYOUT_CANONICAL && weight_layout != B200MOE_LAYOUT_ASCEND)
@@ -951,12 +971,15 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
     if (M < 0 || K <= 0 || N <= 0 || G <= 0 || G > kMaxExperts || M > 0x7FFFFFF0LL || K > 0x7FFFFFF0LL ||
         N > 0x7FFFFFF0LL || G * K > 0x7FFFFFF0LL)
         return B200MOE_ERR_SHAPE;
-    if ((K % kBK) != 0 || (N % kBN) != 0) return B200MOE_ERR_SHAPE;
-    if (compute_type == B200MOE_CT_FP8 && (K % 128) != 0) return B200MOE_ERR_SHAPE;
+    // fp8: what the reference takes (K and N multiples of its 128 x 128 scale block: a last tile of
+    // 128 columns); the other modes work on whole 256-column tiles
+    if (compute_type == B200MOE_CT_FP8 ? ((K % 128) != 0 || (N % 128) != 0) : ((K % kBK) != 0 || (N % kBN) != 0))
+        return B200MOE_ERR_SHAPE;
     if (compute_type == B200MOE_CT_INT4 && (K % 128) != 0) return B200MOE_ERR_SHAPE;
     if (M == 0) return B200MOE_OK;
-    if (!x || !weight || !scale || !group_list || !y) return B200MOE_ERR_NULL_POINTER;
-    if (!aligned16(x) || !aligned16(weight) || !aligned16(scale) || !aligned16(y) || (offset && !aligned16(offset)))
+    const bool needs_scale = compute_type != B200MOE_CT_BF16;
+    if (!x || !weight || (needs_scale && !scale) || !group_list || !y) return B200MOE_ERR_NULL_POINTER;
+    if (!aligned16(x) || !aligned16(weight) || (scale && !aligned16(scale)) || !aligned16(y) || (offset && !aligned16(offset)))
         return B200MOE_ERR_ALIGNMENT;
     const size_t need = b200moe_grouped_gemm_workspace_bytes(M, K, N, G, compute_type, weight_layout);
     if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return B200MOE_ERR_WORKSPACE;
@@ -991,9 +1014,8 @@ extern "C" int b200moe_grouped_gemm(const void* x, const void* weight, const voi
         a.offset = static_cast<const __nv_bfloat16*>(offset);  // folded into the weights by the dequant warps
         return gm_launch<B200MOE_CT_INT4>(x, weight, a, s);
     }
-    if (compute_type == B200MOE_CT_FP8) {
-        return gm_launch<B200MOE_CT_FP8>(x, weight, a, s);
-    }
+    if (compute_type == B200MOE_CT_FP8) return gm_launch<B200MOE_CT_FP8>(x, weight, a, s);
+    if (compute_type == B200MOE_CT_BF16) return gm_launch<B200MOE_CT_BF16>(x, weight, a, s);
     // the stored ("ascend") order is read in place by the dequant warps
     if (weight_layout == B200MOE_LAYOUT_ASCEND) return gm_launch<kCtFp4Ascend>(x, weight, a, s);
     return gm_launch<B200MOE_CT_FP4>(x, weight, a, s);

@@ -90,10 +90,7 @@ __device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, Barriers* 
             if (*abort) return false;
             if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
                 *abort = 1;
-                if (status != nullptr) {
-                    atomicCAS(status, kDevOk, kDevWaitExpired);
-                    status[1] = id;
-                }
+                report_status(status, kDevWaitExpired, id);
                 return false;
             }
         }
@@ -121,7 +118,7 @@ __device__ __forceinline__ int next_tile(Barriers* sb, uint32_t& seq, int n_tile
                 if (*abort) return n_tiles;
                 if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
                     *abort = 1;
-                    if (status != nullptr && atomicCAS(status, kDevOk, kDevWaitExpired) == kDevOk) status[1] = 90;
+                    report_status(status, kDevWaitExpired, 90);
                     return n_tiles;
                 }
             }

@@ -336,7 +336,9 @@ __device__ __forceinline__ void gv_compute_mma(const GemvArgs& a, const __nv_bfl
     }
 
     constexpr int kStepRows = 16 * kGvMmaParts;  // k rows the CTA consumes per step
-    for (int k0 = kg * 16; k0 < a.K; k0 += 2 * kStepRows) {
+    // (fp8 accepts N % 256 == 128: in the last slab the warps of the second column half have no columns)
+    const int k_end = (n0 + 128 * hc < a.N) ? a.K : 0;
+    for (int k0 = kg * 16; k0 < k_end; k0 += 2 * kStepRows) {
         const bool second = k0 + kStepRows < a.K;
         float sf = 1.f;
         if constexpr (kBlockScale)  // k0 and k0 + 64 lie in the same 128-row block (K % 128 == 0)
@@ -421,7 +423,7 @@ __device__ __forceinline__ void gv_compute_mma(const GemvArgs& a, const __nv_bfl
         }
 #pragma unroll
         for (int m = 0; m < kGvRows; ++m) {
-            if (m < rows_valid) {
+            if (m < rows_valid && n < a.N) {
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < kGvMmaParts; ++w) v += red[(w * kGvRows + m) * kGvSlabN + tc];
@@ -562,7 +564,7 @@ __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvA
     }
     __syncthreads();
 
-    const int n_slabs = a.N / kGvSlabN;
+    const int n_slabs = (a.N + kGvSlabN - 1) / kGvSlabN;
     const int n_act = *n_active_p;
     const int n_items = n_act * n_slabs;
     const int kvec = a.K / 8;  // 16-byte vectors per x row
@@ -660,8 +662,10 @@ extern "C" int b200moe_grouped_gemv(const void* x, const void* weight, const voi
     if (M < 0 || K <= 0 || N <= 0 || G <= 0 || G > kMaxExperts || M > 0x7FFFFFF0LL || K > 0x7FFFFFF0LL ||
         N > 0x7FFFFFF0LL || G * K > 0x7FFFFFF0LL)
         return B200MOE_ERR_SHAPE;
-    if ((K % 64) != 0 || (N % kGvSlabN) != 0) return B200MOE_ERR_SHAPE;
-    if (compute_type == B200MOE_CT_FP8 && ((K % 128) != 0 || (N % 128) != 0)) return B200MOE_ERR_SHAPE;
+    // fp8: what the reference takes (K and N multiples of its 128 x 128 scale block, i.e. a last slab of
+    // 128 columns); the other modes work on whole 256-column slabs
+    if (compute_type == B200MOE_CT_FP8 ? ((K % 128) != 0 || (N % 128) != 0) : ((K % 64) != 0 || (N % kGvSlabN) != 0))
+        return B200MOE_ERR_SHAPE;
     if (compute_type == B200MOE_CT_INT4 && (K % 128) != 0) return B200MOE_ERR_SHAPE;
     if (M == 0) return B200MOE_OK;
     if (!x || !weight || !scale || !group_list || !y) return B200MOE_ERR_NULL_POINTER;

@@ -82,4 +82,14 @@ int b200moe_read_status(const void* workspace, int32_t out[2], void* stream) {
     return B200MOE_OK;
 }
 
+int b200moe_read_sticky_status(void* workspace, int32_t out[2], int clear, void* stream) {
+    if (workspace == nullptr || out == nullptr) return B200MOE_ERR_NULL_POINTER;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    B200MOE_CUDA_TRY(cudaMemcpyAsync(out, static_cast<const uint8_t*>(workspace) + 16, 2 * sizeof(int32_t),
+                                     cudaMemcpyDeviceToHost, s));
+    if (clear) B200MOE_CUDA_TRY(cudaMemsetAsync(static_cast<uint8_t*>(workspace) + 16, 0, 8, s));
+    B200MOE_CUDA_TRY(cudaStreamSynchronize(s));
+    return B200MOE_OK;
+}
+
 }  // extern "C"

@@ -156,3 +156,28 @@ def config4(device, n_tokens=4096, hidden=7168, n_experts=256, inter=2048, top_k
         s2[i] = _uniform((hidden,), 0.001, 0.01, ge, device)
         o2[i] = _uniform((hidden,), -4.0, 4.0, ge, device)
     return dict(x=x, logits=logits, w13=w13, s13=s13, o13=o13, w2=w2, s2=s2, o2=o2, top_k=top_k)
+
+
+def config4_fp4(device, n_tokens=4096, hidden=7168, n_experts=256, inter=2048, top_k=8, seed=4,
+                expert_lo=0, expert_hi=None):
+    """The MoE layer with its expert weights STORED as FP4 e2m1 the way the dequantisation benchmark
+    stores them: packed two per byte along the last dimension (low nibble = even element), one e8m0
+    scale byte (uniform in 119..127, i.e. 2**-8 .. 2**0) per 32 elements of the last dimension.
+    Tokens and router logits are those of config4; weights are drawn per expert."""
+    expert_hi = n_experts if expert_hi is None else expert_hi
+    gen = _gen(seed, "cpu")
+    x = torch.randn(n_tokens, hidden, generator=gen).to(torch.bfloat16)
+    logits = torch.randn(n_tokens, n_experts, generator=gen).to(torch.bfloat16)
+    n_local = expert_hi - expert_lo
+    c13 = torch.empty(n_local, hidden, inter, dtype=torch.uint8, device=device)           # [E, H, 2I/2]
+    s13 = torch.empty(n_local, hidden, 2 * inter // 32, dtype=torch.uint8, device=device)
+    c2 = torch.empty(n_local, inter, hidden // 2, dtype=torch.uint8, device=device)       # [E, I, H/2]
+    s2 = torch.empty(n_local, inter, hidden // 32, dtype=torch.uint8, device=device)
+    for e in range(expert_lo, expert_hi):
+        ge = _gen(seed * 100003 + 50000 + e, device)
+        i = e - expert_lo
+        c13[i] = torch.randint(0, 256, c13.shape[1:], generator=ge, device=device, dtype=torch.uint8)
+        s13[i] = torch.randint(119, 128, s13.shape[1:], generator=ge, device=device, dtype=torch.uint8)
+        c2[i] = torch.randint(0, 256, c2.shape[1:], generator=ge, device=device, dtype=torch.uint8)
+        s2[i] = torch.randint(119, 128, s2.shape[1:], generator=ge, device=device, dtype=torch.uint8)
+    return dict(x=x, logits=logits, c13=c13, s13=s13, c2=c2, s2=s2, top_k=top_k)

@@ -44,7 +44,8 @@ class CudaRowOps:
 
 class MoELayer:
     def __init__(self, w13, s13, o13, w2, s2, o2, n_experts: int, top_k: int, group=None, row_ops=CudaRowOps,
-                 exchange: str = "nccl", max_tokens: int = 0, fuse_silu: bool = None, gemm: str = None):
+                 exchange: str = "nccl", max_tokens: int = 0, fuse_silu: bool = None, gemm: str = None,
+                 weight_format: str = "int8"):
         """w13 int8 [E_local, H, 2I] (gate columns first), w2 int8 [E_local, I, H]; per-channel bf16
         scales/offsets [E_local, N].  ``group``: a torch.distributed process group or None.
         ``row_ops`` exists so the dispatch / regroup / combine index logic can be exercised by CPU
@@ -58,7 +59,14 @@ class MoELayer:
         ``gemm``: "packed" (default with the CUDA row operations) repacks both weight tensors once
         into the tile order of ``ops.grouped_gemm_packed`` and keeps only those copies -- the expert
         GEMMs then dequantise straight into tensor memory and SiLU(gate) * up runs in the first
-        one's epilogue; "generic" calls the drop-in operator on the [G, K, N] tensors."""
+        one's epilogue; "generic" calls the drop-in operator on the [G, K, N] tensors.
+        ``weight_format="fp4"``: the experts are STORED as FP4 e2m1 -- w13 uint8 [E_local, H, 2I/2] and w2
+        uint8 [E_local, I, H/2], two codes per byte along the last dimension, with s13 / s2 one e8m0 byte
+        per 32 elements of the last dimension ([E_local, H, 2I/32] / [E_local, I, H/32]); o13 / o2 must be
+        None.  Every pass dequantises them to bf16 buffers owned by the layer (FP4 -> BF16 kernel) and
+        runs the bf16 grouped GEMM on those: the two-phase structure of the reference's own kernel
+        (dequantise to a bf16 workspace, then multiply: grouped_matmul_antiquant.h:632-654,
+        grouped_matmul.h:409-463) with the benchmark's storage format."""
         self.ops = row_ops
         self.w13, self.s13, self.o13, self.w2, self.s2, self.o2 = w13, s13, o13, w2, s2, o2
         self.n_experts, self.top_k = n_experts, top_k
@@ -73,6 +81,19 @@ class MoELayer:
         assert self.e_local * self.world == n_experts
         self.hidden, self.inter = w13.shape[1], w2.shape[1]
         self.device = w13.device
+        if weight_format not in ("int8", "fp4"):
+            raise ValueError("weight_format must be 'int8' or 'fp4'")
+        self.weight_format = weight_format
+        self.bf13 = self.bf2 = None
+        if weight_format == "fp4":
+            if o13 is not None or o2 is not None or row_ops is not CudaRowOps:
+                raise ValueError("FP4-stored experts take no offsets and run on the CUDA row operations only")
+            if w13.shape[2] != self.inter or w2.shape[2] * 2 != self.hidden:
+                raise ValueError("expected w13 [E, H, 2I/2] and w2 [E, I, H/2] packed codes")
+            fuse_silu, gemm = False, "generic"
+            # the bf16 weights of one pass: overwritten by every pass, never read across passes
+            self.bf13 = torch.empty(self.e_local, self.hidden, 2 * self.inter, dtype=torch.bfloat16, device=self.device)
+            self.bf2 = torch.empty(self.e_local, self.inter, self.hidden, dtype=torch.bfloat16, device=self.device)
         self.fuse_silu = (row_ops is CudaRowOps) if fuse_silu is None else bool(fuse_silu)
         if gemm is None:
             gemm = "packed" if (row_ops is CudaRowOps and self.fuse_silu) else "generic"
@@ -101,6 +122,19 @@ class MoELayer:
         # expert GEMMs come next (HostPipeline starts the neighbouring steps' host copies there)
         self.mid_hook = None
 
+    def read_status(self, clear: bool = True):
+        """Device-side findings of the passes run so far, read at a synchronisation point of the caller's
+        choosing (it waits for the layer's stream): raises if a grouped GEMM saw an invalid group list or
+        a bounded wait expired, in an operator or in the token exchange; returns (0, 0) otherwise."""
+        code, detail = ops.last_status(self.device, clear=clear)
+        if code == 0 and self.px is not None:
+            code, detail = self.px.read_status()
+        if code != 0:
+            raise RuntimeError(f"MoE layer: device status {code} (detail {detail}): "
+                               + ("invalid group list, rows were clamped" if code == 1 else
+                                  "a bounded wait expired, results are incomplete"))
+        return code, detail
+
     def _mid(self):
         if self.mid_hook is not None:
             self.mid_hook()
@@ -117,6 +151,21 @@ class MoELayer:
         self.timing = None
         if ev:
             ev[0].record()
+        if self.weight_format == "fp4":
+            ops.fp4_dequant(self.w13, self.s13, self.bf13)
+            h = torch.empty(R, 2 * self.inter, dtype=torch.bfloat16, device=self.device)
+            ops.grouped_gemm(rows, self.bf13, None, None, counts, "bf16", h, group_list_type=1)
+            if ev:
+                ev[1].record()
+            act = ops.silu_mul(h) if n_rows is None else ops.silu_mul_dyn(h, n_rows)
+            if ev:
+                ev[2].record()
+            ops.fp4_dequant(self.w2, self.s2, self.bf2)
+            ops.grouped_gemm(act, self.bf2, None, None, counts, "bf16", y, group_list_type=1)
+            if ev:
+                ev[3].record()
+                self.timing = ev
+            return y
         if self.gemm == "packed":
             act = torch.empty(R, self.inter, dtype=torch.bfloat16, device=self.device)
             ops.grouped_gemm_packed(rows, self.w13, self.s13, self.o13, counts, act, group_list_type=1,

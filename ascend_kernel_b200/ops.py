@@ -45,7 +45,7 @@ def _need_cuda(**tensors):
 def _compute_type(computeType: str) -> int:
     if computeType not in CT:
         # the reference reports an unknown computeType this way (grouped_gemm.cpp:10-16,129-133)
-        print(f'Invalid compute type: {computeType}. Supported: "fp4", "fp8", "int8", "int4"')
+        print(f'Invalid compute type: {computeType}. Supported: "fp4", "fp8", "int8", "int4", "bf16"')
         raise RuntimeError("Host tiling failed!")
     return CT[computeType]
 
@@ -57,7 +57,10 @@ def _check_common(x, weight, group_list, output, ct):
         raise RuntimeError("group_list must be int64")
     if x.dim() != 2 or weight.dim() != 3 or output.dim() != 2:
         raise RuntimeError("expected x [M,K], weight [G,K,N(/2)], output [M,N]")
-    if weight.element_size() != 1:
+    if ct == CT["bf16"]:
+        if weight.dtype != torch.bfloat16:
+            raise RuntimeError("weight must be bfloat16 for computeType bf16")
+    elif weight.element_size() != 1:
         raise RuntimeError("weight must be a 1-byte container (uint8 / int8)")
     M, K = x.shape
     G, Kw, Nw = weight.shape
@@ -75,8 +78,54 @@ def _check_scale(scale, ct, G, K, N, what):
         raise RuntimeError(f"{what} must be {want[1]} of shape {want[0]}, got {scale.dtype} {tuple(scale.shape)}")
 
 
+# One persistent workspace per (device, stream): its first 256 bytes hold the kernels' status words, of
+# which words 4 / 5 keep the first finding of any call since they were last cleared (an invalid group
+# list that was clamped, a bounded wait that expired).  `last_status` / `check_status` read them at the
+# caller's synchronisation points, so a failed call cannot pass unnoticed even though no operator
+# synchronises.  Calls on one stream run one after the other, so they can share the buffer.
+_WS = {}
+
+
 def _workspace(need, device):
-    return torch.empty(need, dtype=torch.uint8, device=device)
+    device = torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+    ws = _WS.get(key)
+    if ws is None or ws.numel() < need:
+        new = torch.zeros(max(int(need), 1 << 20), dtype=torch.uint8, device=torch.device("cuda", idx))
+        if ws is not None:
+            new[16:24].copy_(ws[16:24])  # carry the sticky status words over
+        _WS[key] = ws = new
+    return ws
+
+
+def last_status(device=None, clear: bool = False):
+    """(code, detail) of the first device-side finding of any operator call on ``device`` (default: the
+    current one) since the status was last cleared; (0, 0) if none.  code 1: a group_list was invalid and
+    rows were clamped (detail = expert index); 2: a bounded wait inside a kernel expired and the output
+    is incomplete.  Synchronises the streams the operators ran on."""
+    import ctypes
+
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    found = (0, 0)
+    for (d, stream), ws in list(_WS.items()):
+        if d != idx:
+            continue
+        out = (ctypes.c_int32 * 2)()
+        with torch.cuda.device(d):
+            _abi.check(_lib.b200moe_read_sticky_status(_ptr(ws), out, int(bool(clear)), stream), "read_sticky_status")
+        if found == (0, 0) and out[0] != 0:
+            found = (int(out[0]), int(out[1]))
+    return found
+
+
+def check_status(device=None):
+    """Raises if an operator call on ``device`` left a device-side finding (and clears it)."""
+    code, detail = last_status(device, clear=True)
+    if code != 0:
+        what = {1: "a group_list was invalid (rows were clamped); first bad expert index",
+                2: "a bounded wait inside a kernel expired (results are incomplete); barrier id"}.get(code, "status")
+        raise RuntimeError(f"b200moe device status {code}: {what} {detail}")
 
 
 def _run(fn, ws_fn, what, x, weight, scale, offset, group_list, output, ct, group_list_type, layout, M, K, N, G):
@@ -97,7 +146,10 @@ def grouped_gemm(x, weight, antiquantScaleOptional, antiquantOffsetOptional, gro
     _need_cuda(x=x, weight=weight, scale=antiquantScaleOptional, offset=antiquantOffsetOptional,
                group_list=groupListOptional, output=output)
     M, K, N, G = _check_common(x, weight, groupListOptional, output, ct)
-    _check_scale(antiquantScaleOptional, ct, G, K, N, "antiquantScaleOptional")
+    if ct == CT["bf16"]:
+        antiquantScaleOptional = None  # the matmul phase alone: no scale, no offset
+    else:
+        _check_scale(antiquantScaleOptional, ct, G, K, N, "antiquantScaleOptional")
     offset = antiquantOffsetOptional if ct in (CT["int8"], CT["int4"]) else None  # ignored for fp8/fp4
     if offset is not None:
         _check_scale(offset, ct, G, K, N, "antiquantOffsetOptional")
@@ -140,7 +192,7 @@ def grouped_gemm_silu(x, weight, scale, offset, group_list, output, group_list_t
     if offset is not None:
         _check_scale(offset, CT["int8"], G, K, N, "offset")
     need = _lib.b200moe_grouped_gemm_workspace_bytes(M, K, N, G, CT["int8"], LAYOUT["canonical"])
-    ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+    ws = _workspace(need, x.device)
     with torch.cuda.device(x.device):
         rc = _lib.b200moe_grouped_gemm_int8_silu(_ptr(x), _ptr(weight), _ptr(scale), _ptr(offset), _ptr(group_list),
                                                  _ptr(output), M, K, N, G, group_list_type, _ptr(ws), need, _stream())
@@ -224,6 +276,54 @@ def fp4_dequant(codes, scale, output):
                                       _abi.FP4_SCALE_NONE if scale is None else _abi.FP4_SCALE_E8M0_PER32, _stream())
     _abi.check(rc, "fp4_dequant")
     _count(1)
+
+
+def fp4_dequant_bf16_scale(codes, scale, output, weight_layout: str = "ascend"):
+    """The reference's FP4 weight format on its own: codes int8/uint8 [G, K, N/2], scale bf16 [G, K/16, N]
+    -> output bf16 [G, K, N] = rne_bf16(e2m1 * scale), the weights its GEMM kernel multiplies with."""
+    _need_cuda(codes=codes, scale=scale, output=output)
+    G, K, C = codes.shape
+    N = 2 * C
+    if codes.element_size() != 1 or scale.dtype != torch.bfloat16 or tuple(scale.shape) != (G, K // 16, N):
+        raise RuntimeError("codes: bytes [G, K, N/2]; scale: bfloat16 [G, K/16, N]")
+    if output.dtype != torch.bfloat16 or tuple(output.shape) != (G, K, N):
+        raise RuntimeError("output must be bfloat16 [G, K, N]")
+    with torch.cuda.device(codes.device):
+        rc = _lib.b200moe_fp4_dequant_bf16_scale(_ptr(codes), _ptr(scale), _ptr(output), G, K, N, LAYOUT[weight_layout],
+                                                 _stream())
+    _abi.check(rc, "fp4_dequant_bf16_scale")
+    _count(1)
+
+
+def fp8_dequant(codes, scale, output):
+    """The reference's FP8 weight format on its own: codes uint8 [G, K, N], scale float32 [G, K/128, N/128] ->
+    output bf16 [G, K, N] = rne_bf16(e4m3 * scale) (0x7F / 0xFF decode to +-480, as in the reference)."""
+    _need_cuda(codes=codes, scale=scale, output=output)
+    G, K, N = codes.shape
+    if codes.element_size() != 1 or scale.dtype != torch.float32 or tuple(scale.shape) != (G, K // 128, N // 128):
+        raise RuntimeError("codes: uint8 [G, K, N]; scale: float32 [G, K/128, N/128]")
+    if output.dtype != torch.bfloat16 or tuple(output.shape) != (G, K, N):
+        raise RuntimeError("output must be bfloat16 [G, K, N]")
+    with torch.cuda.device(codes.device):
+        rc = _lib.b200moe_fp8_dequant(_ptr(codes), _ptr(scale), _ptr(output), G, K, N, _stream())
+    _abi.check(rc, "fp8_dequant")
+    _count(1)
+
+
+def fp4_scale_fold(block_scale, global_scale):
+    """block_scale bf16 [G, N, K/16] x global_scale float32 [G, 1, 1] or [G, 2, 1] (gate / up halves of the N
+    rows) -> bf16 [G, K/16, N]: the scale tensor the fp4 operators take."""
+    _need_cuda(block_scale=block_scale, global_scale=global_scale)
+    G, N, KB = block_scale.shape
+    n_global = global_scale.numel() // max(G, 1)
+    if block_scale.dtype != torch.bfloat16 or global_scale.dtype != torch.float32 or n_global not in (1, 2):
+        raise RuntimeError("block_scale: bfloat16 [G, N, K/16]; global_scale: float32 [G, 1 or 2, 1]")
+    out = torch.empty(G, KB, N, dtype=torch.bfloat16, device=block_scale.device)
+    with torch.cuda.device(block_scale.device):
+        rc = _lib.b200moe_fp4_scale_fold(_ptr(block_scale), _ptr(global_scale), _ptr(out), G, N, KB, n_global, _stream())
+    _abi.check(rc, "fp4_scale_fold")
+    _count(1)
+    return out
 
 
 def fp4_layout(src, to_ascend: bool):

@@ -39,7 +39,9 @@ enum {
     B200MOE_OK = 0,
     B200MOE_ERR_COMPUTE_TYPE = 1, /* not one of the B200MOE_CT_* values                     */
     B200MOE_ERR_NULL_POINTER = 2, /* a required pointer is NULL                              */
-    B200MOE_ERR_SHAPE = 3,        /* negative size, or K/N not a multiple the mode requires  */
+    B200MOE_ERR_SHAPE = 3,        /* negative size, or K/N not a multiple the mode requires:
+                                     fp8 K % 128 and N % 128 (as the reference); fp4 / int8 / bf16
+                                     K % 64 and N % 256; int4 K % 128 and N % 256                */
     B200MOE_ERR_ALIGNMENT = 4,    /* a pointer is not 16-byte aligned                        */
     B200MOE_ERR_WORKSPACE = 5,    /* workspace missing or smaller than *_workspace_bytes()   */
     B200MOE_ERR_ARGUMENT = 6,     /* invalid enum value (group_list_type, layout, ...)       */
@@ -54,8 +56,11 @@ enum {
     B200MOE_CT_FP4 = 1,  /* "fp4": e2m1 pairs [G,K,N/2] (low nibble = even n), bf16 scale
                                    [G,K/16,N]                                                */
     B200MOE_CT_INT8 = 2, /* "int8": int8 [G,K,N], bf16 scale/offset [G,N]: (W+offset)*scale  */
-    B200MOE_CT_INT4 = 3  /* "int4": two's-complement pairs [G,K,N/2], bf16 scale/offset
+    B200MOE_CT_INT4 = 3, /* "int4": two's-complement pairs [G,K,N/2], bf16 scale/offset
                                    [G,K/128,N]                                               */
+    B200MOE_CT_BF16 = 4  /* "bf16": bf16 weights [G,K,N], no scale (grouped GEMM only): the
+                                   matmul phase of the reference kernel on its own,
+                                   grouped_gemm/op_kernel/grouped_matmul.h:409-463            */
 };
 
 enum { B200MOE_GROUP_LIST_CUMSUM = 0, B200MOE_GROUP_LIST_COUNTS = 1 };
@@ -64,10 +69,15 @@ enum { B200MOE_GROUP_LIST_CUMSUM = 0, B200MOE_GROUP_LIST_COUNTS = 1 };
 enum { B200MOE_LAYOUT_CANONICAL = 0, B200MOE_LAYOUT_ASCEND = 1 };
 enum { B200MOE_FP4_SCALE_NONE = 0, B200MOE_FP4_SCALE_E8M0_PER32 = 1 };
 
-/* Device-side status words live in the first 16 bytes of every workspace:
+/* Device-side status words live in the first 256 bytes of every workspace:
  *   word 0: 0 = ok; 1 = group_list invalid (not monotone / exceeds M; rows were clamped);
  *           2 = a bounded pipeline wait expired inside a kernel (results are incomplete)
- *   word 1: detail (expert index or barrier id). */
+ *   word 1: detail (expert index or barrier id)
+ *   words 2, 3: used by the kernels
+ *   words 4, 5: the first non-zero (word 0, word 1) of any call that used this workspace since the
+ *           caller last zeroed them.  Every entry point zeroes words 0 to 3 before its launch and never
+ *           words 4, 5: a binding that reuses one workspace reads them at its own synchronisation points
+ *           (b200moe_read_sticky_status) instead of after every call. */
 #define B200MOE_STATUS_BYTES 256
 
 /* Grouped GEMM for prefill-sized expert batches:
@@ -157,6 +167,27 @@ size_t b200moe_grouped_gemv_workspace_bytes(int64_t M, int64_t K, int64_t N, int
  * out: n_elems bf16.  n_elems must be a multiple of 32.  Bit-exact. */
 int b200moe_fp4_dequant(const void* codes, const void* scale_e8m0, void* out_bf16, int64_t n_elems,
                         int scale_kind, void* stream);
+
+/* The reference's two weight formats dequantised on their own: the dequant phase of its GEMM kernel
+ * (grouped_gemm/op_kernel/grouped_matmul_antiquant.h:632-654 writes exactly these bf16 weights to
+ * its workspace), bit-exact against the reference's Python goldens.
+ *   fp4: codes [G,K,N/2] (canonical or stored order), bf16 scale [G,K/16,N]:
+ *        out[g,k,n] = rne_bf16(e2m1(code) * scale[g,k/16,n])        antiquant_impl.h:23-85,146-169,210-251
+ *   fp8: uint8 codes [G,K,N], fp32 scale [G,K/128,N/128]:
+ *        out[g,k,n] = rne_bf16(e4m3(code) * scale[g,k/128,n/128])   antiquant_impl.h:87-129,171-208,253-266
+ * out: bf16 [G,K,N].  fp4: K % 64 == 0, N % 256 == 0; fp8: K % 128 == 0, N % 128 == 0. */
+int b200moe_fp4_dequant_bf16_scale(const void* codes, const void* scale, void* out_bf16, int64_t G, int64_t K, int64_t N,
+                                   int weight_layout, void* stream);
+int b200moe_fp8_dequant(const void* codes, const float* scale, void* out_bf16, int64_t G, int64_t K, int64_t N,
+                        void* stream);
+
+/* Two-level FP4 scale fold, the preparation the reference's test applies on the host
+ * (grouped_gemm/test/python/test_group_gemm_fp4.py:86-94 and the transpose of :186): block_scale bf16
+ * [G, N, KB] (one per 16 k, KB = K/16) times the expert's fp32 global scale -- global_scale fp32
+ * [G, n_global], n_global 1 (whole expert) or 2 (first / second half of the N rows, i.e. gate / up) --
+ * rounded to bf16 and written [G, KB, N], the scale tensor the fp4 operators take. */
+int b200moe_fp4_scale_fold(const void* block_scale, const float* global_scale, void* out, int64_t G, int64_t N, int64_t KB,
+                           int64_t n_global, void* stream);
 
 /* FP4 weight layout conversion, [G,K,N/2] bytes: to_ascend != 0 canonical -> stored ("ascend")
  * order, 0 the inverse.  src and dst must not overlap. */
@@ -251,6 +282,9 @@ int b200moe_ipc_free(void* ptr);
 
 /* Copies the two device status words of a workspace to the host (synchronises the stream). */
 int b200moe_read_status(const void* workspace, int32_t out[2], void* stream);
+/* Copies words 4, 5 (the first finding since they were last zeroed) to the host (synchronises the
+ * stream); clear != 0 zeroes them afterwards. */
+int b200moe_read_sticky_status(void* workspace, int32_t out[2], int clear, void* stream);
 
 const char* b200moe_strerror(int code);
 /* "major.minor" of this ABI; a binding can refuse to run against another major. */

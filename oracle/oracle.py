@@ -241,6 +241,8 @@ def grouped_gemm(x, weight, antiquantScaleOptional, antiquantOffsetOptional, gro
         wd = dequant_int8(weight, antiquantScaleOptional, antiquantOffsetOptional)
     elif computeType == "int4":
         wd = dequant_int4(weight, antiquantScaleOptional, antiquantOffsetOptional)
+    elif computeType == "bf16":  # the matmul phase alone (grouped_matmul.h:409-463): B = bf16 weights as they are
+        wd = weight.float()
     else:
         raise RuntimeError("Host tiling failed!")  # grouped_gemm.cpp:10-16,129-133
     acc = torch.float64 if computeType in ("int8", "int4") else torch.float32
@@ -278,10 +280,28 @@ def golden_f32(x, weight, scale, offset, group_list, compute_type, group_list_ty
         wd = dequant_int8(weight, scale, offset)
     elif compute_type == "int4":
         wd = dequant_int4(weight, scale, offset)
+    elif compute_type == "bf16":
+        wd = weight.float()
     else:
         raise RuntimeError("Host tiling failed!")
     acc = torch.float64 if compute_type in ("int8", "int4") else torch.float32
     return grouped_matmul(x, wd, group_list, group_list_type, acc).float()
+
+
+def fp4_scale_fold(block_scale: torch.Tensor, global_scale: torch.Tensor) -> torch.Tensor:
+    """Two-level FP4 scale fold: block_scale bf16 [G,N,K/16] times the fp32 global scale [G,1,1] (or
+    [G,2,1]: first / second half of the N rows), rounded to bf16, transposed to [G,K/16,N].
+    Restates anti_quant_fp8_scale and the transpose that follows it
+    (grouped_gemm/test/python/test_group_gemm_fp4.py:86-94,185-186): the in-place multiply of a bf16
+    tensor by an fp32 one computes in fp32 and rounds once."""
+    G, N, KB = block_scale.shape
+    g = global_scale.float().reshape(G, -1)
+    if g.shape[1] == 1:
+        per_row = g.expand(G, N)
+    else:
+        per_row = torch.cat([g[:, :1].expand(G, N // 2), g[:, 1:2].expand(G, N - N // 2)], dim=1)
+    folded = (block_scale.float() * per_row.unsqueeze(-1)).to(torch.bfloat16)
+    return folded.transpose(-2, -1).contiguous()
 
 
 # --------------------------------------------------------------------------------------------
@@ -336,3 +356,24 @@ def moe_layer(x, logits, w13, s13, o13, w2, s2, o2, top_k: int) -> torch.Tensor:
 def to_numpy_bits(t: torch.Tensor) -> np.ndarray:
     """bf16 tensor -> uint16 bit pattern array (fixtures are stored as bits)."""
     return t.contiguous().view(torch.uint16).numpy().copy()
+
+
+def moe_layer_fp4_stored(x, logits, c13, s13, c2, s2, top_k: int) -> torch.Tensor:
+    """Golden of the layer on FP4-stored experts: codes [E,H,2I/2] / [E,I,H/2] with one e8m0 scale per 32
+    elements of the last dimension, dequantised to bf16 (exact), then route -> x @ W13 (bf16) ->
+    SiLU(gate)*up (bf16) -> @ W2 (bf16) -> weighted sum over the token's experts (fp32 -> bf16)."""
+    T, H = x.shape
+    E, I = c13.shape[0], c2.shape[1]
+    wts, idx = route_topk(logits, top_k)
+    out = torch.zeros(T, H, dtype=torch.float32)
+    for e in range(E):
+        tok, slot = (idx == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        wd1 = fp4_dequant_e8m0(c13[e], s13[e]).double()
+        h = (x[tok].double() @ wd1).float().to(torch.bfloat16).float()
+        act = (torch.nn.functional.silu(h[:, :I]) * h[:, I:]).to(torch.bfloat16)
+        wd2 = fp4_dequant_e8m0(c2[e], s2[e]).double()
+        y = (act.double() @ wd2).float().to(torch.bfloat16).float()
+        out.index_add_(0, tok, y * wts[tok, slot].unsqueeze(-1))
+    return out.to(torch.bfloat16)

@@ -1,6 +1,6 @@
 """Generate the golden fixtures of this directory from the reference's own Python test helpers.
 
-Run once, in a container where the reference checkout is present:
+Run once, where the reference checkout is present:
 
     python tests/golden/make_golden.py /path/to/reference
 
@@ -18,6 +18,9 @@ Outputs (all small, ``np.savez_compressed``):
   gemm_fp4.npz         the reference fp4 pipeline (quantise, pack, repack, scale fold) on a
                        seeded case plus a uniform-random-code case
   gemv_fp8.npz / gemv_fp4.npz   the GEMV goldens (fp32 weights kept for fp8)
+  scale_fold.npz       the two-level FP4 scale fold (anti_quant_fp8_scale + transpose) on seeded
+                       scales, with one and with two global scales per expert
+                       (``--only scale_fold`` writes this file alone)
 """
 import ast
 import os
@@ -64,7 +67,27 @@ def grouped_matmul_f32(x, wd, cumsum):
     return out
 
 
-def main(ref):
+def scale_fold_fixture(g4):
+    """anti_quant_fp8_scale (test_group_gemm_fp4.py:86-94) followed by the transpose of :186."""
+    gen = torch.Generator().manual_seed(41)
+    out = {}
+    for tag, G, N, KB, S in (("one", 3, 64, 8, 1), ("two", 2, 96, 12, 2)):
+        block = (torch.randn(G, N, KB, generator=gen) * 100).clamp(-448, 448).to(torch.bfloat16)
+        glob = (torch.rand(G, S, 1, generator=gen) * 0.01 + 1e-4).to(torch.float32)
+        folded = g4["anti_quant_fp8_scale"](block.clone(), glob)      # bf16 [G, N, K/16]
+        new_scale = folded.transpose(-2, -1).contiguous()              # [G, K/16, N]
+        out[f"{tag}_block_bits"] = bits(block)
+        out[f"{tag}_global"] = glob.numpy()
+        out[f"{tag}_folded_bits"] = bits(new_scale)
+    np.savez_compressed(f"{HERE}/scale_fold.npz", **out)
+
+
+def main(ref, only=None):
+    if only == "scale_fold":
+        g4 = lift(f"{ref}/grouped_gemm/test/python/test_group_gemm_fp4.py", ["anti_quant_fp8_scale"])
+        scale_fold_fixture(g4)
+        print("scale_fold.npz", os.path.getsize(f"{HERE}/scale_fold.npz"))
+        return
     g8 = lift(f"{ref}/grouped_gemm/test/python/test_group_gemm_fp8.py", ["anti_quant_fp8"])
     v8 = lift(f"{ref}/grouped_soft_gemv/test/python/test_group_soft_gemv_fp8.py", ["anti_quant_fp8"])
     g4 = lift(
@@ -154,10 +177,17 @@ def main(ref):
     b = fp4_case(34, 256, 4, torch.tensor([1, 2, 3, 4], dtype=torch.int64), True)
     np.savez_compressed(f"{HERE}/gemv_fp4.npz", **{f"ref_{k}": v for k, v in a.items()},
                         **{f"uni_{k}": v for k, v in b.items()})
+    scale_fold_fixture(g4)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(f"{HERE}/{f}"))
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    import argparse
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("reference", help="path of the reference checkout")
+    ap.add_argument("--only", choices=["scale_fold"], default=None, help="write this fixture alone")
+    ns_ = ap.parse_args()
+    main(ns_.reference, only=ns_.only)

@@ -48,6 +48,14 @@ def test_argument_validation_returns_status_codes(fn):
     assert call(ws=None) == 5 and call(wsb=8) == 5
     assert call(glt=5) == 6 and call(lay=7) == 6
     assert call(M=0) == 0                       # nothing to do, nothing launched
+    # fp8 takes what the reference takes (N % 128 == 0); the other modes need whole 256-column tiles
+    assert call(ct=0, N=384, M=0) == 0 and call(ct=0, N=448, M=0) == 3
+    assert call(ct=2, N=384, M=0) == 3 and call(ct=1, N=384, M=0) == 3
+    if fn == "b200moe_grouped_gemm":
+        assert call(ct=4, M=0) == 0             # bf16: the matmul phase alone
+        assert call(ct=4, ptrs=[P, P, None, None, P, P], M=8, ws=None) == 5   # no scale needed; reaches the workspace check
+    else:
+        assert call(ct=4) == 1                  # the GEMV has no bf16 mode
 
 
 def test_dequant_validation():
@@ -57,6 +65,16 @@ def test_dequant_validation():
     assert abi.lib.b200moe_fp4_dequant(P, None, P, 64, 5, None) == 6
     assert abi.lib.b200moe_fp4_dequant(None, None, None, 0, 0, None) == 0
     assert abi.lib.b200moe_fp4_layout(P, P, 1, 100, 256, 1, None) == 3
+    assert abi.lib.b200moe_fp8_dequant(P, P, P, 1, 192, 256, None) == 3          # K % 128
+    assert abi.lib.b200moe_fp8_dequant(P, P, P, 1, 128, 384, None) != 3          # N % 128 is enough
+    assert abi.lib.b200moe_fp8_dequant(P, None, P, 1, 128, 128, None) == 2
+    assert abi.lib.b200moe_fp4_dequant_bf16_scale(P, P, P, 1, 64, 128, 0, None) == 3
+    assert abi.lib.b200moe_fp4_dequant_bf16_scale(P, P, P, 1, 64, 256, 3, None) == 6
+    assert abi.lib.b200moe_fp4_scale_fold(P, P, P, 2, 64, 8, 3, None) == 3       # one or two global scales
+    assert abi.lib.b200moe_fp4_scale_fold(P, P, P, 0, 64, 8, 1, None) == 0
+    assert abi.lib.b200moe_pack_weight_int8(P, P, 1, 100, 256, 0, None) == 3
+    assert abi.lib.b200moe_grouped_gemm_int8_packed(P, P, P, None, P, P, 8, 64, 128, 1, 0, 0, P, 1 << 20, None) == 3
+    assert abi.lib.b200moe_grouped_gemm_int8_packed(P, P, P, None, P, P, 0, 64, 256, 1, 0, 0, P, 1 << 20, None) == 0
 
 
 def test_python_mirror_rejects_cpu_tensors_and_bad_compute_type():

@@ -309,6 +309,54 @@ def test_layer_on_packed_weights_agrees_with_the_drop_in_operator_path():
 
 
 @pytest.mark.gpu
+def test_layer_on_fp4_stored_experts_matches_oracle():
+    """Experts stored as FP4 e2m1 with e8m0 block scales, dequantised to bf16 in every pass and multiplied by
+    the bf16 grouped GEMM, against the CPU golden of the same two phases."""
+    from ascend_kernel_b200.moe_layer import MoELayer
+
+    gen = torch.Generator().manual_seed(9)
+    T, H, E, I, k = 300, 256, 8, 256, 2
+    x = torch.randn(T, H, generator=gen).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=gen).to(torch.bfloat16)
+    c13 = torch.randint(0, 256, (E, H, I), generator=gen, dtype=torch.uint8)
+    s13 = torch.randint(119, 128, (E, H, 2 * I // 32), generator=gen, dtype=torch.uint8)
+    c2 = torch.randint(0, 256, (E, I, H // 2), generator=gen, dtype=torch.uint8)
+    s2 = torch.randint(119, 128, (E, I, H // 32), generator=gen, dtype=torch.uint8)
+    layer = MoELayer(c13.cuda(), s13.cuda(), None, c2.cuda(), s2.cuda(), None, E, k, weight_format="fp4")
+    out = layer.forward(x.cuda(), logits.cuda())
+    torch.cuda.synchronize()
+    layer.read_status()
+    # the layer's bf16 weight buffers hold the exact dequantised values
+    assert torch.equal(layer.bf13.cpu().view(torch.int16), O.fp4_dequant_e8m0(c13, s13).view(torch.int16))
+    gold = O.moe_layer_fp4_stored(x, logits, c13, s13, c2, s2, k)
+    close(out.cpu(), gold)
+    with pytest.raises(ValueError):
+        MoELayer(c13.cuda(), s13.cuda(), s13.cuda(), c2.cuda(), s2.cuda(), None, E, k, weight_format="fp4")
+
+
+@pytest.mark.gpu
+def test_layer_reports_device_findings():
+    """MoELayer.read_status raises when a kernel of an earlier pass left a finding (here: a grouped GEMM
+    called directly with a group list that is not monotone) and is quiet otherwise."""
+    import ascend_kernel_b200 as ak
+    from ascend_kernel_b200.moe_layer import MoELayer
+
+    c = small_case(T=64, H=256, E=8, I=256, k=2)
+    d = {k_: (v.cuda() if torch.is_tensor(v) else v) for k_, v in c.items()}
+    layer = MoELayer(d["w13"], d["s13"], d["o13"], d["w2"], d["s2"], d["o2"], c["E"], c["top_k"])
+    ak.check_status()
+    layer.forward(d["x"], d["logits"])
+    assert layer.read_status() == (0, 0)
+    out = torch.zeros(64, 512, dtype=torch.bfloat16, device="cuda")
+    bad = torch.tensor([40, 3, 3, 3, 3, 3, 3, 3], dtype=torch.int64, device="cuda")  # cumulative list going down
+    ak.grouped_gemm(d["x"], d["w13"], d["s13"], d["o13"], bad, "int8", out)
+    layer.forward(d["x"], d["logits"])
+    with pytest.raises(RuntimeError, match="group list"):
+        layer.read_status()
+    assert layer.read_status() == (0, 0)
+
+
+@pytest.mark.gpu
 def test_aux_kernels_match_torch():
     import ascend_kernel_b200 as ak
 

@@ -120,3 +120,11 @@ def test_e8m0_dequant_exact():
     ex = v * torch.pow(2.0, sc.double() - 127).repeat_interleave(32, dim=-1)
     assert torch.equal(out.double(), ex)
     assert torch.equal(O.fp4_dequant_e8m0(codes, None).double(), v)
+
+
+def test_scale_fold_matches_reference_helper():
+    """The two-level FP4 scale fold against the output of the reference's own anti_quant_fp8_scale."""
+    d = load("scale_fold.npz")
+    for tag in ("one", "two"):
+        got = O.fp4_scale_fold(bf16(d[tag + "_block_bits"]), torch.from_numpy(d[tag + "_global"]))
+        assert same_bits(got, bf16(d[tag + "_folded_bits"])), tag

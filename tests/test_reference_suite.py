@@ -7,8 +7,9 @@ import sys
 
 import pytest
 
-REF = os.environ.get("ASCEND_KERNEL_REFERENCE", "/root/reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
+# the reference checkout: $ASCEND_KERNEL_REFERENCE, else a directory `reference` beside this repository
+REF = os.environ.get("ASCEND_KERNEL_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 SCRIPTS = [
     "grouped_gemm/test/python/test_group_gemm_fp8.py",
