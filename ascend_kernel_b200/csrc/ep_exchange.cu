@@ -22,9 +22,11 @@
 // its counts only after its own combine of step n, and nobody writes rows before it has seen the
 // counts of every rank.
 //
-// Every wait is bounded (ptx::kWaitLimitNs): on expiry the kernel records status 2 and carries on
-// with whatever is there; all addresses are computed locally and clamped to the buffer capacity,
-// so a missing peer can produce wrong numbers but never a fault or a hang.  Peer memory is only
+// Every wait is bounded (ptx::kWaitLimitNs): on expiry the kernel records status 2, stores no rows into
+// any rank's buffers (dispatch) or treats the missing results as absent rows (combine), and still posts
+// its own signals; all addresses are computed locally and clamped to the buffer capacity, so a
+// missing peer can produce wrong numbers on the rank that waited but never a fault, a hang, or
+// overwritten buffers on a healthy rank.  Peer memory is only
 // touched with plain loads and stores (no TMA, no multicast).
 #include <cstring>
 
@@ -127,7 +129,10 @@ ep_dispatch_kernel(EpComm c, const uint4* __restrict__ x, const int32_t* __restr
                    long long* __restrict__ n_recv, int* __restrict__ done_counter) {
     __shared__ int s_start[kMaxExperts + 1], s_base[kMaxExperts], s_tot[kMaxExperts], s_before[kMaxExperts];
     step = ep_step(c, step);
-    (void)ep_wait_all(c, kSigCounts, step, 1);
+    // If the counts of some rank never arrive the plan below would be built from a stale table: no row is
+    // stored anywhere then (a healthy peer's buffers must not be overwritten by a rank that is out of step);
+    // the local outputs are still written and the rows signal is still posted, so nobody waits for this rank.
+    const bool counts_ok = ep_wait_all(c, kSigCounts, step, 1);
     const int E = c.n_experts;
     const int32_t* tab = c.counts[c.rank];
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -175,10 +180,10 @@ ep_dispatch_kernel(EpComm c, const uint4* __restrict__ x, const int32_t* __restr
         }
         const int e = lo, d = e / c.e_local;
         const long long pos = (long long)s_base[e] + (i - s_start[e]);
-        const bool fits = i < s_start[E] && pos < c.cap_rows;
+        const bool fits = counts_ok && i < s_start[E] && pos < c.cap_rows;
         if (lane == 0) remote_pos[i] = fits ? (int32_t)(d * c.cap_rows + pos) : -1;
         if (!fits) {
-            if (lane == 0 && atomicCAS(c.status, kDevOk, kDevBadGroupList) == kDevOk) c.status[1] = e;
+            if (counts_ok && lane == 0 && atomicCAS(c.status, kDevOk, kDevBadGroupList) == kDevOk) c.status[1] = e;
             continue;
         }
         const uint4* src = x + (long long)token_of[i] * c.width16;
@@ -201,13 +206,14 @@ ep_dispatch_kernel(EpComm c, const uint4* __restrict__ x, const int32_t* __restr
 __global__ void ep_combine_kernel(EpComm c, const int32_t* __restrict__ remote_pos, const int32_t* __restrict__ slot,
                                   const float* __restrict__ weight, uint4* __restrict__ out, int top_k,
                                   unsigned long long step) {
-    (void)ep_wait_all(c, kSigResults, ep_step(c, step), 2);
+    // results that were never signalled complete are not read: their rows count as absent
+    const bool results_ok = ep_wait_all(c, kSigResults, ep_step(c, step), 2);
     const long long t = blockIdx.x;
     __shared__ const uint4* s_row[32];
     __shared__ float s_w[32];
     if ((int)threadIdx.x < top_k) {
         const int rp = remote_pos[slot[t * top_k + threadIdx.x]];
-        s_row[threadIdx.x] = rp < 0 ? nullptr : c.y[rp / c.cap_rows] + (rp % c.cap_rows) * c.width16;
+        s_row[threadIdx.x] = (rp < 0 || !results_ok) ? nullptr : c.y[rp / c.cap_rows] + (rp % c.cap_rows) * c.width16;
         s_w[threadIdx.x] = weight[t * top_k + threadIdx.x];
     }
     __syncthreads();

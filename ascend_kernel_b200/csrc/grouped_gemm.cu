@@ -1077,6 +1077,10 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[B200MOE_STATUS_
 
 // Device address of the scratch array on the current device, resolved once per device.  The array's
 // name is only a host-side handle: a kernel must be given the address cudaGetSymbolAddress returns.
+// This lookup and the first launch of the kernel on a device (the driver loads the kernel image, with
+// the array in it, at that point) are the set-up a warm-up call gets out of the way: callers make one
+// call per device before their allocation-free phase and before any stream capture.  The cached
+// address is valid for the life of the process, not across a device reset.
 static int noalloc_scratch(void** out) {
     static void* addr[64];
     static std::mutex mu;

@@ -139,8 +139,12 @@ int b200moe_grouped_gemm_int8_packed(const void* x, const void* packed, const vo
  * 256 B + 4 B x b200moe_grouped_gemm_int8_noalloc_max_rows() = 256.25 KiB held on every GPU that
  * loads the library, until the process exits.  M beyond that limit returns
  * B200MOE_ERR_NOALLOC_LIMIT and launches nothing.  The call performs no cudaMalloc / cudaFree and
- * uses no allocating library routine.  The first call on each device looks up the array's device
- * address (cudaGetSymbolAddress): make that first call before any stream capture begins.  All calls
+ * uses no allocating library routine.  The FIRST call on each device does set-up work that is not
+ * allocation-free: it looks up the array's device address (cudaGetSymbolAddress) and, being the
+ * first launch of the kernel there, makes the driver load the kernel image (with the array in it),
+ * which takes device memory.  So make one warm-up call per device before the phase in which nothing
+ * may be allocated, and before any stream capture begins.  The looked-up address is cached per
+ * device for the life of the process; it does not survive a device reset.  All calls
  * share the one array: calls that overlap on the GPU (different streams) race on it; serialise
  * them.  The device status words of the last call can be read with b200moe_noalloc_read_status. */
 int b200moe_grouped_gemm_int8_noalloc(const void* x, const void* weight, const void* scale, const void* offset,

@@ -446,6 +446,22 @@ def test_peer_memory_wait_expires_with_status_instead_of_hanging():
     assert 1.0 < time.time() - t0 < 10.0
     assert p2p.px.read_status()[0] == 2
     p2p.px.status.zero_()
+    # a dispatch whose counts never arrive (a step was opened, nobody posted counts) stores no row anywhere,
+    # and a combine whose results are never signalled reads none: the buffers keep what they held
+    from ascend_kernel_b200 import ops
+
+    p2p.px.recv_x.fill_(-3.0)
+    p2p.px.y.fill_(-5.0)
+    p2p.px.begin_step()
+    _, wts, _, token_of, slot = ops.moe_route(d["logits"], c["top_k"])
+    remote_pos, _, _ = p2p.px.dispatch(d["x"], token_of)
+    late = p2p.px.combine(remote_pos, slot, wts)
+    torch.cuda.synchronize()
+    assert p2p.px.read_status()[0] == 2
+    assert bool((remote_pos == -1).all())
+    assert bool((p2p.px.recv_x == -3.0).all()) and bool((p2p.px.y == -5.0).all())
+    assert bool((late == 0).all())
+    p2p.px.status.zero_()
     out = p2p.forward(d["x"], d["logits"])
     want = MoELayer(*w, c["E"], c["top_k"]).forward(d["x"], d["logits"])
     torch.cuda.synchronize()

@@ -64,6 +64,36 @@ def test_two_calls_in_a_row_match_the_regular_entry_point():
         assert torch.equal(got.view(torch.int16), want.view(torch.int16))
 
 
+def test_a_warmed_up_call_takes_no_device_memory():
+    """After one warm-up call on the device (which loads the kernel image and looks up the scratch array's
+    address), further calls leave the free device memory and torch's allocation count exactly as they
+    were: nothing is allocated, by the driver or by torch, on behalf of the call."""
+    from ascend_kernel_b200 import _abi
+
+    x, w, scale, offset, counts = _case([40, 0, 260], 128, 256, 21, True)
+    M, K = x.shape
+    G, _, N = w.shape
+    y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        rc = _abi.lib.b200moe_grouped_gemm_int8_noalloc(x.data_ptr(), w.data_ptr(), scale.data_ptr(), offset.data_ptr(),
+                                                        counts.data_ptr(), y.data_ptr(), M, K, N, G, 1, stream)
+        assert rc == 0, _abi.strerror(rc)
+
+    call()                       # warm-up: module load, symbol lookup
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    live0 = torch.cuda.memory_stats()["allocation.all.current"]
+    reserved0 = torch.cuda.memory_reserved()
+    for _ in range(2):
+        call()
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free0
+        assert torch.cuda.memory_stats()["allocation.all.current"] == live0
+        assert torch.cuda.memory_reserved() == reserved0
+
+
 def test_rejects_more_rows_than_the_scratch_holds():
     from ascend_kernel_b200 import _abi
 
