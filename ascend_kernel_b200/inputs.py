@@ -2,7 +2,10 @@
 configurations (DeepSeek-V3 is only a shape donor; no dataset is involved).
 
 Small cases are drawn on the CPU (so the CPU oracle and the GPU path see identical bits on any
-machine) and moved to ``device``; full-size tensors are drawn directly on ``device``.
+machine) and moved to ``device``; full-size tensors are drawn directly on ``device``, except the MoE
+layer's weights, which are a hash of the element index and so have the same bits wherever they are
+materialised.  This module imports nothing but torch: the benchmark's CPU arm loads it by path, without
+importing the package (and with it the CUDA library).
 """
 from __future__ import annotations
 
@@ -17,6 +20,46 @@ def _gen(seed, device):
 
 def _uniform(shape, lo, hi, gen, device, dtype=torch.bfloat16):
     return (torch.rand(shape, generator=gen, device=device) * (hi - lo) + lo).to(dtype)
+
+
+# ---- counter-based values: the same bits on the CPU and on a GPU ------------------------------------
+# torch's CPU and CUDA generators are different algorithms, so tensors drawn on the device cannot be
+# reproduced on the host.  Where both sides must see the same bits (the benchmark's CPU arm and GPU arm)
+# values are a hash of (seed, element index) instead: splitmix64's finaliser in int64 tensor arithmetic,
+# which wraps the same way on both devices.
+def _mix64(idx, seed: int):
+    m34, m37, m33 = (1 << 34) - 1, (1 << 37) - 1, (1 << 33) - 1
+    g = (seed * 0x9E3779B97F4A7C15 + 0x632BE59BD9B4E019) & 0x7FFFFFFFFFFFFFFF
+    z = idx + g
+    z = (z ^ ((z >> 30) & m34)) * -4658895280553007687    # 0xBF58476D1CE4E5B9 as int64
+    z = (z ^ ((z >> 27) & m37)) * -7723592293110705685    # 0x94D049BB133111EB as int64
+    return z ^ ((z >> 31) & m33)
+
+
+def hashed_bytes(shape, seed: int, device, dtype=torch.uint8):
+    """Bytes uniform over 0..255 (int8: -128..127), identical on every device, in chunks that bound the
+    int64 temporaries."""
+    n = 1
+    for d in shape:
+        n *= int(d)
+    out = torch.empty(n, dtype=torch.uint8, device=device)
+    step = 1 << 24
+    for i in range(0, n, step):
+        idx = torch.arange(i, min(n, i + step), dtype=torch.int64, device=device)
+        out[i:i + idx.numel()] = (_mix64(idx, seed) & 0xFF).to(torch.uint8)
+    out = out.reshape(shape)
+    return out.view(torch.int8) if dtype == torch.int8 else out
+
+
+def hashed_uniform(shape, lo: float, hi: float, seed: int, device, dtype=torch.bfloat16):
+    """lo + (hi - lo) * u with u a 24-bit fraction of the hash, in float32 (one multiply, one add, each
+    rounded on its own: the same on every device), then cast."""
+    n = 1
+    for d in shape:
+        n *= int(d)
+    idx = torch.arange(n, dtype=torch.int64, device=device)
+    u = ((_mix64(idx, seed) >> 8) & 0xFFFFFF).to(torch.float32) * (1.0 / (1 << 24))
+    return (u * (hi - lo) + lo).to(dtype).reshape(shape)
 
 
 def int8_weights(G, K, N, gen, device):
@@ -133,8 +176,9 @@ def config3_variants(device, kind, n_rows=65536, n_experts=256, K=7168, N=4096, 
 
 def config4(device, n_tokens=4096, hidden=7168, n_experts=256, inter=2048, top_k=8, seed=4,
             expert_lo=0, expert_hi=None):
-    """MoE FFN layer inputs.  Tokens and router logits are global; weights are drawn per expert so
-    a rank can materialise only its own slice [expert_lo, expert_hi) with identical values."""
+    """MoE FFN layer inputs.  Tokens and router logits are global (CPU generator); the weights of expert
+    e are a hash of (seed, e, element index), so a rank can materialise only its own slice
+    [expert_lo, expert_hi) and the CPU golden path can materialise single experts with the same bits."""
     expert_hi = n_experts if expert_hi is None else expert_hi
     gen = _gen(seed, "cpu")
     x = torch.randn(n_tokens, hidden, generator=gen).to(torch.bfloat16)
@@ -147,15 +191,22 @@ def config4(device, n_tokens=4096, hidden=7168, n_experts=256, inter=2048, top_k
     s2 = torch.empty(n_local, hidden, dtype=torch.bfloat16, device=device)
     o2 = torch.empty_like(s2)
     for e in range(expert_lo, expert_hi):
-        ge = _gen(seed * 100003 + e, device)
-        i = e - expert_lo
-        w13[i] = torch.randint(-128, 128, (hidden, 2 * inter), generator=ge, device=device, dtype=torch.int8)
-        w2[i] = torch.randint(-128, 128, (inter, hidden), generator=ge, device=device, dtype=torch.int8)
-        s13[i] = _uniform((2 * inter,), 0.001, 0.01, ge, device)
-        o13[i] = _uniform((2 * inter,), -4.0, 4.0, ge, device)
-        s2[i] = _uniform((hidden,), 0.001, 0.01, ge, device)
-        o2[i] = _uniform((hidden,), -4.0, 4.0, ge, device)
+        i, se = e - expert_lo, (seed * 100003 + e) * 8
+        w13[i] = hashed_bytes((hidden, 2 * inter), se, device, torch.int8)
+        w2[i] = hashed_bytes((inter, hidden), se + 1, device, torch.int8)
+        s13[i] = hashed_uniform((2 * inter,), 0.001, 0.01, se + 2, device)
+        o13[i] = hashed_uniform((2 * inter,), -4.0, 4.0, se + 3, device)
+        s2[i] = hashed_uniform((hidden,), 0.001, 0.01, se + 4, device)
+        o2[i] = hashed_uniform((hidden,), -4.0, 4.0, se + 5, device)
     return dict(x=x, logits=logits, w13=w13, s13=s13, o13=o13, w2=w2, s2=s2, o2=o2, top_k=top_k)
+
+
+def config4_tokens(n_tokens=4096, hidden=7168, n_experts=256, seed=4):
+    """Only the tokens and router logits of config4 (bf16, CPU)."""
+    gen = _gen(seed, "cpu")
+    x = torch.randn(n_tokens, hidden, generator=gen).to(torch.bfloat16)
+    logits = torch.randn(n_tokens, n_experts, generator=gen).to(torch.bfloat16)
+    return x, logits
 
 
 def config4_fp4(device, n_tokens=4096, hidden=7168, n_experts=256, inter=2048, top_k=8, seed=4,
@@ -174,10 +225,9 @@ def config4_fp4(device, n_tokens=4096, hidden=7168, n_experts=256, inter=2048, t
     c2 = torch.empty(n_local, inter, hidden // 2, dtype=torch.uint8, device=device)       # [E, I, H/2]
     s2 = torch.empty(n_local, inter, hidden // 32, dtype=torch.uint8, device=device)
     for e in range(expert_lo, expert_hi):
-        ge = _gen(seed * 100003 + 50000 + e, device)
-        i = e - expert_lo
-        c13[i] = torch.randint(0, 256, c13.shape[1:], generator=ge, device=device, dtype=torch.uint8)
-        s13[i] = torch.randint(119, 128, s13.shape[1:], generator=ge, device=device, dtype=torch.uint8)
-        c2[i] = torch.randint(0, 256, c2.shape[1:], generator=ge, device=device, dtype=torch.uint8)
-        s2[i] = torch.randint(119, 128, s2.shape[1:], generator=ge, device=device, dtype=torch.uint8)
+        i, se = e - expert_lo, (seed * 100003 + 50000 + e) * 8
+        c13[i] = hashed_bytes(c13.shape[1:], se, device)
+        s13[i] = 119 + hashed_bytes(s13.shape[1:], se + 1, device) % 9
+        c2[i] = hashed_bytes(c2.shape[1:], se + 2, device)
+        s2[i] = 119 + hashed_bytes(s2.shape[1:], se + 3, device) % 9
     return dict(x=x, logits=logits, c13=c13, s13=s13, c2=c2, s2=s2, top_k=top_k)

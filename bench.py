@@ -36,7 +36,21 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 CFG = dict(n_tokens=4096, hidden=7168, n_experts=256, inter=2048, top_k=8, seed=4)
+# dram bytes / algorithmic bytes of the layer's grouped GEMMs, from a profiler capture of a small case
+DRAM_OVER_ALGORITHMIC = 1.08
+CPU_SAMPLE_EVERY = 32  # the CPU legs time every 32nd expert by load rank (8 of 256) with all its routed rows
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def inputs_module():
+    """ascend_kernel_b200/inputs.py loaded by path: it needs only torch, and importing it through the
+    package would load the CUDA library, which the CPU arm must not map."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("_b200moe_inputs", os.path.join(ROOT, "ascend_kernel_b200", "inputs.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
 
 
 def load_peaks():
@@ -106,9 +120,9 @@ def cpu_sample_inputs(every: int):
     """Routing of the full configuration; weights only for every `every`-th expert by load rank."""
     import torch
 
-    from ascend_kernel_b200 import inputs
     from oracle import oracle as O
 
+    inputs = inputs_module()
     c = inputs.config4("cpu", expert_lo=0, expert_hi=0, **CFG)
     wts, idx = O.route_topk(c["logits"], CFG["top_k"])
     counts = torch.bincount(idx.reshape(-1), minlength=CFG["n_experts"])
@@ -170,7 +184,7 @@ def run_reference(args):
     import torch
 
     threads = use_all_host_cores()
-    every = 32
+    every = CPU_SAMPLE_EVERY
     prepared = cpu_sample_inputs(every)
     for _ in range(args.warmup):
         cpu_moe_sample(every, prepared)
@@ -205,9 +219,15 @@ def workload_config(n_gpus):
 # ------------------------------------------------------------------------------------------------
 # per-kernel lines (N = 1)
 # ------------------------------------------------------------------------------------------------
-def time_launches(fn, n_warm, n_iter):
-    """Median CUDA-event time of one call of fn (its own kernels only), after an idle second so a
-    kernel timed alone is not measured at the power-capped clock the previous one left behind."""
+LAST_BACK_TO_BACK_MS = None
+
+
+def time_launches(fn, n_warm, n_iter, n_sustained=50):
+    """CUDA-event time of one call of fn (its own kernels only): the median of the first n_iter calls after
+    an idle second (the clocks a kernel timed alone sees), which is returned, and the median of
+    n_sustained further calls issued back to back (the clocks inside a long run, usually under the power
+    cap), left in LAST_BACK_TO_BACK_MS."""
+    global LAST_BACK_TO_BACK_MS
     import torch
 
     torch.cuda.synchronize()
@@ -215,13 +235,15 @@ def time_launches(fn, n_warm, n_iter):
     for _ in range(n_warm):
         fn()
     torch.cuda.synchronize()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_iter)]
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_iter + n_sustained)]
     for a, b in evs:
         a.record()
         fn()
         b.record()
     torch.cuda.synchronize()
-    return statistics.median(a.elapsed_time(b) for a, b in evs)
+    times = [a.elapsed_time(b) for a, b in evs]
+    LAST_BACK_TO_BACK_MS = statistics.median(times[n_iter:]) if n_sustained else None
+    return statistics.median(times[:n_iter])
 
 
 def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
@@ -245,7 +267,7 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
                                                group_list_type=1), 3, 10)
       flops = 2.0 * M * K * N
       out["grouped_gemm_prefill_int8"] = {
-        "ms": ms, "tflops": flops / ms / 1e9, "frac_of_measured_sustained": flops / ms / 1e9 / peaks["bf16_tflops_sustained"],
+        "ms": ms, "ms_back_to_back": LAST_BACK_TO_BACK_MS, "tflops": flops / ms / 1e9, "frac_of_measured_sustained": flops / ms / 1e9 / peaks["bf16_tflops_sustained"],
         "frac_of_measured_burst": flops / ms / 1e9 / peaks["bf16_tflops"], "frac_of_spec_2250": flops / ms / 1e9 / 2250.0,
         "shape": {"M": M, "K": K, "N": N, "G": G, "active_experts": int((c["counts"] > 0).sum())}}
     # ---- decode grouped GEMV (configuration 1): reuse the weight tensor ----
@@ -259,7 +281,7 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
       ms = time_launches(lambda: ak.grouped_soft_gemv(xv, c["weight"], c["scale"], counts, "int8", yv,
                                                     group_list_type=1), 3, 10)
       by = n_act * K * N + 2.0 * Mv * K + 2.0 * Mv * N + n_act * N * 2
-      out["grouped_gemv_decode_int8_pass1"] = {"ms": ms, "gbs": by / ms / 1e6, "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
+      out["grouped_gemv_decode_int8_pass1"] = {"ms": ms, "ms_back_to_back": LAST_BACK_TO_BACK_MS, "gbs": by / ms / 1e6, "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
                                              "frac_of_spec_8000": by / ms / 1e6 / 8000.0,
                                              "shape": {"M": Mv, "K": K, "N": N, "G": G, "active_experts": n_act}}
     del c, y, xv, yv
@@ -279,9 +301,10 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
             off = c["offset"] if kind == "int4" else torch.zeros(1, device=dev)
             fn = (lambda: ak.grouped_gemm(c["x"], c["weight"], c["scale"], off, gl, kind, y,
                                           group_list_type=1 if kind == "int4" else 0, weight_layout=layout))
-            ms = time_launches(fn, 2, 5)
+            ms = time_launches(fn, 2, 5, 50)
             flops = 2.0 * M * K * N
-            out[f"grouped_gemm_prefill_{name}"] = {"ms": ms, "tflops": flops / ms / 1e9,
+            out[f"grouped_gemm_prefill_{name}"] = {"ms": ms, "ms_back_to_back": LAST_BACK_TO_BACK_MS, "tflops": flops / ms / 1e9,
+                                                   "frac_of_measured_burst": flops / ms / 1e9 / peaks["bf16_tflops"],
                                                    "frac_of_measured_sustained": flops / ms / 1e9 / peaks["bf16_tflops_sustained"]}
             del c, y
             torch.cuda.empty_cache()
@@ -294,7 +317,7 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
         y2 = torch.empty(Mv, N2, dtype=torch.bfloat16, device=dev)
         ms = time_launches(lambda: ak.grouped_soft_gemv(x2, w2, s2, counts, "int8", y2, group_list_type=1), 3, 10)
         by = n_act * K2 * N2 + 2.0 * Mv * K2 + 2.0 * Mv * N2 + n_act * N2 * 2
-        out["grouped_gemv_decode_int8_pass2"] = {"ms": ms, "gbs": by / ms / 1e6, "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
+        out["grouped_gemv_decode_int8_pass2"] = {"ms": ms, "ms_back_to_back": LAST_BACK_TO_BACK_MS, "gbs": by / ms / 1e6, "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
                                                  "frac_of_spec_8000": by / ms / 1e6 / 8000.0,
                                                  "shape": {"M": Mv, "K": K2, "N": N2, "G": G, "active_experts": n_act}}
         del w2, s2, x2, y2
@@ -321,7 +344,7 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
             ms = time_launches(lambda: ak.grouped_soft_gemv(x1, w1, s1, counts, kind, y1, group_list_type=1,
                                                             weight_layout=layout), 3, 10)
             by = n_act * K1 * cols + sbytes + 2.0 * Mv * K1 + 2.0 * Mv * N1
-            out[f"grouped_gemv_decode_{name}"] = {"ms": ms, "gbs": by / ms / 1e6,
+            out[f"grouped_gemv_decode_{name}"] = {"ms": ms, "ms_back_to_back": LAST_BACK_TO_BACK_MS, "gbs": by / ms / 1e6,
                                                   "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
                                                   "shape": {"M": Mv, "K": K1, "N": N1, "G": G, "active_experts": n_act}}
             del w1, s1
@@ -335,10 +358,118 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
     o = torch.empty(n, dtype=torch.bfloat16, device=dev)
     ms = time_launches(lambda: ak.fp4_dequant(d["codes"], d["scale"], o), 3, 10)
     by = n * (0.5 + 1.0 / 32 + 2.0)
-    out["fp4_dequant_e8m0"] = {"ms": ms, "gbs": by / ms / 1e6, "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
+    out["fp4_dequant_e8m0"] = {"ms": ms, "ms_back_to_back": LAST_BACK_TO_BACK_MS, "gbs": by / ms / 1e6, "frac_of_measured": by / ms / 1e6 / peaks["hbm_gbs"],
                                "frac_of_spec_8000": by / ms / 1e6 / 8000.0, "elements": n}
     del d, o
     torch.cuda.empty_cache()
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# correctness of the measured configuration, outside every timed region
+# ------------------------------------------------------------------------------------------------
+def parity_check(out_dev, x_host, lg_host, dev, n_check=8, tol=4e-3):
+    """The CPU golden path on `n_check` of this rank's tokens against the layer's output `out_dev`
+    (the rows of this rank's tokens, on the device).  A token needs the weights of its top-k experts,
+    wherever they live: each is materialised on the device from its hash (the same bits every rank
+    holds), copied to the host and put through the float32 CPU formulas.  Returns (worst rel-L2, count)."""
+    import torch
+
+    from ascend_kernel_b200 import inputs
+    from oracle import oracle as O
+
+    lg = lg_host.float()
+    k = CFG["top_k"]
+    srt = torch.sort(lg, dim=1, descending=True)[0]
+    tie_free = (srt[:, k - 1] != srt[:, k]).nonzero().flatten().tolist()  # a tie at the boundary may go either way
+    toks = sorted({tie_free[int(round(i * (len(tie_free) - 1) / max(1, n_check - 1)))] for i in range(n_check)})
+    w, idx = O.route_topk(lg_host[toks], k)
+    I = CFG["inter"]
+    cache, worst = {}, 0.0
+    for i, t in enumerate(toks):
+        acc = torch.zeros(CFG["hidden"], dtype=torch.float64)
+        for j in range(k):
+            e = int(idx[i, j])
+            if e not in cache:
+                if len(cache) >= 12:
+                    cache.clear()
+                c = inputs.config4(dev, n_tokens=1, hidden=CFG["hidden"], n_experts=CFG["n_experts"], inter=I, top_k=k,
+                                   seed=CFG["seed"], expert_lo=e, expert_hi=e + 1)
+                cache[e] = {n: c[n][0].cpu() for n in ("w13", "s13", "o13", "w2", "s2", "o2")}
+            p = cache[e]
+            wd1 = (p["w13"].float() + p["o13"].float()) * p["s13"].float()
+            h = (x_host[t:t + 1].float() @ wd1).to(torch.bfloat16).float()
+            act = (torch.nn.functional.silu(h[:, :I]) * h[:, I:]).to(torch.bfloat16).float()
+            wd2 = (p["w2"].float() + p["o2"].float()) * p["s2"].float()
+            y = (act @ wd2).to(torch.bfloat16).double()
+            acc += float(w[i, j]) * y[0]
+        worst = max(worst, O.rel_l2(out_dev[t].cpu().double(), acc))
+    return worst, len(toks)
+
+
+def fp4_stored_line(peaks, steps=5, warmup=2):
+    """Configuration 4 with its experts STORED as FP4 e2m1 (+ e8m0 scale per 32) and dequantised to bf16
+    in every pass (the reference kernel's own two phases: dequantise to a bf16 buffer, then the bf16
+    grouped matmul).  One GPU, device-resident inputs."""
+    import torch
+
+    from ascend_kernel_b200 import inputs
+    from ascend_kernel_b200.moe_layer import MoELayer
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    c = inputs.config4_fp4(dev, **CFG)
+    layer = MoELayer(c["c13"], c["s13"], None, c["c2"], c["s2"], None, CFG["n_experts"], CFG["top_k"], weight_format="fp4")
+    x, lg = c["x"].to(dev), c["logits"].to(dev)
+    for _ in range(warmup):
+        layer.forward(x, lg)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        layer.forward(x, lg)
+    e1.record()
+    torch.cuda.synchronize()
+    layer.read_status()
+    ms = e0.elapsed_time(e1) / steps
+    E, H, I = CFG["n_experts"], CFG["hidden"], CFG["inter"]
+    elems = E * (H * 2 * I + I * H)
+    rows = CFG["n_tokens"] * CFG["top_k"]
+    # packed codes + scales in, bf16 weights out, bf16 weights in again, activations
+    by = elems * (0.5 + 1.0 / 32 + 2.0 + 2.0) + rows * 2.0 * (H + 2 * I + 2 * I + I + I + H)
+    return {"ms_per_step": ms, "tokens_per_s": CFG["n_tokens"] / (ms / 1e3), "steps": steps,
+            "roofline": {"bound": "hbm", "achieved": by / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": by / ms / 1e6 / peaks["hbm_gbs"], "algorithmic_bytes": by},
+            "what": "FP4 e2m1 experts (e8m0 scale per 32) -> bf16 buffers per pass (fp4_dequant_kernel) -> bf16 grouped GEMM"}
+
+
+def layer_gemm_case(quick: bool):
+    """The two expert GEMMs of the layer alone, on rows distributed like the layer's (128 +- 11 per expert):
+    a case for profiler captures (--quick: 32 experts, about 1.4 GB of weights)."""
+    import torch
+
+    from ascend_kernel_b200 import ops
+
+    dev = "cuda"
+    G = 32 if quick else 256
+    gen = torch.Generator(device=dev).manual_seed(0)
+    cnt = torch.clamp((torch.randn(G, generator=gen, device=dev) * 11.3 + 128).round(), 1, 400).to(torch.int64)
+    M = int(cnt.sum())
+    H, I = CFG["hidden"], CFG["inter"]
+    out = {"rows": M, "experts": G}
+    for name, K, N, gate_up in (("gate_up_silu", H, 2 * I, True), ("down", I, H, False)):
+        x = torch.randn(M, K, generator=gen, device=dev).to(torch.bfloat16)
+        w = torch.randint(-128, 128, (G, K, N), generator=gen, device=dev, dtype=torch.int8)
+        sc = (torch.rand(G, N, generator=gen, device=dev) * 0.009 + 0.001).to(torch.bfloat16)
+        of = (torch.rand(G, N, generator=gen, device=dev) * 8 - 4).to(torch.bfloat16)
+        wp = ops.pack_weight_int8(w, gate_up=gate_up)
+        del w
+        y = torch.empty(M, N // 2 if gate_up else N, dtype=torch.bfloat16, device=dev)
+        ms = time_launches(lambda: ops.grouped_gemm_packed(x, wp, sc, of, cnt, y, group_list_type=1, gate_up_silu=gate_up),
+                           3, 10, 0)
+        out[name] = {"ms": ms, "tflops": 2.0 * M * K * N / ms / 1e9,
+                     "algorithmic_bytes": G * K * N + 2.0 * M * K + 2.0 * M * (N // 2 if gate_up else N) + 4.0 * G * N}
+        del x, wp, y
+        torch.cuda.empty_cache()
     return out
 
 
@@ -397,7 +528,14 @@ def run_ours(args):
 
     # ---- device-resident timing ----
     for _ in range(args.warmup):
-        layer.forward(x, lg)
+        out_dev = layer.forward(x, lg)
+    barrier()
+    # correctness of exactly this configuration (all ranks, the exchange in use), before anything is timed
+    worst, n_checked = parity_check(out_dev, x_host, lg_host, dev)
+    worst = max_over_ranks(worst)
+    parity = {"tokens": n_checked * world, "rel_l2_max": worst, "tol": 4e-3, "ok": bool(worst <= 4e-3),
+              "against": "CPU golden path (float32) on sampled tokens of every rank, experts fetched wherever they live"}
+    del out_dev
     barrier()
     ops.LAUNCHES = 0
     gemm_ms, gemm_events, phase_events = 0.0, [], []
@@ -467,42 +605,55 @@ def run_ours(args):
     gemm_ms_step = gemm_ms / max(1, len(gemm_events))
     H_, I_ = CFG["hidden"], CFG["inter"]
     algo_bytes = (E / world) * (H_ * 2 * I_ + I_ * H_) + rows_local * 2.0 * (H_ + 2 * I_ + I_ + H_)
-    traffic = 1.08 * algo_bytes
+    traffic = DRAM_OVER_ALGORITHMIC * algo_bytes
     achieved = flops_step / gemm_ms_step / 1e9 if gemm_ms_step > 0 else 0.0
-    roofline = {"bound": "tensor", "kernel": "grouped_gemm_kernel<int8> (2 launches per step, rank 0)",
+    sm_mhz = clk.result.get("sm_mhz")
+    roofline = {"bound": "tensor", "kernel": "grouped_gemm_packed_kernel (2 launches per step, rank 0)",
                 "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops_sustained"], "peak_kind": f"{peak_kind} (sustained cuBLAS bf16)",
+                "frac_burst": achieved / peaks["bf16_tflops"], "peak_burst": peaks["bf16_tflops"],
+                "frac_of_spec_2250": achieved / 2250.0,
                 "traffic": traffic, "traffic_unit": "bytes per step (both launches)",
-                "traffic_source": "algorithmic bytes (weights once + x + y) x 1.08, the dram bytes / algorithmic bytes "
-                                  "ratio of the ncu capture of a small case (profiles/grouped_gemm_int8_small_case_ncu.txt); "
-                                  "the full-size launch is too large to capture",
-                "ms_per_step_in_kernel": gemm_ms_step}
+                "traffic_source": f"algorithmic bytes (weights once + x + y) x {DRAM_OVER_ALGORITHMIC}: dram bytes / "
+                                  "algorithmic bytes of one profiler capture of `--workload layer_gemm --quick` (32 "
+                                  "experts, rows distributed like the layer's); the full-size launch is too large to capture",
+                "ms_per_step_in_kernel": gemm_ms_step,
+                "gemm_mcycles_per_step": (gemm_ms_step * sm_mhz / 1e3) if sm_mhz else None}
 
     line = {
         "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16 x int8 -> fp32 accumulate", "data": "synthetic",
-        "config": {**workload_config(world), "exchange": exchange, "exchange_status": exchange_status},
+        "config": workload_config(world), "exchange": exchange, "exchange_status": exchange_status,
         "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps_in_flight": 2, "cuda_graph": graphed is not None,
                 "single_step_latency_ms": latency_ms},
         "gpu_launches": launches * args.steps, "gpu_launches_per_step": launches,
         "roofline": roofline, "clocks": clk.result, "phases_ms_rank0": {k: round(v, 4) for k, v in phases.items()},
+        "parity_check": parity,
     }
     if world == 1 and rank == 0:
         del layer, c
         torch.cuda.empty_cache()
         if not args.no_kernels:
-            line["kernels"] = kernel_lines(peaks, quick=args.quick)
-            line["kernels"]["peaks"] = {**peaks, "kind": peak_kind}
+            line["moe_layer_fp4_stored"] = fp4_stored_line(peaks)
+            torch.cuda.empty_cache()
+            kernels = kernel_lines(peaks, quick=args.quick)
+            kernels["peaks"] = {**peaks, "kind": peak_kind}
+            # their own line, ahead of the headline line: a reader of the output's tail loses nothing
+            print(json.dumps({"kernels": kernels}), flush=True)
+            line["kernels"] = {k: {f: v[f] for f in ("ms", "ms_back_to_back", "tflops", "gbs", "frac_of_measured",
+                                                      "frac_of_measured_sustained", "frac_of_measured_burst") if f in v}
+                               for k, v in kernels.items() if k != "peaks"}
         if not args.no_cpu:
-            # a bounded sample: 32 of the 256 experts, passes repeated until about ten seconds are timed
+            # the bounded sample of the reference arm (8 of the 256 experts), passes repeated until about ten
+            # seconds are timed
             use_all_host_cores()
-            prepared = cpu_sample_inputs(8)
-            cpu_moe_sample(8, prepared)  # warm-up (thread pool, allocator)
+            prepared = cpu_sample_inputs(CPU_SAMPLE_EVERY)
+            cpu_moe_sample(CPU_SAMPLE_EVERY, prepared)  # warm-up (thread pool, allocator)
             rows_sum, secs, passes = 0, 0.0, 0
-            while secs < 10.0 and passes < 20:
-                _, t, rows, desc = cpu_moe_sample(8, prepared)
+            while secs < 10.0 and passes < 40:
+                _, t, rows, desc = cpu_moe_sample(CPU_SAMPLE_EVERY, prepared)
                 rows_sum, secs, passes = rows_sum + rows, secs + t, passes + 1
             tok_s = rows_sum / CFG["top_k"] / secs
             line["cpu_baseline"] = {"value": tok_s, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
@@ -515,6 +666,8 @@ def run_ours(args):
         torch.cuda.synchronize()
         dist.barrier(group=group)  # peers may read this rank's exchange buffers until they are done too
         dist.destroy_process_group()
+    if not parity["ok"]:
+        raise SystemExit(f"parity check failed: rel-L2 {parity['rel_l2_max']:.3e} > {parity['tol']}")
 
 
 def main():
@@ -523,7 +676,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="moe", choices=["moe", "gemm", "gemv", "dequant"],
+    ap.add_argument("--workload", default="moe", choices=["moe", "gemm", "gemv", "dequant", "layer_gemm"],
                     help="moe: the benchmark line; others: one kernel alone (for profiling)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="token exchange between ranks (N > 1): this package's peer-memory kernels or NCCL all-to-all")
@@ -543,7 +696,8 @@ def main():
         torch.cuda.set_device(0)
         peaks, kind = load_peaks()
         line = {"workload": args.workload, "quick": args.quick, "peaks": {**peaks, "kind": kind},
-                "kernels": kernel_lines(peaks, quick=args.quick, which=(args.workload,))}
+                "kernels": (layer_gemm_case(args.quick) if args.workload == "layer_gemm"
+                            else kernel_lines(peaks, quick=args.quick, which=(args.workload,)))}
         print(json.dumps(line), flush=True)
     else:
         run_ours(args)

@@ -103,3 +103,18 @@ def test_workspace_sizes():
     assert abi.lib.b200moe_grouped_gemm_workspace_bytes(8, 256, 512, 4, 1, 1) == 256
     assert abi.lib.b200moe_grouped_gemv_workspace_bytes(8, 256, 512, 4, 2, 0) == 256
     assert abi.lib.b200moe_grouped_gemv_workspace_bytes(8, 256, 512, 4, 1, 1) == 256
+
+
+def test_install_check_lists_the_reference_operators():
+    """The drop-in module exposes the reference's operator names (and the additions); the check fails
+    loudly for a name the module lacks."""
+    from ascend_kernel_b200 import check_installed_ops as chk
+
+    chk.check(verbose=False)
+    assert chk.REFERENCE_OPS == ["grouped_soft_gemv", "grouped_gemm"]
+    chk.ADDED_OPS.append("no_such_operator")
+    try:
+        with pytest.raises(RuntimeError, match="no_such_operator"):
+            chk.check(verbose=False)
+    finally:
+        chk.ADDED_OPS.pop()

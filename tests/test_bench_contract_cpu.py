@@ -37,3 +37,31 @@ def test_product_arm_has_no_cpu_path():
     r = _run("--steps", "1", "--warmup", "0")
     assert r.returncode != 0
     assert "CUDA" in (r.stderr + r.stdout)
+
+
+def test_reference_arm_does_not_load_the_product_library():
+    """The CPU arm is the baseline: it must run without the package (and so without libb200moe.so) ever
+    being imported; the input generators are loaded by path."""
+    code = ("import sys, bench; c = bench.cpu_sample_inputs(128); "
+            "assert not any(m == 'ascend_kernel_b200' or m.startswith('ascend_kernel_b200.') for m in sys.modules); "
+            "maps = open('/proc/self/maps').read(); assert 'libb200moe' not in maps; print('clean')")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert r.returncode == 0 and "clean" in r.stdout, r.stderr[-2000:]
+
+
+def test_hashed_inputs_are_reproducible_and_uniform():
+    """The layer's weights are a hash of (seed, element index): the same call gives the same bits, a slice
+    of experts equals the same experts of a larger slice, and the bytes are spread over all 256 values."""
+    from ascend_kernel_b200 import inputs
+
+    a = inputs.hashed_bytes((64, 1024), 77, "cpu", torch.int8)
+    assert torch.equal(a, inputs.hashed_bytes((64, 1024), 77, "cpu", torch.int8))
+    assert not torch.equal(a, inputs.hashed_bytes((64, 1024), 78, "cpu", torch.int8))
+    h = torch.bincount(a.view(torch.uint8).reshape(-1).long(), minlength=256)
+    assert int(h.min()) > 150 and int(h.max()) < 380          # 65 536 draws over 256 bins: 256 +- 16
+    one = inputs.config4("cpu", n_tokens=2, hidden=64, n_experts=4, inter=32, top_k=2, seed=4, expert_lo=2, expert_hi=3)
+    two = inputs.config4("cpu", n_tokens=2, hidden=64, n_experts=4, inter=32, top_k=2, seed=4, expert_lo=1, expert_hi=4)
+    for k in ("w13", "s13", "o13", "w2", "s2", "o2"):
+        assert torch.equal(one[k][0], two[k][1]), k
+    u = inputs.hashed_uniform((4096,), -4.0, 4.0, 5, "cpu").float()
+    assert -4.0 <= float(u.min()) and float(u.max()) <= 4.0 and abs(float(u.mean())) < 0.2

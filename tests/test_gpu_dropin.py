@@ -92,3 +92,19 @@ def test_fp4_dequant_entry():
     m.fp4_dequant(codes.cuda(), sc.cuda(), out)
     torch.cuda.synchronize()
     assert torch.equal(out.cpu().view(torch.int16), O.fp4_dequant_e8m0(codes, sc).view(torch.int16))
+
+
+def test_hashed_inputs_have_the_same_bits_on_the_gpu_and_on_the_cpu():
+    """The benchmark's CPU arm and GPU arm materialise the layer's weights separately; both must see the
+    same bits."""
+    from ascend_kernel_b200 import inputs
+
+    for seed in (1, 9_000_017):
+        assert torch.equal(inputs.hashed_bytes((300, 517), seed, "cuda", torch.int8).cpu(),
+                           inputs.hashed_bytes((300, 517), seed, "cpu", torch.int8))
+        assert torch.equal(inputs.hashed_uniform((5000,), 0.001, 0.01, seed, "cuda").cpu().view(torch.int16),
+                           inputs.hashed_uniform((5000,), 0.001, 0.01, seed, "cpu").view(torch.int16))
+    a = inputs.config4("cuda", n_tokens=2, hidden=64, n_experts=4, inter=32, top_k=2, seed=4, expert_lo=1, expert_hi=3)
+    b = inputs.config4("cpu", n_tokens=2, hidden=64, n_experts=4, inter=32, top_k=2, seed=4, expert_lo=1, expert_hi=3)
+    for k in ("w13", "s13", "o13", "w2", "s2", "o2"):
+        assert torch.equal(a[k].cpu().view(torch.uint8), b[k].view(torch.uint8)), k
