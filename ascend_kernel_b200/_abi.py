@@ -26,7 +26,7 @@ EXPORTS = [
     "b200moe_moe_route", "b200moe_moe_regroup_index", "b200moe_grouped_gemm_int8_noalloc", "b200moe_grouped_gemm_int8_noalloc_max_rows", "b200moe_noalloc_read_status",
     "b200moe_ep_post_counts", "b200moe_ep_dispatch", "b200moe_ep_wait", "b200moe_ep_post", "b200moe_ep_combine",
     "b200moe_fp4_dequant_bf16_scale", "b200moe_fp8_dequant", "b200moe_fp4_scale_fold",
-    "b200moe_silu_mul_dyn", "b200moe_grouped_gemm_int8_silu", "b200moe_pack_weight_int8", "b200moe_grouped_gemm_int8_packed", "b200moe_ipc_alloc", "b200moe_ipc_open", "b200moe_ipc_close", "b200moe_ipc_free",
+    "b200moe_silu_mul_dyn", "b200moe_grouped_gemm_int8_silu", "b200moe_pack_weight_int8", "b200moe_grouped_gemm_int8_packed", "b200moe_grouped_gemm_int8_packed_scatter", "b200moe_ipc_alloc", "b200moe_ipc_open", "b200moe_ipc_close", "b200moe_ipc_free",
 ]
 
 EP_MAX_WORLD = 8
@@ -40,7 +40,9 @@ class EpComm(ctypes.Structure):
                 ("reserved", ctypes.c_int32), ("cap_rows", ctypes.c_int64), ("hidden", ctypes.c_int64),
                 ("peer_recv_x", ctypes.c_void_p * EP_MAX_WORLD), ("peer_y", ctypes.c_void_p * EP_MAX_WORLD),
                 ("peer_counts", ctypes.c_void_p * EP_MAX_WORLD), ("peer_signal", ctypes.c_void_p * EP_MAX_WORLD),
-                ("status", ctypes.c_void_p), ("step_counter", ctypes.c_void_p)]
+                ("status", ctypes.c_void_p), ("step_counter", ctypes.c_void_p),
+                ("peer_ret", ctypes.c_void_p * EP_MAX_WORLD), ("peer_ret_code", ctypes.c_void_p * EP_MAX_WORLD),
+                ("cap_send", ctypes.c_int64)]
 
 
 class B200MoeError(RuntimeError):
@@ -70,6 +72,9 @@ def _load() -> ctypes.CDLL:
     lib.b200moe_pack_weight_int8.restype = i32
     lib.b200moe_grouped_gemm_int8_packed.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp, sz, vp]
     lib.b200moe_grouped_gemm_int8_packed.restype = i32
+    lib.b200moe_grouped_gemm_int8_packed_scatter.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.POINTER(vp), i64, i64, i64, i64, i64,
+                                                             i64, i32, vp, sz, vp]
+    lib.b200moe_grouped_gemm_int8_packed_scatter.restype = i32
     lib.b200moe_grouped_gemm_int8_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, vp]
     lib.b200moe_grouped_gemm_int8_noalloc.restype = i32
     lib.b200moe_grouped_gemm_int8_noalloc_max_rows.argtypes = []

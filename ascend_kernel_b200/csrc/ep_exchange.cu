@@ -45,6 +45,7 @@ struct EpComm {
     unsigned long long* signal[B200MOE_EP_MAX_WORLD];  // [3, B200MOE_EP_MAX_WORLD] on every rank
     int* status;                                       // local: two status words
     unsigned long long* step_counter;                  // local: the step number when the host passes 0
+    long long* ret_code[B200MOE_EP_MAX_WORLD];         // optional: where each delivered row's result returns to
 };
 
 constexpr int kSigCounts = 0, kSigRows = 1, kSigResults = 2;
@@ -181,7 +182,11 @@ ep_dispatch_kernel(EpComm c, const uint4* __restrict__ x, const int32_t* __restr
         const int e = lo, d = e / c.e_local;
         const long long pos = (long long)s_base[e] + (i - s_start[e]);
         const bool fits = counts_ok && i < s_start[E] && pos < c.cap_rows;
-        if (lane == 0) remote_pos[i] = fits ? (int32_t)(d * c.cap_rows + pos) : -1;
+        if (lane == 0) {
+            remote_pos[i] = fits ? (int32_t)(d * c.cap_rows + pos) : -1;
+            // the return address of the row's result: this rank, sorted position i
+            if (fits && c.ret_code[d] != nullptr) c.ret_code[d][pos] = ((long long)c.rank << 32) | (unsigned int)i;
+        }
         if (!fits) {
             if (counts_ok && lane == 0 && atomicCAS(c.status, kDevOk, kDevBadGroupList) == kDevOk) c.status[1] = e;
             continue;
@@ -284,7 +289,9 @@ static int to_comm(const b200moe_ep_comm* h, EpComm* c) {
         c->y[r] = static_cast<const uint4*>(h->peer_y[r]);
         c->counts[r] = h->peer_counts[r];
         c->signal[r] = reinterpret_cast<unsigned long long*>(h->peer_signal[r]);
+        c->ret_code[r] = reinterpret_cast<long long*>(h->peer_ret_code[r]);
     }
+    for (int r = h->world; r < B200MOE_EP_MAX_WORLD; ++r) c->ret_code[r] = nullptr;
     if (!h->status || !h->step_counter) return B200MOE_ERR_NULL_POINTER;
     c->status = h->status;
     c->step_counter = reinterpret_cast<unsigned long long*>(h->step_counter);

@@ -13,6 +13,12 @@ struct GemmArgs {
     __nv_bfloat16* y;
     int M, K, N, G, gl_type;
     int* status;
+    // packed kernel only, optional: result row r goes to dst_base[row_code[r] >> 32] + (low 32 bits) * N
+    // instead of y + r * N (rows handed back to the ranks they came from)
+    const long long* row_code = nullptr;
+    __nv_bfloat16* dst_base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int n_base = 0;
+    long long dst_rows = 0;
 };
 
 // out[m] = sum_k x[m, k] in fp32 for the rows the group list uses (grouped_gemm.cu).

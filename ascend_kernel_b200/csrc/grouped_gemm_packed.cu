@@ -205,6 +205,8 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* x_ring = base;
     Barriers* sb = reinterpret_cast<Barriers*>(x_ring + kXStages * kXSlotBytes);
+    __shared__ __nv_bfloat16* s_dst_base[8];  // scatter mode: the destination tensors (indexed per row)
+    if (threadIdx.x < 8) s_dst_base[threadIdx.x] = a.dst_base[threadIdx.x];
     float* epi_rowsum = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sb) + kBarrierBytes);
     int* row_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(epi_rowsum) + kEpiWarps * kEpiStripBytes);
     int* tile_prefix = row_start + (a.G + 1);
@@ -401,6 +403,7 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             }
             const int ld_out = GATE_UP ? (a.N >> 1) : a.N;
             const int n_chunks = (ti.rows + 15) >> 4;
+            bool scattered = false;
             // row sums of the tile's rows into the warp's strip while the tile is still being accumulated
             float* rsum = epi_rowsum + (warp - kWarpEpi0) * kMaxR;
             if (has_offset) {
@@ -442,10 +445,25 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     }
                     ob[i] = __bfloat16_as_ushort(__float2bfloat16_rn(o));
                 }
+                if (GATE_UP || a.row_code == nullptr) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    if (i < n_valid) reinterpret_cast<unsigned short*>(yp)[(size_t)i * ld_out] = ob[i];
+                    for (int i = 0; i < 16; ++i)
+                        if (i < n_valid) reinterpret_cast<unsigned short*>(yp)[(size_t)i * ld_out] = ob[i];
+                } else {
+                    // scatter mode: every row has its own destination (possibly another GPU's memory)
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        if (i >= n_valid) continue;
+                        const long long code = __ldg(a.row_code + r0 + i);
+                        const unsigned int bi = (unsigned int)(code >> 32), ri = (unsigned int)code;
+                        if ((int)bi < a.n_base && (long long)ri < a.dst_rows)
+                            reinterpret_cast<unsigned short*>(s_dst_base[bi])[(size_t)ri * ld_out + out_col] = ob[i];
+                    }
+                    scattered = true;
+                }
             }
+            // rows stored into other GPUs' memory must be visible there before a later kernel signals them
+            if (scattered) __threadfence_system();
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->t_empty));
@@ -575,19 +593,21 @@ extern "C" int b200moe_pack_weight_int8(const void* weight, void* packed, int64_
     return B200MOE_OK;
 }
 
-extern "C" int b200moe_grouped_gemm_int8_packed(const void* x, const void* packed, const void* scale, const void* offset,
-                                                const int64_t* group_list, void* y, int64_t M, int64_t K, int64_t N,
-                                                int64_t G, int group_list_type, int gate_up_silu, void* workspace,
-                                                size_t workspace_bytes, void* stream) {
+static int packed_launch(const void* x, const void* packed, const void* scale, const void* offset,
+                         const int64_t* group_list, void* y, const int64_t* row_code, void* const* dst_base, int64_t n_base,
+                         int64_t dst_rows, int64_t M, int64_t K, int64_t N, int64_t G, int group_list_type, int gate_up_silu,
+                         void* workspace, size_t workspace_bytes, void* stream) {
     if (group_list_type != B200MOE_GROUP_LIST_CUMSUM && group_list_type != B200MOE_GROUP_LIST_COUNTS)
         return B200MOE_ERR_ARGUMENT;
     if (M < 0 || K <= 0 || N <= 0 || G <= 0 || G > kMaxExperts || M > 0x7FFFFFF0LL || K > 0x7FFFFFF0LL ||
         N > 0x7FFFFFF0LL || G * (N / pk::kTileN) * (M / 16 + 2) > 0x7FFFFFF0LL)
         return B200MOE_ERR_SHAPE;
     if ((K % pk::kBK) != 0 || (N % pk::kTileN) != 0) return B200MOE_ERR_SHAPE;
+    if (row_code != nullptr && (gate_up_silu || n_base < 1 || n_base > 8 || dst_rows < 0 || dst_base == nullptr))
+        return B200MOE_ERR_ARGUMENT;
     if (M == 0) return B200MOE_OK;
-    if (!x || !packed || !scale || !group_list || !y) return B200MOE_ERR_NULL_POINTER;
-    if (!aligned16(x) || !aligned16(packed) || !aligned16(scale) || !aligned16(y) || (offset && !aligned16(offset)))
+    if (!x || !packed || !scale || !group_list || (!y && !row_code)) return B200MOE_ERR_NULL_POINTER;
+    if (!aligned16(x) || !aligned16(packed) || !aligned16(scale) || (y && !aligned16(y)) || (offset && !aligned16(offset)))
         return B200MOE_ERR_ALIGNMENT;
     const size_t need = b200moe_grouped_gemm_workspace_bytes(M, K, N, G, B200MOE_CT_INT8, B200MOE_LAYOUT_CANONICAL);
     if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return B200MOE_ERR_WORKSPACE;
@@ -602,6 +622,15 @@ extern "C" int b200moe_grouped_gemm_int8_packed(const void* x, const void* packe
     a.M = (int)M; a.K = (int)K; a.N = (int)N; a.G = (int)G;
     a.gl_type = group_list_type;
     a.status = static_cast<int*>(workspace);
+    if (row_code != nullptr) {
+        a.row_code = reinterpret_cast<const long long*>(row_code);
+        a.n_base = (int)n_base;
+        a.dst_rows = dst_rows;
+        for (int i = 0; i < (int)n_base; ++i) {
+            if (dst_base[i] == nullptr) return B200MOE_ERR_NULL_POINTER;
+            a.dst_base[i] = static_cast<__nv_bfloat16*>(dst_base[i]);
+        }
+    }
     if (offset != nullptr) {
         float* rowsum = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + B200MOE_STATUS_BYTES);
         launch_rowsum(x, rowsum, M, K, group_list, G, group_list_type, s);
@@ -627,4 +656,23 @@ extern "C" int b200moe_grouped_gemm_int8_packed(const void* x, const void* packe
     }
     B200MOE_CUDA_TRY(cudaGetLastError());
     return B200MOE_OK;
+}
+
+extern "C" int b200moe_grouped_gemm_int8_packed(const void* x, const void* packed, const void* scale, const void* offset,
+                                                const int64_t* group_list, void* y, int64_t M, int64_t K, int64_t N,
+                                                int64_t G, int group_list_type, int gate_up_silu, void* workspace,
+                                                size_t workspace_bytes, void* stream) {
+    return packed_launch(x, packed, scale, offset, group_list, y, nullptr, nullptr, 0, 0, M, K, N, G, group_list_type,
+                         gate_up_silu, workspace, workspace_bytes, stream);
+}
+
+extern "C" int b200moe_grouped_gemm_int8_packed_scatter(const void* x, const void* packed, const void* scale,
+                                                        const void* offset, const int64_t* group_list,
+                                                        const int64_t* row_code, void* const* dst_base, int64_t n_base,
+                                                        int64_t dst_rows, int64_t M, int64_t K, int64_t N, int64_t G,
+                                                        int group_list_type, void* workspace, size_t workspace_bytes,
+                                                        void* stream) {
+    if (row_code == nullptr) return B200MOE_ERR_NULL_POINTER;
+    return packed_launch(x, packed, scale, offset, group_list, nullptr, row_code, dst_base, n_base, dst_rows, M, K, N, G,
+                         group_list_type, 0, workspace, workspace_bytes, stream);
 }

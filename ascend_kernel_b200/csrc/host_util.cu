@@ -72,7 +72,7 @@ const char* b200moe_strerror(int code) {
     }
 }
 
-const char* b200moe_version(void) { return "1.0"; }
+const char* b200moe_version(void) { return "1.1"; }
 
 int b200moe_read_status(const void* workspace, int32_t out[2], void* stream) {
     if (workspace == nullptr || out == nullptr) return B200MOE_ERR_NULL_POINTER;

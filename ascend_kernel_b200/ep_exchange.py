@@ -48,8 +48,11 @@ class PeerExchange:
         if self.world > _abi.EP_MAX_WORLD:
             raise RuntimeError(f"at most {_abi.EP_MAX_WORLD} ranks")
         self.step = 0
+        # rows this rank itself dispatches at most (its tokens x top_k): the size of its return buffer
+        self.cap_send = max(1, cap_rows // self.world)
         sizes = {"recv_x": cap_rows * hidden * 2, "y": cap_rows * hidden * 2,
-                 "counts": self.world * n_experts * 4, "signal": 3 * _abi.EP_MAX_WORLD * 8}
+                 "counts": self.world * n_experts * 4, "signal": 3 * _abi.EP_MAX_WORLD * 8,
+                 "ret": self.cap_send * hidden * 2, "ret_code": cap_rows * 8}
         self._own, handles = {}, {}
         with torch.cuda.device(self.device):
             for name, nbytes in sizes.items():
@@ -86,6 +89,8 @@ class PeerExchange:
         for r in range(self.world):
             c.peer_recv_x[r], c.peer_y[r] = self._peer["recv_x"][r], self._peer["y"][r]
             c.peer_counts[r], c.peer_signal[r] = self._peer["counts"][r], self._peer["signal"][r]
+            c.peer_ret[r], c.peer_ret_code[r] = self._peer["ret"][r], self._peer["ret_code"][r]
+        c.cap_send = self.cap_send
         self._step_dev = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.device_steps = False  # True: the step number lives on the device (constant kernel arguments)
         c.status = self.status.data_ptr()
@@ -94,6 +99,11 @@ class PeerExchange:
         # torch views of the two local row buffers (inputs / outputs of the grouped GEMMs)
         self.recv_x = _as_tensor(self._own["recv_x"], (cap_rows, hidden), torch.bfloat16, self.device)
         self.y = _as_tensor(self._own["y"], (cap_rows, hidden), torch.bfloat16, self.device)
+        # results pushed back by the owners' down projections: this rank's return buffer (one row per
+        # dispatched (token, j) pair, in sorted order), and the return addresses of the rows it received
+        self.ret = _as_tensor(self._own["ret"], (self.cap_send, hidden), torch.bfloat16, self.device)
+        self.ret_code = _as_tensor(self._own["ret_code"], (cap_rows,), torch.int64, self.device)
+        self.ret_ptrs = [self._peer["ret"][r] for r in range(self.world)]
 
     # ---- one step ---------------------------------------------------------------------------
     def _s(self):
@@ -165,7 +175,7 @@ class PeerExchange:
             for p in self._opened:
                 _lib.b200moe_ipc_close(p)
             self._opened = []
-            self.recv_x = self.y = None
+            self.recv_x = self.y = self.ret = self.ret_code = None
             for name, p in list(self._own.items()):
                 _lib.b200moe_ipc_free(p)
             self._own = {}

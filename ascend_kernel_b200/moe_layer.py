@@ -139,9 +139,12 @@ class MoELayer:
         if self.mid_hook is not None:
             self.mid_hook()
 
-    def _experts(self, rows, counts, record, y=None, n_rows=None):
+    def _experts(self, rows, counts, record, y=None, n_rows=None, scatter=None):
         """rows [R, H] expert-major with per-local-expert counts -> [R, H] (into ``y`` when given).
-        ``n_rows``: int64 device tensor with the number of rows in use when R is only a capacity."""
+        ``n_rows``: int64 device tensor with the number of rows in use when R is only a capacity.
+        ``scatter`` = (row_code, destination pointers, destination rows): the down projection stores
+        each result row where its code says (the return buffer of the rank the token came from) instead
+        of into ``y``; packed GEMMs only."""
         R = rows.shape[0]
         if y is None:
             y = torch.empty(R, self.hidden, dtype=torch.bfloat16, device=self.device)
@@ -173,7 +176,11 @@ class MoELayer:
             if ev:
                 ev[1].record()
                 ev[2].record()
-            ops.grouped_gemm_packed(act, self.w2, self.s2, self.o2, counts, y, group_list_type=1)
+            if scatter is not None:
+                ops.grouped_gemm_packed_scatter(act, self.w2, self.s2, self.o2, counts, scatter[0], scatter[1], scatter[2],
+                                                group_list_type=1)
+            else:
+                ops.grouped_gemm_packed(act, self.w2, self.s2, self.o2, counts, y, group_list_type=1)
             if ev:
                 ev[3].record()
                 self.timing = ev
@@ -227,10 +234,20 @@ class MoELayer:
             px.wait(1)                                            # rows of every source rank have landed
             mark("dispatch")
             self._mid()
-            self._experts(px.recv_x, local_counts, record, y=px.y, n_rows=n_recv)
-            px.post(2)                                            # results of this rank are complete
-            mark("experts")
-            out = px.combine(remote_pos, slot, wts, out=out_host)  # a pinned host tensor is written directly
+            if self.gemm == "packed":
+                # the down projection hands every result row straight back to the rank its token came from
+                # (stores over NVLink from the GEMM's epilogue); the weighted sum is then local
+                self._experts(px.recv_x, local_counts, record, y=px.y, n_rows=n_recv,
+                              scatter=(px.ret_code, px.ret_ptrs, px.cap_send))
+                px.post(2)                                        # this rank's pushes are complete and visible
+                mark("experts")
+                px.wait(2)                                        # every owner has pushed this rank's rows
+                out = finish(px.ret, slot, wts)
+            else:
+                self._experts(px.recv_x, local_counts, record, y=px.y, n_rows=n_recv)
+                px.post(2)                                        # results of this rank are complete
+                mark("experts")
+                out = px.combine(remote_pos, slot, wts, out=out_host)  # a pinned host tensor is written directly
             mark("combine")
             self.phases = marks
             return out

@@ -246,6 +246,35 @@ def grouped_gemm_packed(x, packed, scale, offset, group_list, output, group_list
     return ws if return_workspace else None
 
 
+def grouped_gemm_packed_scatter(x, packed, scale, offset, group_list, row_code, dst_ptrs, dst_rows: int,
+                                group_list_type: int = 0):
+    """grouped_gemm_packed whose result row r is stored at row ``row_code[r] & 0xffffffff`` of the bf16
+    [dst_rows, N] tensor at device address ``dst_ptrs[row_code[r] >> 32]`` (addresses may be other GPUs'
+    memory mapped into this process)."""
+    import ctypes
+
+    _need_cuda(x=x, packed=packed, scale=scale, offset=offset, group_list=group_list, row_code=row_code)
+    if x.dtype != torch.bfloat16 or group_list.dtype != torch.int64 or row_code.dtype != torch.int64:
+        raise RuntimeError("x must be bfloat16, group_list and row_code int64")
+    G, K, N = packed.shape
+    M = x.shape[0]
+    if x.shape[1] != K or group_list.numel() != G or row_code.numel() < M or not 1 <= len(dst_ptrs) <= 8:
+        raise RuntimeError("shape mismatch")
+    _check_scale(scale, CT["int8"], G, K, N, "scale")
+    if offset is not None:
+        _check_scale(offset, CT["int8"], G, K, N, "offset")
+    need = _lib.b200moe_grouped_gemm_workspace_bytes(M, K, N, G, CT["int8"], LAYOUT["canonical"])
+    ws = _workspace(need, x.device)
+    bases = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    with torch.cuda.device(x.device):
+        rc = _lib.b200moe_grouped_gemm_int8_packed_scatter(_ptr(x), _ptr(packed), _ptr(scale), _ptr(offset), _ptr(group_list),
+                                                           _ptr(row_code), bases, len(dst_ptrs), dst_rows, M, K, N, G,
+                                                           group_list_type, _ptr(ws), need, _stream())
+    _abi.check(rc, "grouped_gemm_packed_scatter")
+    if M > 0:
+        _count(1 + (offset is not None))
+
+
 def grouped_soft_gemv(x, weight, scale, groupList, computeType, output, group_list_type: int = 0,
                       weight_layout: str = "ascend", offset=None, return_workspace: bool = False):
     ct = _compute_type(computeType)

@@ -129,6 +129,20 @@ int b200moe_grouped_gemm_int8_packed(const void* x, const void* packed, const vo
                                      int group_list_type, int gate_up_silu, void* workspace, size_t workspace_bytes,
                                      void* stream);
 
+/* b200moe_grouped_gemm_int8_packed (gate_up_silu == 0) whose result rows go where a table says instead of
+ * into one [M, N] tensor (no reference counterpart; it is the down projection of an expert-parallel layer
+ * handing each row straight back to the rank the token came from, over NVLink, while the GEMM is still
+ * running): row r of the product is stored at dst_base[row_code[r] >> 32] + (row_code[r] & 0xffffffff) * N
+ * elements.  row_code int64 [M] on the device; dst_base: n_base (<= 8) device pointers, each to bf16
+ * [dst_rows, N], which may be another GPU's memory mapped into this process (plain 2-byte stores, 64
+ * contiguous bytes per warp; no TMA, no multicast).  A code whose base index is >= n_base or whose row
+ * index is >= dst_rows is skipped.  Every thread issues a system-scope fence after the stores of a tile,
+ * so a signal posted by a later kernel on the stream covers them. */
+int b200moe_grouped_gemm_int8_packed_scatter(const void* x, const void* packed, const void* scale, const void* offset,
+                                             const int64_t* group_list, const int64_t* row_code, void* const* dst_base,
+                                             int64_t n_base, int64_t dst_rows, int64_t M, int64_t K, int64_t N, int64_t G,
+                                             int group_list_type, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Allocation-free int8 grouped GEMM.  (No counterpart in the reference: its host binding always
  * obtains a workspace with aclrtMalloc.)  For callers that must not allocate device memory -- a
  * plug-in running inside another framework's step whose allocator owns all device memory, or a
@@ -251,6 +265,17 @@ typedef struct b200moe_ep_comm {
     uint64_t* peer_signal[B200MOE_EP_MAX_WORLD];
     int32_t* status;        /* local device memory, >= 2 words, zeroed by the caller */
     uint64_t* step_counter; /* local device memory, one word, zeroed by the caller (see `step`) */
+    /* Optional (all NULL = not used): results pushed back by the owner's down projection instead of being
+     * fetched by b200moe_ep_combine.  Every rank owns
+     *   ret       bf16 [cap_send, hidden]  one row per (token, j) pair this rank dispatched, in its sorted order
+     *   ret_code  int64 [cap_rows]         for the row at each position of this rank's recv_x: the source rank
+     *                                      << 32 | the row's index in the source's sorted order
+     * b200moe_ep_dispatch fills ret_code next to every row it delivers; b200moe_grouped_gemm_int8_packed_scatter
+     * stores each result row at ret[index] of its source rank; the source then combines locally
+     * (b200moe_ep_wait for the results signal, b200moe_combine over its own ret). */
+    void* peer_ret[B200MOE_EP_MAX_WORLD];
+    int64_t* peer_ret_code[B200MOE_EP_MAX_WORLD];
+    int64_t cap_send;
 } b200moe_ep_comm;
 enum { B200MOE_EP_SIG_COUNTS = 0, B200MOE_EP_SIG_ROWS = 1, B200MOE_EP_SIG_RESULTS = 2 };
 

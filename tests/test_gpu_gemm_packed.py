@@ -81,3 +81,36 @@ def test_packed_bad_group_list_is_clamped_and_reported():
     x, w, scale, offset, cnt = _int8_case([10, 20], 64, 256, 9, False)
     out, st = run_packed(x, w, scale, None, torch.tensor([20, 5]), gl_type=0)
     assert st[0] == 1 and st[1] == 1
+
+
+def test_packed_scatter_stores_rows_where_the_codes_say():
+    """The scatter variant against the plain one: row r lands at row (code & 0xffffffff) of destination tensor
+    (code >> 32); a code naming no destination or a row past the destination's end is skipped."""
+    from ascend_kernel_b200 import ops
+
+    x, w, scale, offset, cnt = _int8_case([137, 0, 20, 161], 256, 512, 3, True)
+    M, N = x.shape[0], w.shape[2]
+    want, st = run_packed(x, w, scale, offset, cnt)
+    assert st == (0, 0)
+    gen = torch.Generator().manual_seed(8)
+    perm = torch.randperm(M, generator=gen)
+    base = (torch.arange(M) % 2).to(torch.int64)              # two destination tensors, rows alternate
+    code = (base << 32) | perm.to(torch.int64)
+    code[5] = (7 << 32) | 0                                    # no such destination
+    code[9] = (0 << 32) | (M + 10)                             # row past the end
+    d0 = torch.full((M, N), SENTINEL, dtype=torch.bfloat16, device="cuda")
+    d1 = torch.full((M, N), SENTINEL, dtype=torch.bfloat16, device="cuda")
+    wp = ops.pack_weight_int8(w.cuda())
+    ops.grouped_gemm_packed_scatter(x.cuda(), wp, scale.cuda(), offset.cuda(), cnt.cuda(), code.cuda(),
+                                    [d0.data_ptr(), d1.data_ptr()], M, group_list_type=1)
+    torch.cuda.synchronize()
+    got = torch.stack([d0, d1])
+    for r in range(M):
+        if r in (5, 9):
+            continue
+        assert torch.equal(got[int(base[r]), int(perm[r])].view(torch.int16), want[r].view(torch.int16)), r
+    written = torch.zeros(2, M, dtype=torch.bool)
+    keep = torch.ones(M, dtype=torch.bool)
+    keep[5] = keep[9] = False
+    written[base[keep], perm[keep]] = True
+    assert bool((got[~written.cuda()].float() == SENTINEL).all())   # nothing else was touched
