@@ -43,7 +43,7 @@ constexpr int kBK = 64;        // k per stage
 constexpr int kTileN = 256;    // weight columns per tile: two MMA halves of 128
 constexpr int kMaxR = 160;     // token rows per tile (the MMA's N extent), a multiple of 32
 constexpr int kStages = 3;     // A ring (tensor memory), 64 k per stage
-constexpr int kXStages = 6;    // x ring (shared memory), 64 k per stage
+constexpr int kXStages = 6;    // x ring (shared memory), 64 k per stage (120 KB; 80 KB more hold the epilogue's staging tile)
 constexpr int kThreads = 896;
 constexpr int kWarpProd = 0, kWarpMma = 2, kWarpEpi0 = 4, kEpiWarps = 8, kWarpDq0 = 12;
 constexpr int kDqGroups = 2, kDqGroupWarps = 8;
@@ -59,6 +59,7 @@ constexpr uint32_t kACol = 2 * kMaxR;          // first column of the A ring
 constexpr uint32_t kAStageCols = 64;           // 2 halves x 32 columns (64 k as bf16 pairs)
 constexpr int kBarrierBytes = 512;
 constexpr int kEpiStripBytes = kMaxR * 4;  // per epilogue warp: the row sums of the tile's rows
+constexpr int kStageTileBytes = kMaxR * kTileN * 2;  // the epilogue's bf16 staging tile (80 KB)
 static_assert(kACol + kStages * kAStageCols <= kTmemCols, "tensor memory budget");
 
 struct Barriers {
@@ -67,6 +68,7 @@ struct Barriers {
     uint64_t full[kStages];   // the 8 dequant warps of the stage's group: A slot written AND x tile landed
     uint64_t empty[kStages];  // one tcgen05.commit per stage
     uint64_t t_full, t_empty; // accumulator hand-off with the epilogue
+    uint64_t stage_full, stage_free;  // the epilogue warps among themselves: staging tile written / stored
     uint64_t drain;
     uint32_t tmem_base;
     int abort;
@@ -204,7 +206,8 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* x_ring = base;
-    Barriers* sb = reinterpret_cast<Barriers*>(x_ring + kXStages * kXSlotBytes);
+    uint8_t* epi_stage = x_ring + kXStages * kXSlotBytes;
+    Barriers* sb = reinterpret_cast<Barriers*>(epi_stage + kStageTileBytes);
     __shared__ __nv_bfloat16* s_dst_base[8];  // scatter mode: the destination tensors (indexed per row)
     if (threadIdx.x < 8) s_dst_base[threadIdx.x] = a.dst_base[threadIdx.x];
     float* epi_rowsum = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sb) + kBarrierBytes);
@@ -237,6 +240,8 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         }
         ptx::mbar_init(ptx::smem_u32(&sb->t_full), 1);
         ptx::mbar_init(ptx::smem_u32(&sb->t_empty), kEpiWarps);
+        ptx::mbar_init(ptx::smem_u32(&sb->stage_full), kEpiWarps);
+        ptx::mbar_init(ptx::smem_u32(&sb->stage_free), kEpiWarps);
         ptx::mbar_init(ptx::smem_u32(&sb->drain), 1);
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_x);
@@ -374,12 +379,22 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
     } else if (warp >= kWarpEpi0 && warp < kWarpEpi0 + kEpiWarps) {
         // ------------------------------ epilogue ------------------------------
         // Lane = weight column (TMEM lane 32 * quarter + lane of a half), accumulator columns = token
-        // rows.  Plain: warp (quarter, half) drains its half.  GATE_UP: both warps of a quarter read
-        // the gate and the up accumulator and share the tile's 16-row chunks between them.
-        const int quarter = warp & 3, second = (warp - kWarpEpi0) >> 2;
+        // rows.  Two phases per tile.  A: TMEM -> registers -> scale / offset (and SiLU(gate) * up) -> bf16
+        // into a [rows][tile columns] staging tile in shared memory; plain: warp (quarter, half) drains its
+        // half, GATE_UP: both warps of a quarter read both accumulators and share the 16-row chunks.  The
+        // accumulators are handed back to the MMA warp as soon as a warp's own reads are done.  B: the
+        // eight warps store the staged rows, a whole row segment (512 or 256 contiguous bytes, 16 per lane)
+        // per instruction -- to y, or in scatter mode to each row's own destination, which may be another
+        // GPU's memory -- while the next tile is already being accumulated.
+        const int ew = warp - kWarpEpi0, quarter = warp & 3, second = ew >> 2;
         const bool has_offset = a.offset != nullptr;
         const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+        constexpr int kRowBytes = GATE_UP ? 256 : 512;  // bytes of a staged row
+        const uint32_t stage_u32 = ptx::smem_u32(epi_stage);
+        // the thread's column in the staging tile
+        const uint32_t my_col_bytes = (uint32_t)(((GATE_UP ? 0 : second * 128) + quarter * 32 + lane) * 2);
         uint32_t use = 0, seq = 0;
+        bool scattered = false;
         for (;;) {
             const int t = next_tile(sb, seq, n_tiles, a.status);
             if (t >= n_tiles) break;
@@ -388,35 +403,31 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(a.scale) + (size_t)ti.g * a.N;
             const __nv_bfloat16* op = has_offset ? a.offset + (size_t)ti.g * a.N : nullptr;
             float s0, so0 = 0.f, s1 = 0.f, so1 = 0.f;
-            int out_col;
             if constexpr (GATE_UP) {
                 const int cg = ti.j * 128 + ci, cu = (a.N >> 1) + cg;
                 s0 = __bfloat162float(sp[cg]);
                 s1 = __bfloat162float(sp[cu]);
                 if (has_offset) { so0 = s0 * __bfloat162float(op[cg]); so1 = s1 * __bfloat162float(op[cu]); }
-                out_col = cg;
             } else {
                 const int c = ti.j * kTileN + second * 128 + ci;
                 s0 = __bfloat162float(sp[c]);
                 if (has_offset) so0 = s0 * __bfloat162float(op[c]);
-                out_col = c;
             }
             const int ld_out = GATE_UP ? (a.N >> 1) : a.N;
             const int n_chunks = (ti.rows + 15) >> 4;
-            bool scattered = false;
             // row sums of the tile's rows into the warp's strip while the tile is still being accumulated
-            float* rsum = epi_rowsum + (warp - kWarpEpi0) * kMaxR;
+            float* rsum = epi_rowsum + ew * kMaxR;
             if (has_offset) {
                 __syncwarp();
                 for (int i = lane; i < ti.rows; i += 32) rsum[i] = __ldg(a.rowsum + ti.row0 + i);
                 __syncwarp();
             }
             if (!__all_sync(0xffffffffu, pk_wait(&sb->t_full, use & 1, sb, a.status, 60))) break;
-            ++use;
+            // every warp has stored the previous tile's rows: the staging tile may be overwritten
+            if (use >= 1 && !__all_sync(0xffffffffu, pk_wait(&sb->stage_free, (use - 1) & 1, sb, a.status, 62))) break;
             ptx::tc_fence_after();
+            // ---- phase A ----
             for (int c = GATE_UP ? second : 0; c < n_chunks; c += GATE_UP ? 2 : 1) {
-                const int r0 = ti.row0 + c * 16;
-                const int n_valid = min(16, ti.rows - c * 16);
                 uint32_t v0[16], v1[16];
                 if constexpr (GATE_UP) {
                     ptx::tmem_ld_32x16(tmem_base + lane_sel + c * 16, v0);
@@ -425,9 +436,8 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     ptx::tmem_ld_32x16(tmem_base + lane_sel + second * kMaxR + c * 16, v0);
                 }
                 ptx::tmem_ld_wait();
-                __nv_bfloat16* yp = a.y + (size_t)r0 * ld_out + out_col;
-                // three passes over the chunk's 16 rows (loads, arithmetic, stores), so that the rows'
-                // dependent chains overlap instead of running one after the other
+                // passes over the chunk's 16 rows (loads, arithmetic, stores), so that the rows' dependent
+                // chains overlap instead of running one after the other
                 float rs[16];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {  // (the strip is kMaxR long: a ragged last chunk reads stale, unused values)
@@ -445,29 +455,47 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     }
                     ob[i] = __bfloat16_as_ushort(__float2bfloat16_rn(o));
                 }
-                if (GATE_UP || a.row_code == nullptr) {
+                const uint32_t sa = stage_u32 + (uint32_t)(c * 16 * kRowBytes) + my_col_bytes;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        if (i < n_valid) reinterpret_cast<unsigned short*>(yp)[(size_t)i * ld_out] = ob[i];
-                } else {
-                    // scatter mode: every row has its own destination (possibly another GPU's memory)
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        if (i >= n_valid) continue;
-                        const long long code = __ldg(a.row_code + r0 + i);
-                        const unsigned int bi = (unsigned int)(code >> 32), ri = (unsigned int)code;
-                        if ((int)bi < a.n_base && (long long)ri < a.dst_rows)
-                            reinterpret_cast<unsigned short*>(s_dst_base[bi])[(size_t)ri * ld_out + out_col] = ob[i];
-                    }
-                    scattered = true;
-                }
+                for (int i = 0; i < 16; ++i)
+                    asm volatile("st.shared.b16 [%0], %1;" ::"r"(sa + (uint32_t)(i * kRowBytes)), "h"(ob[i]) : "memory");
             }
-            // rows stored into other GPUs' memory must be visible there before a later kernel signals them
-            if (scattered) __threadfence_system();
+            // this warp's reads of the accumulators are done: hand them back, report the staging written
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->t_empty));
+            if (lane == 0) {
+                ptx::mbar_arrive(ptx::smem_u32(&sb->t_empty));
+                ptx::mbar_arrive(ptx::smem_u32(&sb->stage_full));
+            }
+            if (!__all_sync(0xffffffffu, pk_wait(&sb->stage_full, use & 1, sb, a.status, 64))) break;
+            ++use;
+            // ---- phase B ----
+            constexpr int kLanesPerRow = kRowBytes / 16, kRowsPerStep = 32 / kLanesPerRow;  // 32 / 1 or 16 / 2
+            const int lr = lane / kLanesPerRow, lc = lane % kLanesPerRow;
+            const size_t col0 = (size_t)ti.j * (GATE_UP ? 128 : kTileN) + (size_t)lc * 8;  // first of the lane's 8 columns
+            for (int r = ew * kRowsPerStep + lr; r < ti.rows; r += kEpiWarps * kRowsPerStep) {
+                uint4 v;
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                             : "r"(stage_u32 + (uint32_t)(r * kRowBytes + lc * 16)));
+                __nv_bfloat16* dst;
+                if (GATE_UP || a.row_code == nullptr) {
+                    dst = a.y + (size_t)(ti.row0 + r) * ld_out;
+                } else {
+                    // scatter mode: the row's own destination (a code naming none is skipped)
+                    const long long code = __ldg(a.row_code + ti.row0 + r);
+                    const unsigned int bi = (unsigned int)(code >> 32), ri = (unsigned int)code;
+                    if ((int)bi >= a.n_base || (long long)ri >= a.dst_rows) continue;
+                    dst = s_dst_base[bi] + (size_t)ri * ld_out;
+                    scattered = true;
+                }
+                *reinterpret_cast<uint4*>(dst + col0) = v;
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sb->stage_free));
         }
+        // rows stored into other GPUs' memory must be visible there before a later kernel signals them
+        if (scattered) __threadfence_system();
     } else if (warp >= kWarpDq0) {
         // ------------------------------ dequant ------------------------------
         const int dq_tid = threadIdx.x - kWarpDq0 * 32;
@@ -628,6 +656,7 @@ static int packed_launch(const void* x, const void* packed, const void* scale, c
         a.dst_rows = dst_rows;
         for (int i = 0; i < (int)n_base; ++i) {
             if (dst_base[i] == nullptr) return B200MOE_ERR_NULL_POINTER;
+            if (!aligned16(dst_base[i])) return B200MOE_ERR_ALIGNMENT;
             a.dst_base[i] = static_cast<__nv_bfloat16*>(dst_base[i]);
         }
     }
@@ -643,7 +672,7 @@ static int packed_launch(const void* x, const void* packed, const void* scale, c
     if (rc != B200MOE_OK) return rc;
     rc = make_tensor_map_2d(&txs, x, 2, (uint64_t)M, (uint64_t)K, pk::kSmallBox, pk::kBK, true);
     if (rc != B200MOE_OK) return rc;
-    const size_t smem = 1024 + (size_t)pk::kXStages * pk::kXSlotBytes + pk::kBarrierBytes +
+    const size_t smem = 1024 + (size_t)pk::kXStages * pk::kXSlotBytes + pk::kStageTileBytes + pk::kBarrierBytes +
                         (size_t)pk::kEpiWarps * pk::kEpiStripBytes + sizeof(int) * 2 * (size_t)(G + 1);
     if (gate_up_silu) {
         B200MOE_CUDA_TRY(cudaFuncSetAttribute(pk::grouped_gemm_packed_kernel<true>,
