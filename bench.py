@@ -37,7 +37,7 @@ if ROOT not in sys.path:
 
 CFG = dict(n_tokens=4096, hidden=7168, n_experts=256, inter=2048, top_k=8, seed=4)
 # dram bytes / algorithmic bytes of the layer's grouped GEMMs, from a profiler capture of a small case
-DRAM_OVER_ALGORITHMIC = 1.08
+DRAM_OVER_ALGORITHMIC = 1.00
 CPU_SAMPLE_EVERY = 32  # the CPU legs time every 32nd expert by load rank (8 of 256) with all its routed rows
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
