@@ -57,10 +57,15 @@ constexpr int kBigBox = 128, kSmallBox = 32;  // rows of the two x boxes
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kACol = 2 * kMaxR;          // first column of the A ring
 constexpr uint32_t kAStageCols = 64;           // 2 halves x 32 columns (64 k as bf16 pairs)
-constexpr int kBarrierBytes = 512;
+constexpr int kBarrierBytes = 1024;
 constexpr int kEpiStripBytes = kMaxR * 4;  // per epilogue warp: the row sums of the tile's rows
 constexpr int kStageTileBytes = kMaxR * kTileN * 2;  // the epilogue's bf16 staging tile (80 KB)
 static_assert(kACol + kStages * kAStageCols <= kTmemCols, "tensor memory budget");
+
+struct TileInfo {
+    int g, row0, rows;  // expert, first row, rows of the expert inside the tile (1 .. kMaxR)
+    int j;              // tile column index (256 weight columns each)
+};
 
 struct Barriers {
     uint64_t x_full[kXStages];   // x ring: TMA bytes; waited for by the relay lane of the stage's dequant group
@@ -74,14 +79,14 @@ struct Barriers {
     int abort;
     int n_tiles;
     int pad;
-    unsigned long long tile_ring[kTileRing];  // entry i % kTileRing = (i + 1) << 32 | tile
+    // The published tiles, resolved once by the publisher: entry i % kTileRing = {i + 1, first row,
+    // expert | rows << 16 (rows 0 = end of the schedule), tile column}, written and read as one aligned
+    // 16-byte vector, so a reader sees the sequence number and the tile together.  Every other role reads
+    // the entry instead of repeating the search and the divisions at each tile switch.
+    uint4 tile_ring[kTileRing];
 };
 static_assert(sizeof(Barriers) <= kBarrierBytes, "barrier block");
 
-struct TileInfo {
-    int g, row0, rows;  // expert, first row, rows of the expert inside the tile (1 .. kMaxR)
-    int j;              // tile column index (256 weight columns each)
-};
 
 __device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, Barriers* sb, int* status, int id) {
     volatile int* abort = &sb->abort;
@@ -105,30 +110,41 @@ __device__ __forceinline__ bool pk_wait(uint64_t* bar, uint32_t parity, Barriers
     return wait_slow(b, parity, sb, status, id);
 }
 
-// The seq-th tile of this CTA (seq is advanced), or n_tiles when the schedule has ended, a wait
+__device__ __forceinline__ uint4 ring_load(const uint4* e) {
+    uint4 v;
+    asm volatile("ld.volatile.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(ptx::smem_u32(e)));
+    return v;
+}
+
+// The seq-th tile of this CTA (seq is advanced) into `ti`; false when the schedule has ended, a wait
 // expired or another role aborted.
-__device__ __forceinline__ int next_tile(Barriers* sb, uint32_t& seq, int n_tiles, int* status) {
-    const volatile unsigned long long* e = &sb->tile_ring[seq % kTileRing];
+__device__ __forceinline__ bool next_tile(Barriers* sb, uint32_t& seq, TileInfo& ti, int* status) {
+    const uint4* e = &sb->tile_ring[seq % kTileRing];
     const uint32_t want = seq + 1;
-    unsigned long long v = *e;
-    if ((uint32_t)(v >> 32) != want) {
+    uint4 v = ring_load(e);
+    if (v.x != want) {
         volatile int* abort = &sb->abort;
         const uint64_t t0 = ptx::globaltimer_ns();
         uint32_t spins = 0;
-        while ((uint32_t)((v = *e) >> 32) != want) {
+        while ((v = ring_load(e)).x != want) {
             if ((++spins & 0xFF) == 0) {
-                if (*abort) return n_tiles;
+                if (*abort) return false;
                 if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
                     *abort = 1;
                     report_status(status, kDevWaitExpired, 90);
-                    return n_tiles;
+                    return false;
                 }
             }
         }
     }
     ++seq;
-    const int t = (int)(uint32_t)v;
-    return t < n_tiles ? t : n_tiles;
+    ti.row0 = (int)v.y;
+    ti.g = (int)(v.z & 0xFFFFu);
+    ti.rows = (int)(v.z >> 16);
+    ti.j = (int)v.w;
+    return ti.rows != 0;
 }
 
 // Rows of an m-tile of an expert with `rows` rows: the expert is cut into the fewest tiles of at
@@ -169,21 +185,18 @@ __device__ __forceinline__ TileInfo locate_tile(int t, const int* tile_prefix, c
 // Position of a dequant thread in the (tile, stage) sequence of its CTA; wp = the thread's 16 bytes
 // of k-chunk 0 of that stage.
 struct DqIter {
-    int t, kt;
+    int kt;
     uint32_t seq;
     bool valid;
+    TileInfo ti;
     const uint8_t* wp;
 };
-__device__ __forceinline__ void dq_locate(DqIter& it, const uint8_t* __restrict__ w, const GemmArgs& a, int thread_off,
-                                          int n_tiles, int n_kt, const int* tile_prefix, const int* row_start, int n_nt) {
-    it.valid = it.t < n_tiles;
+__device__ __forceinline__ void dq_locate(DqIter& it, const uint8_t* __restrict__ w, int thread_off, int n_kt, int n_nt) {
     if (!it.valid) return;
-    const TileInfo ti = locate_tile(it.t, tile_prefix, row_start, a.G, n_nt);
-    it.wp = w + (((size_t)ti.g * n_nt + ti.j) * n_kt + it.kt) * (size_t)kStageWBytes + thread_off;
+    it.wp = w + (((size_t)it.ti.g * n_nt + it.ti.j) * n_kt + it.kt) * (size_t)kStageWBytes + thread_off;
 }
 __device__ __forceinline__ void dq_advance(DqIter& it, int step, const uint8_t* __restrict__ w, const GemmArgs& a,
-                                           int thread_off, int n_kt, int n_tiles, const int* tile_prefix,
-                                           const int* row_start, int n_nt, Barriers* sb) {
+                                           int thread_off, int n_kt, int n_nt, Barriers* sb) {
     it.kt += step;
     if (it.kt < n_kt) {
         it.wp += (size_t)step * kStageWBytes;
@@ -191,9 +204,9 @@ __device__ __forceinline__ void dq_advance(DqIter& it, int step, const uint8_t* 
     }
     do {
         it.kt -= n_kt;
-        it.t = next_tile(sb, it.seq, n_tiles, a.status);
-    } while (it.kt >= n_kt && it.t < n_tiles);
-    dq_locate(it, w, a, thread_off, n_tiles, n_kt, tile_prefix, row_start, n_nt);
+        it.valid = next_tile(sb, it.seq, it.ti, a.status);
+    } while (it.kt >= n_kt && it.valid);
+    dq_locate(it, w, thread_off, n_kt, n_nt);
 }
 
 // GATE_UP: a tile's half 0 holds 128 gate columns and half 1 the up columns of the same indices; the
@@ -229,7 +242,7 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         }
         sb->n_tiles = acc;
         sb->abort = 0;
-        for (int i = 0; i < kTileRing; ++i) sb->tile_ring[i] = 0ull;
+        for (int i = 0; i < kTileRing; ++i) sb->tile_ring[i] = make_uint4(0u, 0u, 0u, 0u);
         for (int i = 0; i < kXStages; ++i) {
             ptx::mbar_init(ptx::smem_u32(&sb->x_full[i]), 1);
             ptx::mbar_init(ptx::smem_u32(&sb->x_empty[i]), 1);
@@ -265,35 +278,43 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             bool ok = true;
             int* ticket = a.status + 2;  // zeroed by the host before the launch
             int held = atomicAdd(ticket, 1);
-            auto publish = [&]() -> int {
-                const int t = held < n_tiles ? held : n_tiles;
-                *reinterpret_cast<volatile unsigned long long*>(&sb->tile_ring[published % kTileRing]) =
-                    ((unsigned long long)(published + 1) << 32) | (uint32_t)t;
+            TileInfo far_ti;  // the tile published last, resolved
+            auto publish = [&]() -> bool {
+                const bool live = held < n_tiles;
+                uint4 entry = make_uint4(published + 1, 0u, 0u, 0u);  // rows 0: the schedule has ended
+                if (live) {
+                    far_ti = locate_tile(held, tile_prefix, row_start, a.G, n_nt);
+                    entry.y = (uint32_t)far_ti.row0;
+                    entry.z = (uint32_t)far_ti.g | ((uint32_t)far_ti.rows << 16);
+                    entry.w = (uint32_t)far_ti.j;
+                }
+                asm volatile("st.volatile.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(
+                                 ptx::smem_u32(&sb->tile_ring[published % kTileRing])),
+                             "r"(entry.x), "r"(entry.y), "r"(entry.z), "r"(entry.w)
+                             : "memory");
                 ++published;
-                if (t < n_tiles) held = atomicAdd(ticket, 1);
-                return t;
+                if (live) held = atomicAdd(ticket, 1);
+                return live;
             };
             // L2 prefetch of the packed stage kL2Ahead further on (a stage is 16 KB contiguous)
-            int far_t = publish(), far_kt = 0;
+            bool far_live = publish();
+            int far_kt = 0;
             const uint8_t* far_p = nullptr;
             auto far_locate = [&]() {
-                if (far_t >= n_tiles) return;
-                const TileInfo ti = locate_tile(far_t, tile_prefix, row_start, a.G, n_nt);
-                far_p = weight + ((size_t)ti.g * n_nt + ti.j) * n_kt * (size_t)kStageWBytes;
+                if (far_live) far_p = weight + ((size_t)far_ti.g * n_nt + far_ti.j) * n_kt * (size_t)kStageWBytes;
             };
             far_locate();
             auto far_step = [&]() {
                 ptx::bulk_prefetch_l2(far_p + (size_t)far_kt * kStageWBytes, kStageWBytes);
                 if (++far_kt < n_kt) return;
                 far_kt = 0;
-                far_t = publish();
+                far_live = publish();
                 far_locate();
             };
-            for (int i = 0; i < kL2Ahead && far_t < n_tiles; ++i) far_step();
+            for (int i = 0; i < kL2Ahead && far_live; ++i) far_step();
             for (;;) {
-                const int t = next_tile(sb, seq, n_tiles, a.status);
-                if (t >= n_tiles || !ok) break;
-                const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
+                TileInfo ti;
+                if (!next_tile(sb, seq, ti, a.status) || !ok) break;
                 // the tile's rows rounded up to the small box; rows past the expert's end belong to the
                 // next expert (or are zero-filled past M) and land in accumulator columns never stored
                 const int r32 = (ti.rows + kSmallBox - 1) & ~(kSmallBox - 1);
@@ -310,7 +331,7 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     for (int b = 0; b < n_small; ++b)
                         ptx::tma_load_2d(dst + (uint32_t)((n_big * kBigBox + b * kSmallBox) * kBK * 2), &tmap_xs, bar, kx,
                                          ti.row0 + n_big * kBigBox + b * kSmallBox);
-                    if (far_t < n_tiles) far_step();
+                    if (far_live) far_step();
                 }
             }
             if (!ok)
@@ -334,9 +355,8 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             // after a stage's MMAs are issued, so that the poll's latency runs beside the commit's
             bool ready = false;
             for (;;) {
-                const int t = next_tile(sb, seq, n_tiles, a.status);
-                if (t >= n_tiles || !ok) break;
-                const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
+                TileInfo ti;
+                if (!next_tile(sb, seq, ti, a.status) || !ok) break;
                 const uint32_t idesc = ptx::umma_idesc_bf16(128, (ti.rows + 15) & ~15, false);
                 // the epilogue must have drained the previous tile's accumulators
                 if (tiles_done >= 1 && !pk_wait(&sb->t_empty, (tiles_done - 1) & 1, sb, a.status, 30)) { ok = false; break; }
@@ -396,9 +416,8 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         uint32_t use = 0, seq = 0;
         bool scattered = false;
         for (;;) {
-            const int t = next_tile(sb, seq, n_tiles, a.status);
-            if (t >= n_tiles) break;
-            const TileInfo ti = locate_tile(t, tile_prefix, row_start, a.G, n_nt);
+            TileInfo ti;
+            if (!next_tile(sb, seq, ti, a.status)) break;
             const int ci = quarter * 32 + lane;  // column inside a half
             const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(a.scale) + (size_t)ti.g * a.N;
             const __nv_bfloat16* op = has_offset ? a.offset + (size_t)ti.g * a.N : nullptr;
@@ -506,10 +525,10 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         const uint32_t ta0 = tmem_base + kACol + (uint32_t)((wb >> 2) * 32) + ((uint32_t)((wb & 3) * 32) << 16);
         DqIter pf;
         pf.seq = 0;
-        pf.t = next_tile(sb, pf.seq, n_tiles, a.status);
+        pf.valid = next_tile(sb, pf.seq, pf.ti, a.status);
         pf.kt = 0;
-        dq_locate(pf, weight, a, thread_off, n_tiles, n_kt, tile_prefix, row_start, n_nt);
-        if (grp > 0 && pf.valid) dq_advance(pf, grp, weight, a, thread_off, n_kt, n_tiles, tile_prefix, row_start, n_nt, sb);
+        dq_locate(pf, weight, thread_off, n_kt, n_nt);
+        if (grp > 0 && pf.valid) dq_advance(pf, grp, weight, a, thread_off, n_kt, n_nt, sb);
         uint4 regs[kPrefetch][4];
         bool loaded[kPrefetch];
 #pragma unroll
@@ -518,7 +537,7 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             if (pf.valid) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) regs[u][i] = __ldg(reinterpret_cast<const uint4*>(pf.wp + i * 512));
-                dq_advance(pf, kDqGroups, weight, a, thread_off, n_kt, n_tiles, tile_prefix, row_start, n_nt, sb);
+                dq_advance(pf, kDqGroups, weight, a, thread_off, n_kt, n_nt, sb);
             }
         }
         uint32_t ib = grp;
@@ -560,7 +579,7 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 if (pf.valid) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) regs[u][i] = __ldg(reinterpret_cast<const uint4*>(pf.wp + i * 512));
-                    dq_advance(pf, kDqGroups, weight, a, thread_off, n_kt, n_tiles, tile_prefix, row_start, n_nt, sb);
+                    dq_advance(pf, kDqGroups, weight, a, thread_off, n_kt, n_nt, sb);
                 }
                 ib += kDqGroups;
             }
