@@ -8,7 +8,8 @@ were never published (``ascend-closed/README.md``).
     python -m ascend_kernel_b200.check_installed_ops
 """
 REFERENCE_OPS = ["grouped_soft_gemv", "grouped_gemm"]                     # pybind.cpp:14-19 of the reference
-ADDED_OPS = ["fp4_dequant", "fp4_dequant_bf16_scale", "fp8_dequant", "fp4_scale_fold", "last_status", "check_status"]
+ADDED_OPS = ["fp4_dequant", "fp4_dequant_bf16_scale", "fp8_dequant", "fp4_scale_fold", "pack_weight_int8",
+             "grouped_gemm_packed", "last_status", "check_status"]
 
 
 def check(verbose: bool = True) -> None:

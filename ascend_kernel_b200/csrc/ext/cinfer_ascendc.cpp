@@ -231,6 +231,48 @@ void Fp8Dequant(at::Tensor codes, at::Tensor scale, at::Tensor output) {
              "fp8_dequant");
 }
 
+at::Tensor PackWeightInt8(at::Tensor weight, bool gate_up) {
+    check_tensor(weight, "weight");
+    TORCH_CHECK(weight.dim() == 3 && weight.element_size() == 1, "weight: int8 [G, K, N]");
+    at::Tensor out = at::empty_like(weight);
+    c10::cuda::CUDAGuard guard(weight.device());
+    raise_on(b200moe_pack_weight_int8(weight.data_ptr(), out.data_ptr(), weight.size(0), weight.size(1), weight.size(2),
+                                      gate_up ? 1 : 0, c10::cuda::getCurrentCUDAStream().stream()),
+             "pack_weight_int8");
+    return out;
+}
+
+// grouped_gemm with computeType "int8" on weights from pack_weight_int8 (same keyword names; scale / offset in
+// the original column order; gate_up_silu: output [M, N/2] = bf16(silu(gate) * up)).
+void GroupedGemmPacked(at::Tensor x, at::Tensor weight, at::Tensor antiquantScaleOptional,
+                       c10::optional<at::Tensor> antiquantOffsetOptional, at::Tensor groupListOptional, at::Tensor output,
+                       int64_t group_list_type, bool gate_up_silu) {
+    check_tensor(x, "x"); check_tensor(weight, "weight"); check_tensor(antiquantScaleOptional, "antiquantScaleOptional");
+    check_tensor(groupListOptional, "groupListOptional"); check_tensor(output, "output");
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16 && output.scalar_type() == at::kBFloat16, "x and output must be bfloat16");
+    TORCH_CHECK(groupListOptional.scalar_type() == at::kLong, "group_list must be int64");
+    TORCH_CHECK(x.dim() == 2 && weight.dim() == 3 && weight.element_size() == 1, "expected x [M,K], packed weight [G,K,N]");
+    Dims d{x.size(0), x.size(1), weight.size(2), weight.size(0)};
+    TORCH_CHECK(weight.size(1) == d.K && output.size(0) == d.M && output.size(1) == (gate_up_silu ? d.N / 2 : d.N) &&
+                groupListOptional.numel() == d.G, "shape mismatch between x, weight, output and group_list");
+    check_scale(antiquantScaleOptional, B200MOE_CT_INT8, d, "antiquantScaleOptional");
+    const void* offset = nullptr;
+    if (antiquantOffsetOptional.has_value() && antiquantOffsetOptional->defined() && antiquantOffsetOptional->numel() > 0) {
+        check_tensor(*antiquantOffsetOptional, "antiquantOffsetOptional");
+        check_scale(*antiquantOffsetOptional, B200MOE_CT_INT8, d, "antiquantOffsetOptional");
+        offset = antiquantOffsetOptional->data_ptr();
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    auto stream = c10::cuda::getCurrentCUDAStream();
+    const size_t ws_bytes = b200moe_grouped_gemm_workspace_bytes(d.M, d.K, d.N, d.G, B200MOE_CT_INT8, B200MOE_LAYOUT_CANONICAL);
+    at::Tensor ws = workspace_for(x, ws_bytes, stream.stream());
+    raise_on(b200moe_grouped_gemm_int8_packed(x.data_ptr(), weight.data_ptr(), antiquantScaleOptional.data_ptr(), offset,
+                                              groupListOptional.data_ptr<int64_t>(), output.data_ptr(), d.M, d.K, d.N, d.G,
+                                              (int)group_list_type, gate_up_silu ? 1 : 0, ws.data_ptr(), ws_bytes,
+                                              stream.stream()),
+             "grouped_gemm_packed");
+}
+
 at::Tensor Fp4ScaleFold(at::Tensor block_scale, at::Tensor global_scale) {
     check_tensor(block_scale, "block_scale"); check_tensor(global_scale, "global_scale");
     TORCH_CHECK(block_scale.dim() == 3 && block_scale.scalar_type() == at::kBFloat16, "block_scale: bfloat16 [G, N, K/16]");
@@ -259,6 +301,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("fp4_dequant_bf16_scale", &Fp4DequantBf16Scale, "codes"_a, "scale"_a, "output"_a, "weight_layout"_a = "ascend",
           "FP4(e2m1) x bf16 scale per 16 k -> BF16 weights.");
     m.def("fp8_dequant", &Fp8Dequant, "codes"_a, "scale"_a, "output"_a, "FP8(e4m3) x fp32 scale per 128x128 -> BF16 weights.");
+    m.def("pack_weight_int8", &PackWeightInt8, "weight"_a, "gate_up"_a = false,
+          "int8 [G,K,N] -> the tile-packed order grouped_gemm_packed reads.");
+    m.def("grouped_gemm_packed", &GroupedGemmPacked, "x"_a, "weight"_a, "antiquantScaleOptional"_a,
+          "antiquantOffsetOptional"_a, "groupListOptional"_a, "output"_a, "group_list_type"_a = 0, "gate_up_silu"_a = false,
+          "GROUP GEMM on int8 weights repacked once.");
     m.def("fp4_scale_fold", &Fp4ScaleFold, "block_scale"_a, "global_scale"_a, "Two-level FP4 scale fold.");
     m.def("last_status", [](bool clear) { return LastStatus(clear); }, "clear"_a = false,
           "(code, detail) of the first device-side finding since the status was last cleared.");

@@ -108,3 +108,21 @@ def test_hashed_inputs_have_the_same_bits_on_the_gpu_and_on_the_cpu():
     b = inputs.config4("cpu", n_tokens=2, hidden=64, n_experts=4, inter=32, top_k=2, seed=4, expert_lo=1, expert_hi=3)
     for k in ("w13", "s13", "o13", "w2", "s2", "o2"):
         assert torch.equal(a[k].cpu().view(torch.uint8), b[k].view(torch.uint8)), k
+
+
+def test_packed_int8_path_of_the_compiled_module():
+    """pack_weight_int8 + grouped_gemm_packed of the compiled module give the bits of its grouped_gemm."""
+    m = _module()
+    gen = torch.Generator().manual_seed(2)
+    x = torch.randn(300, 128, generator=gen).to(torch.bfloat16).cuda()
+    w = torch.randint(-128, 128, (3, 128, 512), generator=gen, dtype=torch.int8).cuda()
+    s = (torch.rand(3, 512, generator=gen) * 0.009 + 0.001).to(torch.bfloat16).cuda()
+    o = (torch.rand(3, 512, generator=gen) * 8 - 4).to(torch.bfloat16).cuda()
+    gl = torch.tensor([137, 137, 300], dtype=torch.int64).cuda()
+    a = torch.zeros(300, 512, dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros_like(a)
+    m.grouped_gemm(x, w, s, o, gl, "int8", a)
+    m.grouped_gemm_packed(x, m.pack_weight_int8(w), s, o, gl, b)
+    torch.cuda.synchronize()
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    assert tuple(m.last_status()) == (0, 0)

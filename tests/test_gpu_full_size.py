@@ -81,6 +81,20 @@ def test_prefill_gemm_config3_properties():
              int(starts[nonempty[len(nonempty) // 2]] + 1), 0, M - 1]
     _sample_rows_against_oracle(dict(c, x=x), y, counts, picks)
     assert _check_rows_by_expert(dict(c, x=x), y, counts, "int8", n_experts=12) >= 64
+    # the packed entry point on the same problem (experts from 0 to 16 000 rows: up to 105 m-tiles of one
+    # expert): the same exact products, summed per tile in the same k order
+    from ascend_kernel_b200 import ops
+
+    yp = torch.full((M + 3, N), SENTINEL, dtype=torch.bfloat16, device="cuda")
+    wp = ops.pack_weight_int8(c["weight"])
+    ws = ops.grouped_gemm_packed(x, wp, c["scale"], c["offset"], c["counts"], yp, group_list_type=1, return_workspace=True)
+    torch.cuda.synchronize()
+    assert ak.read_status(ws) == (0, 0)
+    del wp
+    assert bool((yp[M:] == SENTINEL).all())
+    assert _check_rows_by_expert(dict(c, x=x), yp, counts, "int8", n_experts=12) >= 64
+    assert float((yp[:M].float() - y[:M].float()).abs().max()) <= 0.02 * float(y[:M].float().abs().max())
+    del yp
     # linearity: scaling x by two scales every output by two, exactly (no rounding is involved)
     y2 = torch.empty_like(y)
     ak.grouped_gemm((x.float() * 2).to(torch.bfloat16), c["weight"], c["scale"], c["offset"], c["counts"], "int8", y2,
