@@ -26,7 +26,8 @@ EXPORTS = [
     "b200moe_moe_route", "b200moe_moe_regroup_index", "b200moe_grouped_gemm_int8_noalloc", "b200moe_grouped_gemm_int8_noalloc_max_rows", "b200moe_noalloc_read_status",
     "b200moe_ep_post_counts", "b200moe_ep_dispatch", "b200moe_ep_wait", "b200moe_ep_post", "b200moe_ep_combine",
     "b200moe_fp4_dequant_bf16_scale", "b200moe_fp8_dequant", "b200moe_fp4_scale_fold",
-    "b200moe_silu_mul_dyn", "b200moe_grouped_gemm_int8_silu", "b200moe_pack_weight_int8", "b200moe_grouped_gemm_int8_packed", "b200moe_grouped_gemm_int8_packed_scatter", "b200moe_ipc_alloc", "b200moe_ipc_open", "b200moe_ipc_close", "b200moe_ipc_free",
+    "b200moe_silu_mul_dyn", "b200moe_grouped_gemm_int8_silu", "b200moe_pack_weight_int8", "b200moe_grouped_gemm_int8_packed", "b200moe_grouped_gemm_int8_packed_scatter",
+    "b200moe_set_gemm_reserved_sms", "b200moe_ipc_alloc", "b200moe_ipc_open", "b200moe_ipc_close", "b200moe_ipc_free",
 ]
 
 EP_MAX_WORLD = 8
@@ -37,7 +38,7 @@ EP_SIG_COUNTS, EP_SIG_ROWS, EP_SIG_RESULTS = 0, 1, 2
 class EpComm(ctypes.Structure):
     """``b200moe_ep_comm`` of include/b200moe.h."""
     _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("n_experts", ctypes.c_int32),
-                ("reserved", ctypes.c_int32), ("cap_rows", ctypes.c_int64), ("hidden", ctypes.c_int64),
+                ("dispatch_ctas", ctypes.c_int32), ("cap_rows", ctypes.c_int64), ("hidden", ctypes.c_int64),
                 ("peer_recv_x", ctypes.c_void_p * EP_MAX_WORLD), ("peer_y", ctypes.c_void_p * EP_MAX_WORLD),
                 ("peer_counts", ctypes.c_void_p * EP_MAX_WORLD), ("peer_signal", ctypes.c_void_p * EP_MAX_WORLD),
                 ("status", ctypes.c_void_p), ("step_counter", ctypes.c_void_p),
@@ -75,6 +76,8 @@ def _load() -> ctypes.CDLL:
     lib.b200moe_grouped_gemm_int8_packed_scatter.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.POINTER(vp), i64, i64, i64, i64, i64,
                                                              i64, i32, vp, sz, vp]
     lib.b200moe_grouped_gemm_int8_packed_scatter.restype = i32
+    lib.b200moe_set_gemm_reserved_sms.argtypes = [i32]
+    lib.b200moe_set_gemm_reserved_sms.restype = i32
     lib.b200moe_grouped_gemm_int8_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, vp]
     lib.b200moe_grouped_gemm_int8_noalloc.restype = i32
     lib.b200moe_grouped_gemm_int8_noalloc_max_rows.argtypes = []

@@ -43,6 +43,7 @@ struct EpComm {
     const uint4* y[B200MOE_EP_MAX_WORLD];
     int32_t* counts[B200MOE_EP_MAX_WORLD];             // [world, n_experts] on every rank
     unsigned long long* signal[B200MOE_EP_MAX_WORLD];  // [3, B200MOE_EP_MAX_WORLD] on every rank
+    int dispatch_ctas;                                 // 0, or the most CTAs the dispatch kernel may use
     int* status;                                       // local: two status words
     unsigned long long* step_counter;                  // local: the step number when the host passes 0
     long long* ret_code[B200MOE_EP_MAX_WORLD];         // optional: where each delivered row's result returns to
@@ -282,6 +283,7 @@ static int to_comm(const b200moe_ep_comm* h, EpComm* c) {
     c->e_local = h->n_experts / h->world;
     c->cap_rows = h->cap_rows;
     c->width16 = (int)(h->hidden / 8);
+    c->dispatch_ctas = h->dispatch_ctas;
     for (int r = 0; r < h->world; ++r) {
         if (!h->peer_recv_x[r] || !h->peer_y[r] || !h->peer_counts[r] || !h->peer_signal[r]) return B200MOE_ERR_NULL_POINTER;
         if (!aligned16(h->peer_recv_x[r]) || !aligned16(h->peer_y[r])) return B200MOE_ERR_ALIGNMENT;
@@ -324,7 +326,7 @@ extern "C" int b200moe_ep_dispatch(const b200moe_ep_comm* comm, const void* x, c
     if (!aligned16(x)) return B200MOE_ERR_ALIGNMENT;
     // one warp per row, 32 warps per CTA; at least one CTA so that the plan and the signal happen
     long long blocks = (n_rows + 31) / 32;
-    const long long cap = 4LL * sm_count();
+    const long long cap = c.dispatch_ctas > 0 ? (long long)c.dispatch_ctas : 4LL * sm_count();
     blocks = blocks < 1 ? 1 : (blocks > cap ? cap : blocks);
     ep_dispatch_kernel<<<(unsigned)blocks, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
         c, static_cast<const uint4*>(x), token_of, (int)n_rows, (unsigned long long)step, remote_pos,

@@ -32,12 +32,23 @@
 // pair: a relay lane of the dequant group (which has slack) waits for the stage's x tile before the
 // group reports the stage full, and hands the x slot back to the producer when it observes the
 // completion of the MMAs that read it.  Every wait is bounded.
+#include <atomic>
+
 #include "common.cuh"
 #include "gemm_args.cuh"
 #include "ptx.cuh"
 
 namespace b200moe {
 namespace pk {
+
+// SMs the persistent kernels of this file leave to other kernels (b200moe_set_gemm_reserved_sms)
+static std::atomic<int> g_reserved_sms{0};
+static unsigned grid_ctas() {
+    const int sms = sm_count();
+    int r = g_reserved_sms.load(std::memory_order_relaxed);
+    r = r < 0 ? 0 : (r > sms - 1 ? sms - 1 : r);
+    return (unsigned)(sms - r);
+}
 
 constexpr int kBK = 64;        // k per stage
 constexpr int kTileN = 256;    // weight columns per tile: two MMA halves of 128
@@ -625,6 +636,8 @@ __global__ void pack_weight_int8_kernel(const int8_t* __restrict__ w, uint4* __r
 
 using namespace b200moe;
 
+extern "C" int b200moe_set_gemm_reserved_sms(int n) { return pk::g_reserved_sms.exchange(n < 0 ? 0 : n); }
+
 extern "C" int b200moe_pack_weight_int8(const void* weight, void* packed, int64_t G, int64_t K, int64_t N, int gate_up,
                                         void* stream) {
     if (G < 0 || K < 0 || N < 0 || (K % pk::kBK) != 0 || (N % pk::kTileN) != 0) return B200MOE_ERR_SHAPE;
@@ -696,11 +709,11 @@ static int packed_launch(const void* x, const void* packed, const void* scale, c
     if (gate_up_silu) {
         B200MOE_CUDA_TRY(cudaFuncSetAttribute(pk::grouped_gemm_packed_kernel<true>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        pk::grouped_gemm_packed_kernel<true><<<sm_count(), pk::kThreads, smem, s>>>(tx, txs, static_cast<const uint8_t*>(packed), a);
+        pk::grouped_gemm_packed_kernel<true><<<pk::grid_ctas(), pk::kThreads, smem, s>>>(tx, txs, static_cast<const uint8_t*>(packed), a);
     } else {
         B200MOE_CUDA_TRY(cudaFuncSetAttribute(pk::grouped_gemm_packed_kernel<false>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        pk::grouped_gemm_packed_kernel<false><<<sm_count(), pk::kThreads, smem, s>>>(tx, txs, static_cast<const uint8_t*>(packed), a);
+        pk::grouped_gemm_packed_kernel<false><<<pk::grid_ctas(), pk::kThreads, smem, s>>>(tx, txs, static_cast<const uint8_t*>(packed), a);
     }
     B200MOE_CUDA_TRY(cudaGetLastError());
     return B200MOE_OK;

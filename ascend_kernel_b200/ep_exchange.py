@@ -1,8 +1,11 @@
 """Expert-parallel token exchange over NVLink peer memory (host side).
 
-``PeerExchange`` owns this rank's four exchange buffers (allocated by the C library so that the
+``PeerExchange`` owns this rank's exchange buffers (allocated by the C library so that the
 other processes of the node can map them through CUDA IPC), maps every peer's buffers, and wraps
-the exchange kernels of ``include/b200moe.h`` (``b200moe_ep_*``).  torch.distributed is used once,
+the exchange kernels of ``include/b200moe.h`` (``b200moe_ep_*``).  With ``n_buffers=2`` the row,
+count and return buffers exist twice and a step uses the set its ``parity`` names, so that the
+exchange of one step can run while the expert GEMMs of the step before still read the other set
+(moe_layer.OverlappedSteps); the signal words are shared, their step numbers only grow.  torch.distributed is used once,
 at construction, to pass the 64-byte IPC handles around; a layer step itself makes no collective
 call and never synchronises with the host.
 """
@@ -33,10 +36,13 @@ def _as_tensor(ptr: int, shape, dtype, device):
 
 
 class PeerExchange:
-    def __init__(self, group, n_experts: int, hidden: int, cap_rows: int, device):
+    def __init__(self, group, n_experts: int, hidden: int, cap_rows: int, device, n_buffers: int = 1):
         """``group``: the expert-parallel process group (all ranks on one node) or None for a single
         rank.  ``cap_rows``: rows this rank's receive / result buffers hold; the worst case is
-        (tokens of all ranks) x top_k."""
+        (tokens of all ranks) x top_k.  ``n_buffers``: 1, or 2 for steps that overlap."""
+        if n_buffers not in (1, 2):
+            raise ValueError("n_buffers must be 1 or 2")
+        self.n_buffers = n_buffers
         self.device = torch.device(device)
         self.n_experts, self.hidden, self.cap_rows = n_experts, hidden, cap_rows
         if group is not None:
@@ -50,9 +56,12 @@ class PeerExchange:
         self.step = 0
         # rows this rank itself dispatches at most (its tokens x top_k): the size of its return buffer
         self.cap_send = max(1, cap_rows // self.world)
-        sizes = {"recv_x": cap_rows * hidden * 2, "y": cap_rows * hidden * 2,
-                 "counts": self.world * n_experts * 4, "signal": 3 * _abi.EP_MAX_WORLD * 8,
-                 "ret": self.cap_send * hidden * 2, "ret_code": cap_rows * 8}
+        # bytes of ONE set; the sets of a doubled buffer follow one another in the same allocation
+        one = {"recv_x": cap_rows * hidden * 2, "y": cap_rows * hidden * 2,
+               "counts": -(-self.world * n_experts * 4 // 256) * 256, "signal": 3 * _abi.EP_MAX_WORLD * 8,
+               "ret": self.cap_send * hidden * 2, "ret_code": cap_rows * 8}
+        doubled = ("recv_x", "counts", "ret", "ret_code") if n_buffers == 2 else ()
+        sizes = {name: nbytes * (2 if name in doubled else 1) for name, nbytes in one.items()}
         self._own, handles = {}, {}
         with torch.cuda.device(self.device):
             for name, nbytes in sizes.items():
@@ -84,26 +93,38 @@ class PeerExchange:
                 self._peer[name][0] = self._own[name]
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._done = torch.zeros(1, dtype=torch.int32, device=self.device)
-        c = _abi.EpComm()
-        c.world, c.rank, c.n_experts, c.cap_rows, c.hidden = self.world, self.rank, n_experts, cap_rows, hidden
-        for r in range(self.world):
-            c.peer_recv_x[r], c.peer_y[r] = self._peer["recv_x"][r], self._peer["y"][r]
-            c.peer_counts[r], c.peer_signal[r] = self._peer["counts"][r], self._peer["signal"][r]
-            c.peer_ret[r], c.peer_ret_code[r] = self._peer["ret"][r], self._peer["ret_code"][r]
-        c.cap_send = self.cap_send
         self._step_dev = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.device_steps = False  # True: the step number lives on the device (constant kernel arguments)
-        c.status = self.status.data_ptr()
-        c.step_counter = self._step_dev.data_ptr()
-        self._comm = c
-        # torch views of the two local row buffers (inputs / outputs of the grouped GEMMs)
-        self.recv_x = _as_tensor(self._own["recv_x"], (cap_rows, hidden), torch.bfloat16, self.device)
+
+        def at(name, r, p):  # rank r's set p of buffer `name`, as mapped in this process
+            return self._peer[name][r] + (p * one[name] if name in doubled else 0)
+
+        self._comms = []
+        for p in range(n_buffers):
+            c = _abi.EpComm()
+            c.world, c.rank, c.n_experts, c.cap_rows, c.hidden = self.world, self.rank, n_experts, cap_rows, hidden
+            for r in range(self.world):
+                c.peer_recv_x[r], c.peer_y[r] = at("recv_x", r, p), at("y", r, p)
+                c.peer_counts[r], c.peer_signal[r] = at("counts", r, p), at("signal", r, p)
+                c.peer_ret[r], c.peer_ret_code[r] = at("ret", r, p), at("ret_code", r, p)
+            c.cap_send = self.cap_send
+            c.status = self.status.data_ptr()
+            c.step_counter = self._step_dev.data_ptr()
+            self._comms.append(c)
+        self._comm = self._comms[0]
+        # torch views of the local row buffers (inputs / outputs of the grouped GEMMs), one per set
+        self.recv_x_sets = [_as_tensor(at("recv_x", self.rank, p), (cap_rows, hidden), torch.bfloat16, self.device)
+                            for p in range(n_buffers)]
         self.y = _as_tensor(self._own["y"], (cap_rows, hidden), torch.bfloat16, self.device)
         # results pushed back by the owners' down projections: this rank's return buffer (one row per
         # dispatched (token, j) pair, in sorted order), and the return addresses of the rows it received
-        self.ret = _as_tensor(self._own["ret"], (self.cap_send, hidden), torch.bfloat16, self.device)
-        self.ret_code = _as_tensor(self._own["ret_code"], (cap_rows,), torch.int64, self.device)
-        self.ret_ptrs = [self._peer["ret"][r] for r in range(self.world)]
+        self.ret_sets = [_as_tensor(at("ret", self.rank, p), (self.cap_send, hidden), torch.bfloat16, self.device)
+                         for p in range(n_buffers)]
+        self.ret_code_sets = [_as_tensor(at("ret_code", self.rank, p), (cap_rows,), torch.int64, self.device)
+                              for p in range(n_buffers)]
+        self.ret_ptrs_sets = [[at("ret", r, p) for r in range(self.world)] for p in range(n_buffers)]
+        self.recv_x, self.ret, self.ret_code, self.ret_ptrs = (self.recv_x_sets[0], self.ret_sets[0],
+                                                               self.ret_code_sets[0], self.ret_ptrs_sets[0])
 
     # ---- one step ---------------------------------------------------------------------------
     def _s(self):
@@ -120,36 +141,56 @@ class PeerExchange:
         self._step_dev.fill_(self.step)
         self.device_steps = True
 
-    def _step_arg(self) -> int:
+    def use_host_steps(self):
+        """Back to step numbers passed by the host (what overlapping steps need: two of them are in
+        flight, each kernel is told which one it belongs to).  Call between steps, with the device idle."""
+        if self.device_steps:
+            torch.cuda.synchronize(self.device)
+            self.step = int(self._step_dev.item())
+            self.device_steps = False
+
+    def _step_arg(self, step=None) -> int:
+        if step is not None:
+            if self.device_steps:
+                raise RuntimeError("explicit step numbers need use_host_steps()")
+            return step
         return 0 if self.device_steps else self.step
 
-    def post_counts(self, counts):
+    # Every kernel wrapper takes the buffer set (``parity``) and, for steps in flight beside one
+    # another, the step number the kernel belongs to (default: the step begun last).
+    def post_counts(self, counts, parity: int = 0, step: int = None):
         with torch.cuda.device(self.device):
-            _abi.check(_lib.b200moe_ep_post_counts(ctypes.byref(self._comm), counts.data_ptr(), self._step_arg(), self._s()),
-                       "ep_post_counts")
+            _abi.check(_lib.b200moe_ep_post_counts(ctypes.byref(self._comms[parity]), counts.data_ptr(),
+                                                   self._step_arg(step), self._s()), "ep_post_counts")
         ops._count(1)
 
-    def dispatch(self, x, token_of):
-        """-> (remote_pos int32 [rows], local_counts int64 [E/world], n_recv int64 [1])"""
+    def dispatch(self, x, token_of, parity: int = 0, step: int = None, out=None, max_ctas: int = 0):
+        """-> (remote_pos int32 [rows], local_counts int64 [E/world], n_recv int64 [1]); ``out``: these
+        three, preallocated.  ``max_ctas`` > 0 bounds the kernel's grid (a dispatch that shares the GPU
+        with a grouped GEMM)."""
+        self._comms[parity].dispatch_ctas = max_ctas
         n_rows = token_of.numel()
-        remote_pos = torch.empty(n_rows, dtype=torch.int32, device=self.device)
-        local_counts = torch.empty(self.n_experts // self.world, dtype=torch.int64, device=self.device)
-        n_recv = torch.empty(1, dtype=torch.int64, device=self.device)
+        if out is None:
+            out = (torch.empty(n_rows, dtype=torch.int32, device=self.device),
+                   torch.empty(self.n_experts // self.world, dtype=torch.int64, device=self.device),
+                   torch.empty(1, dtype=torch.int64, device=self.device))
+        remote_pos, local_counts, n_recv = out
         with torch.cuda.device(self.device):
-            _abi.check(_lib.b200moe_ep_dispatch(ctypes.byref(self._comm), x.data_ptr(), token_of.data_ptr(), n_rows,
-                                                self._step_arg(), remote_pos.data_ptr(), local_counts.data_ptr(),
-                                                n_recv.data_ptr(), self._done.data_ptr(), self._s()), "ep_dispatch")
+            _abi.check(_lib.b200moe_ep_dispatch(ctypes.byref(self._comms[parity]), x.data_ptr(), token_of.data_ptr(),
+                                                n_rows, self._step_arg(step), remote_pos.data_ptr(),
+                                                local_counts.data_ptr(), n_recv.data_ptr(), self._done.data_ptr(),
+                                                self._s()), "ep_dispatch")
         ops._count(1)
         return remote_pos, local_counts, n_recv
 
-    def wait(self, which: int):
+    def wait(self, which: int, step: int = None):
         with torch.cuda.device(self.device):
-            _abi.check(_lib.b200moe_ep_wait(ctypes.byref(self._comm), which, self._step_arg(), self._s()), "ep_wait")
+            _abi.check(_lib.b200moe_ep_wait(ctypes.byref(self._comm), which, self._step_arg(step), self._s()), "ep_wait")
         ops._count(1)
 
-    def post(self, which: int):
+    def post(self, which: int, step: int = None):
         with torch.cuda.device(self.device):
-            _abi.check(_lib.b200moe_ep_post(ctypes.byref(self._comm), which, self._step_arg(), self._s()), "ep_post")
+            _abi.check(_lib.b200moe_ep_post(ctypes.byref(self._comm), which, self._step_arg(step), self._s()), "ep_post")
         ops._count(1)
 
     def combine(self, remote_pos, slot, weight, out=None):
@@ -176,6 +217,7 @@ class PeerExchange:
                 _lib.b200moe_ipc_close(p)
             self._opened = []
             self.recv_x = self.y = self.ret = self.ret_code = None
+            self.recv_x_sets = self.ret_sets = self.ret_code_sets = []
             for name, p in list(self._own.items()):
                 _lib.b200moe_ipc_free(p)
             self._own = {}

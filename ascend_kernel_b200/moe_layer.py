@@ -45,7 +45,7 @@ class CudaRowOps:
 class MoELayer:
     def __init__(self, w13, s13, o13, w2, s2, o2, n_experts: int, top_k: int, group=None, row_ops=CudaRowOps,
                  exchange: str = "nccl", max_tokens: int = 0, fuse_silu: bool = None, gemm: str = None,
-                 weight_format: str = "int8"):
+                 weight_format: str = "int8", exchange_buffers: int = 1):
         """w13 int8 [E_local, H, 2I] (gate columns first), w2 int8 [E_local, I, H]; per-channel bf16
         scales/offsets [E_local, N].  ``group``: a torch.distributed process group or None.
         ``row_ops`` exists so the dispatch / regroup / combine index logic can be exercised by CPU
@@ -66,7 +66,9 @@ class MoELayer:
         None.  Every pass dequantises them to bf16 buffers owned by the layer (FP4 -> BF16 kernel) and
         runs the bf16 grouped GEMM on those: the two-phase structure of the reference's own kernel
         (dequantise to a bf16 workspace, then multiply: grouped_matmul_antiquant.h:632-654,
-        grouped_matmul.h:409-463) with the benchmark's storage format."""
+        grouped_matmul.h:409-463) with the benchmark's storage format.
+        ``exchange_buffers=2`` (p2p exchange only) doubles the exchange buffers, which ``OverlappedSteps``
+        needs to run one step's token exchange beside the expert GEMMs of the step before."""
         self.ops = row_ops
         self.w13, self.s13, self.o13, self.w2, self.s2, self.o2 = w13, s13, o13, w2, s2, o2
         self.n_experts, self.top_k = n_experts, top_k
@@ -113,7 +115,8 @@ class MoELayer:
 
             if max_tokens <= 0:
                 raise ValueError('exchange="p2p" needs max_tokens')
-            self.px = PeerExchange(group, n_experts, self.hidden, max_tokens * self.world * top_k, self.device)
+            self.px = PeerExchange(group, n_experts, self.hidden, max_tokens * self.world * top_k, self.device,
+                                   n_buffers=exchange_buffers)
         elif exchange != "nccl":
             raise ValueError("exchange must be 'nccl' or 'p2p'")
         self.timing = None  # [ev0..ev3] around GEMM1 / SiLU / GEMM2, filled by forward(record=True)
@@ -305,6 +308,103 @@ class MoELayer:
         return out_host
 
 
+class OverlappedSteps:
+    """Steps of a p2p layer with the token exchange of step k+1 beside the expert GEMMs of step k.
+
+    A step is split over two streams.  The exchange stream routes the step's tokens, posts the counts
+    and stores the rows into their owners' receive buffers; the caller's stream waits for every rank's
+    rows, runs the two grouped GEMMs (the second pushes each result row back to its source rank), waits
+    for the pushes of the other ranks and sums each token's rows.  Steps alternate between the two
+    buffer sets of the exchange, so step k+1's rows land in one set while step k's GEMMs read the
+    other; step k+2's exchange waits for step k's weighted sum.  The persistent GEMM kernels leave
+    ``reserve_sms`` multiprocessors free (``ops.set_gemm_reserved_sms``): their CTAs fill an SM, and the
+    routing and row-store kernels of the next step need somewhere to run.  Nothing here synchronises
+    with the host or calls a collective; every device-side wait is bounded as in the serial pass.
+
+    ``submit`` takes inputs that are COMPLETE on the device when it is called (or by the ``ready`` event)
+    and must stay untouched until the step's ``rows_sent`` event; results come back in submission order.
+    All ranks must submit the same number of steps.  The layer must have been built with
+    ``exchange="p2p", exchange_buffers=2`` and the packed GEMMs."""
+
+    def __init__(self, layer: "MoELayer", n_tokens: int, reserve_sms: int = 8):
+        if layer.px is None or layer.px.n_buffers != 2 or layer.gemm != "packed":
+            raise RuntimeError('OverlappedSteps needs exchange="p2p", exchange_buffers=2 and the packed GEMMs')
+        self.layer, self.n_tokens, self.reserve_sms = layer, n_tokens, reserve_sms
+        dev, px = layer.device, layer.px
+        px.use_host_steps()
+        self.s_x = torch.cuda.Stream(dev, priority=-1)
+        n_rows = n_tokens * layer.top_k
+        self.sets = []
+        for _ in range(2):
+            self.sets.append(dict(
+                route=ops.moe_route_buffers(n_tokens, layer.n_experts, layer.top_k, dev),
+                disp=(torch.empty(n_rows, dtype=torch.int32, device=dev),
+                      torch.empty(layer.e_local, dtype=torch.int64, device=dev),
+                      torch.empty(1, dtype=torch.int64, device=dev)),
+                act=torch.empty(px.cap_rows, layer.inter, dtype=torch.bfloat16, device=dev),
+                done=None))
+        self.n = 0
+        self.rows_sent = None  # event: the rows of the step submitted last have left (its inputs are free)
+
+    def submit(self, x, logits, ready=None, out=None, record: bool = False):
+        """One step; returns its bf16 [T, H] result, complete in the order of the caller's stream.
+        ``record=True`` leaves CUDA events around the two GEMMs in ``layer.timing``."""
+        layer, px = self.layer, self.layer.px
+        if x.shape[0] != self.n_tokens:
+            raise RuntimeError("OverlappedSteps was built for another token count")
+        p = self.n % 2
+        self.n += 1
+        st = self.sets[p]
+        step = px.begin_step()
+        main = torch.cuda.current_stream()
+        with torch.cuda.stream(self.s_x):
+            if ready is not None:
+                self.s_x.wait_event(ready)
+            if st["done"] is not None:       # the step before last: its weighted sum has read this set
+                self.s_x.wait_event(st["done"])
+            idx, wts, counts, token_of, slot = layer.ops.route(logits, layer.top_k, out=st["route"])
+            px.post_counts(counts, parity=p, step=step)
+            # two 1024-thread CTAs per reserved SM: the dispatch never takes an SM the GEMMs could use
+            _, local_counts, n_recv = px.dispatch(x, token_of, parity=p, step=step, out=st["disp"],
+                                                  max_ctas=2 * self.reserve_sms)
+            sent = torch.cuda.Event()
+            sent.record(self.s_x)
+        self.rows_sent = sent
+        main.wait_event(sent)
+        px.wait(1, step=step)                # rows of every source rank have landed
+        # Only the gate/up GEMM makes room: the next step's exchange is released when the previous step's
+        # weighted sum ends, so it runs beside this kernel; by the down projection it has long started (a
+        # kernel that had not would wait for that GEMM's first CTA to leave, which costs time, not correctness).
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if record else None
+        if ev:
+            ev[0].record()
+        prev = ops.set_gemm_reserved_sms(self.reserve_sms)
+        try:
+            ops.grouped_gemm_packed(px.recv_x_sets[p], layer.w13, layer.s13, layer.o13, local_counts, st["act"],
+                                    group_list_type=1, gate_up_silu=True)
+        finally:
+            ops.set_gemm_reserved_sms(prev)
+        if ev:
+            ev[1].record()
+            ev[2].record()
+        ops.grouped_gemm_packed_scatter(st["act"], layer.w2, layer.s2, layer.o2, local_counts, px.ret_code_sets[p],
+                                        px.ret_ptrs_sets[p], px.cap_send, group_list_type=1)
+        if ev:
+            ev[3].record()
+        layer.timing = ev
+        px.post(2, step=step)                # this rank's pushes are complete and visible
+        px.wait(2, step=step)                # every owner has pushed this rank's rows
+        res = layer.ops.combine(px.ret_sets[p], slot, wts) if out is None else layer.ops.combine(px.ret_sets[p], slot, wts, out)
+        st["done"] = torch.cuda.Event()
+        st["done"].record(main)
+        return res
+
+    def drain(self):
+        """Waits (on the host) for everything submitted."""
+        self.s_x.synchronize()
+        torch.cuda.current_stream().synchronize()
+
+
 class GraphedLayer:
     """One layer pass recorded as CUDA graphs and replayed: a step then costs the host two graph
     launches instead of a dozen kernel launches and as many allocations.  The pass is recorded in two
@@ -401,12 +501,19 @@ class HostPipeline:
     submitted step's result is therefore enqueued by the next ``submit``, by ``flush`` or by
     ``drain``.  ``submit`` returns a PendingResult; ``drain`` waits for everything submitted."""
 
-    def __init__(self, layer: MoELayer, depth: int = 2, graphed: GraphedLayer = None):
+    def __init__(self, layer: MoELayer, depth: int = 2, graphed: GraphedLayer = None,
+                 overlapped: "OverlappedSteps" = None):
         """``graphed``: a GraphedLayer of ``layer`` for the token count the pipeline will be fed;
-        the kernels of a step are then two graph launches."""
+        the kernels of a step are then two graph launches.  ``overlapped``: an OverlappedSteps of
+        ``layer`` instead: a step's token exchange then runs beside the GEMMs of the step before, its
+        input copy is released as soon as the rows of the step that last used the slot have left, and
+        its result is copied out as soon as it exists (the exchange is off the critical path there, so
+        nothing is held back)."""
         if depth < 2:
             raise ValueError("depth must be at least 2")
-        self.layer, self.depth, self.graphed = layer, depth, graphed
+        if graphed is not None and overlapped is not None:
+            raise ValueError("graphed and overlapped exclude one another")
+        self.layer, self.depth, self.graphed, self.overlapped = layer, depth, graphed, overlapped
         self.s_in, self.s_out = torch.cuda.Stream(layer.device), torch.cuda.Stream(layer.device)
         self.slots = [dict(x=None, lg=None, out=None, in_done=None, comp_done=None, out_done=None)
                       for _ in range(depth)]
@@ -441,6 +548,26 @@ class HostPipeline:
         if sl["x"] is None or sl["x"].shape != x_host.shape:
             sl["x"] = torch.empty(x_host.shape, dtype=x_host.dtype, device=self.layer.device)
             sl["lg"] = torch.empty(logits_host.shape, dtype=logits_host.dtype, device=self.layer.device)
+        if self.overlapped is not None:
+            with torch.cuda.stream(self.s_in):
+                if sl.get("rows_sent") is not None:      # the exchange that last read these input buffers
+                    self.s_in.wait_event(sl["rows_sent"])
+                sl["lg"].copy_(logits_host, non_blocking=True)
+                sl["x"].copy_(x_host, non_blocking=True)
+                sl["in_done"] = torch.cuda.Event()
+                sl["in_done"].record(self.s_in)
+            if sl["out_done"] is not None:               # the copy that last read this slot's result
+                main.wait_event(sl["out_done"])
+            if sl["out"] is None or sl["out"].shape != x_host.shape:
+                sl["out"] = torch.empty(x_host.shape, dtype=torch.bfloat16, device=self.layer.device)
+            self.overlapped.submit(sl["x"], sl["lg"], ready=sl["in_done"], out=sl["out"])
+            sl["rows_sent"] = self.overlapped.rows_sent
+            sl["comp_done"] = torch.cuda.Event()
+            sl["comp_done"].record(main)
+            handle = PendingResult(self, step)
+            self.pending = (sl, out_host, handle)
+            self._copy_out(None)
+            return handle
         with torch.cuda.stream(self.s_in):
             # the previous step's rows are with their experts; that step follows, on the same stream,
             # the one that last read these input buffers

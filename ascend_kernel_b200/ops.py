@@ -246,6 +246,12 @@ def grouped_gemm_packed(x, packed, scale, offset, group_list, output, group_list
     return ws if return_workspace else None
 
 
+def set_gemm_reserved_sms(n: int) -> int:
+    """SMs the persistent packed-weight GEMM kernels leave free from now on (process-wide; 0 = none);
+    returns the previous value.  For callers that run other kernels beside a grouped GEMM."""
+    return int(_lib.b200moe_set_gemm_reserved_sms(int(n)))
+
+
 def grouped_gemm_packed_scatter(x, packed, scale, offset, group_list, row_code, dst_ptrs, dst_rows: int,
                                 group_list_type: int = 0):
     """grouped_gemm_packed whose result row r is stored at row ``row_code[r] & 0xffffffff`` of the bf16
@@ -406,20 +412,27 @@ def combine(y, slot, weight, out=None):
     return out
 
 
-def moe_route(logits, top_k: int):
+def moe_route_buffers(n_tokens: int, n_experts: int, top_k: int, device):
+    """The six tensors ``moe_route`` fills (its five results and its scratch), for callers that reuse them."""
+    return (torch.empty(n_tokens, top_k, dtype=torch.int32, device=device),
+            torch.empty(n_tokens, top_k, dtype=torch.float32, device=device),
+            torch.empty(n_experts, dtype=torch.int64, device=device),
+            torch.empty(n_tokens * top_k, dtype=torch.int32, device=device),
+            torch.empty(n_tokens, top_k, dtype=torch.int32, device=device),
+            torch.empty(2 * n_experts, dtype=torch.int32, device=device))
+
+
+def moe_route(logits, top_k: int, out=None):
     """logits bf16 [T, E] -> (idx int32 [T,k], weight fp32 [T,k], counts int64 [E], token_of int32 [T*k],
-    slot int32 [T,k])."""
+    slot int32 [T,k]).  ``out``: the tuple of ``moe_route_buffers`` to fill instead of new tensors."""
     _need_cuda(logits=logits)
     if logits.dtype != torch.bfloat16:
         raise RuntimeError("logits must be bfloat16")
     T, E = logits.shape
     dev = logits.device
-    idx = torch.empty(T, top_k, dtype=torch.int32, device=dev)
-    w = torch.empty(T, top_k, dtype=torch.float32, device=dev)
-    counts = torch.empty(E, dtype=torch.int64, device=dev)
-    token_of = torch.empty(T * top_k, dtype=torch.int32, device=dev)
-    slot = torch.empty(T, top_k, dtype=torch.int32, device=dev)
-    scratch = torch.empty(2 * E, dtype=torch.int32, device=dev)
+    idx, w, counts, token_of, slot, scratch = out if out is not None else moe_route_buffers(T, E, top_k, dev)
+    if idx.shape != (T, top_k) or counts.numel() != E or token_of.numel() != T * top_k:
+        raise RuntimeError("moe_route: output buffers of another shape")
     with torch.cuda.device(dev):
         rc = _lib.b200moe_moe_route(_ptr(logits), T, E, top_k, _ptr(idx), _ptr(w), _ptr(counts), _ptr(token_of),
                                     _ptr(slot), _ptr(scratch), _stream())

@@ -517,8 +517,11 @@ def run_ours(args):
     e_local, t_local = E // world, T // world
     c = inputs.config4(dev, expert_lo=rank * e_local, expert_hi=(rank + 1) * e_local, **CFG)
     exchange = args.exchange if world > 1 else "direct"
+    # several ranks on the peer-memory exchange: a step's token exchange runs beside the GEMMs of the step before
+    overlap = exchange == "p2p" and not args.no_overlap
     layer = MoELayer(c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], E, CFG["top_k"], group,
-                     exchange="p2p" if exchange == "p2p" else "nccl", max_tokens=t_local)
+                     exchange="p2p" if exchange == "p2p" else "nccl", max_tokens=t_local,
+                     exchange_buffers=2 if overlap else 1)
     x_host = c["x"][rank * t_local:(rank + 1) * t_local].contiguous().pin_memory()
     lg_host = c["logits"][rank * t_local:(rank + 1) * t_local].contiguous().pin_memory()
     x, lg = x_host.to(dev), lg_host.to(dev)
@@ -551,21 +554,40 @@ def run_ours(args):
     barrier()
 
     # ---- device-resident timing ----
+    from ascend_kernel_b200.moe_layer import GraphedLayer, HostPipeline, OverlappedSteps
+
+    gemm_ms, gemm_events, phase_events = 0.0, [], []
+    ov = None
+    if overlap:
+        # the phases of a step, from serial passes outside the timed region (overlapped steps have no
+        # phase boundaries on one stream)
+        for i in range(4):
+            layer.forward(x, lg, record=i > 0)
+            if i > 0 and layer.phases is not None:
+                phase_events.append(layer.phases)
+        barrier()
+        ov = OverlappedSteps(layer, t_local, reserve_sms=args.reserve_sms)
+
+    def one_step(record=False):
+        if ov is not None:
+            ov.submit(x, lg, record=record)
+        else:
+            layer.forward(x, lg, record=record)
+
     for _ in range(args.warmup):
-        layer.forward(x, lg)
+        one_step()
     barrier()
     ops.LAUNCHES = 0
-    gemm_ms, gemm_events, phase_events = 0.0, [], []
     with ClockSampler(local_rank) as clk:
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` list only the timed steps
         ev0.record()
         for _ in range(args.steps):
-            layer.forward(x, lg, record=True)
+            one_step(record=True)
             if layer.timing is not None:
                 gemm_events.append(layer.timing)
-            if layer.phases is not None:
+            if ov is None and layer.phases is not None:
                 phase_events.append(layer.phases)
         ev1.record()
         barrier()
@@ -593,21 +615,21 @@ def run_ours(args):
     e1.record()
     barrier()
     latency_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
-    # the same calls with two steps in flight (copy-in / kernels / copy-out on three streams)
-    from ascend_kernel_b200.moe_layer import GraphedLayer, HostPipeline
-
-    # the kernels of a step as one CUDA-graph launch where the step has no host synchronisation
-    graphed = GraphedLayer(layer, t_local) if exchange != "nccl" else None
-    pipe = HostPipeline(layer, depth=2, graphed=graphed)
-    outs = [out_host, torch.empty_like(out_host).pin_memory()]
-    for i in range(min(3, args.warmup)):
-        pipe.submit(x_host, lg_host, outs[i % 2])
+    # the same calls with steps in flight (copy-in / kernels / copy-out on three streams); the kernels of a
+    # step are overlapped steps where those ran above, else one CUDA-graph launch where the step has no host
+    # synchronisation
+    graphed = GraphedLayer(layer, t_local) if (exchange != "nccl" and ov is None) else None
+    depth = 3 if ov is not None else 2
+    pipe = HostPipeline(layer, depth=depth, graphed=graphed, overlapped=ov)
+    outs = [out_host] + [torch.empty_like(out_host).pin_memory() for _ in range(depth - 1)]
+    for i in range(max(depth, min(3, args.warmup))):
+        pipe.submit(x_host, lg_host, outs[i % depth])
     pipe.drain()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
-        pipe.submit(x_host, lg_host, outs[i % 2])
+        pipe.submit(x_host, lg_host, outs[i % depth])
     pipe.drain()
     e1.record()
     barrier()
@@ -642,8 +664,11 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16 x int8 -> fp32 accumulate", "data": "synthetic",
         "config": workload_config(world), "exchange": exchange, "exchange_status": exchange_status,
+        "exchange_overlapped": ({"reserved_sms": args.reserve_sms, "phases_from": "serial passes before the timed region"}
+                                if ov is not None else False),
         "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms, "steps_in_flight": 2, "cuda_graph": graphed is not None,
+                "ms_per_step": e2e_ms, "steps_in_flight": depth, "cuda_graph": graphed is not None,
+                "exchange_overlapped": ov is not None,
                 "single_step_latency_ms": latency_ms},
         "gpu_launches": launches * args.steps, "gpu_launches_per_step": launches,
         "roofline": roofline, "clocks": clk.result, "phases_ms_rank0": {k: round(v, 4) for k, v in phases.items()},
@@ -697,6 +722,10 @@ def main():
                     help="moe: the benchmark line; others: one kernel alone (for profiling)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="token exchange between ranks (N > 1): this package's peer-memory kernels or NCCL all-to-all")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="several ranks, p2p: run a step's token exchange serially before its GEMMs")
+    ap.add_argument("--reserve-sms", type=int, default=8,
+                    help="SMs the grouped GEMMs leave to the next step's exchange kernels when steps overlap")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel lines (N=1)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--quick", action="store_true", help="small shapes for the per-kernel lines (profiling)")

@@ -143,6 +143,14 @@ int b200moe_grouped_gemm_int8_packed_scatter(const void* x, const void* packed, 
                                              int64_t n_base, int64_t dst_rows, int64_t M, int64_t K, int64_t N, int64_t G,
                                              int group_list_type, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Number of multiprocessors the persistent packed-weight GEMM kernels leave free (default 0: one CTA on
+ * every SM).  For callers that run other kernels BESIDE a grouped GEMM -- the expert-parallel layer stores
+ * the next step's tokens into their owners' memory on a second stream while the current step's GEMMs run;
+ * a persistent CTA fills an SM's register file, so those kernels need SMs of their own.  Process-wide,
+ * takes effect for launches made after the call; values outside [0, SM count - 1] are clamped.  Returns
+ * the previous value.  (No reference counterpart.) */
+int b200moe_set_gemm_reserved_sms(int n);
+
 /* Allocation-free int8 grouped GEMM.  (No counterpart in the reference: its host binding always
  * obtains a workspace with aclrtMalloc.)  For callers that must not allocate device memory -- a
  * plug-in running inside another framework's step whose allocator owns all device memory, or a
@@ -257,7 +265,9 @@ int b200moe_moe_regroup_index(const int64_t* recv_counts, int64_t world, int64_t
 #define B200MOE_EP_MAX_WORLD 8
 #define B200MOE_IPC_HANDLE_BYTES 64
 typedef struct b200moe_ep_comm {
-    int32_t world, rank, n_experts, reserved;
+    int32_t world, rank, n_experts;
+    int32_t dispatch_ctas;  /* 0 = as many CTAs as the rows call for (up to 4 per SM); > 0 = at most this many, for
+                             * a dispatch that runs beside a grouped GEMM on the SMs that kernel leaves free */
     int64_t cap_rows, hidden;
     void* peer_recv_x[B200MOE_EP_MAX_WORLD];
     void* peer_y[B200MOE_EP_MAX_WORLD];

@@ -124,10 +124,27 @@ def _rank_main(rank, world, port, q, cuda=False, case_kw=None, exchange="nccl", 
         el, tl = c["E"] // world, c["x"].shape[0] // world
         sl = slice(rank * el, (rank + 1) * el)
         w = [c[k][sl].contiguous().to(dev) for k in ("w13", "s13", "o13", "w2", "s2", "o2")]
+        overlap = exchange == "p2p+overlap"
+        if overlap:
+            exchange = "p2p"
         layer = MoELayer(*w, c["E"], c["top_k"], dist.group.WORLD, CudaRowOps if cuda else TorchRowOps,
-                         exchange=exchange, max_tokens=tl)
+                         exchange=exchange, max_tokens=tl, exchange_buffers=2 if overlap else 1)
         outs = []
-        for step in range(steps):
+        if overlap:
+            # every step enqueued before the host looks at anything: the exchange of a step runs beside the
+            # GEMMs of the one before
+            from ascend_kernel_b200.moe_layer import OverlappedSteps
+
+            ins = [tuple(t[rank * tl:(rank + 1) * tl].to(dev) for t in _step_inputs(c, step)) for step in range(steps)]
+            torch.cuda.synchronize()
+            ov = OverlappedSteps(layer, tl, reserve_sms=8)
+            res = [ov.submit(x, lg) for x, lg in ins]
+            ov.drain()
+            outs = [r.cpu().view(torch.int16).numpy() for r in res]
+            # and the serial pass still works on the same layer afterwards
+            x, lg = ins[0]
+            assert torch.equal(layer.forward(x, lg).cpu().view(torch.int16), res[0].cpu().view(torch.int16))
+        for step in range(0 if overlap else steps):
             x, lg = _step_inputs(c, step)
             out = layer.forward(x[rank * tl:(rank + 1) * tl].to(dev), lg[rank * tl:(rank + 1) * tl].to(dev))
             outs.append(out.cpu().view(torch.int16).numpy())
@@ -137,7 +154,7 @@ def _rank_main(rank, world, port, q, cuda=False, case_kw=None, exchange="nccl", 
         dist.barrier()  # peers may still be reading this rank's result buffer until they are done too
         if layer.px is not None:
             layer.px.close()
-        q.put((rank, (outs if steps > 1 else outs[0], status) if exchange == "p2p" else outs[0]))
+        q.put((rank, (outs if steps > 1 else outs[0], status) if exchange == "p2p" else outs[0]))  # ("p2p+overlap" -> "p2p" above)
     finally:
         dist.destroy_process_group()
 
@@ -493,6 +510,78 @@ def test_two_gpu_ranks_peer_memory_exchange_matches_oracle():
     for r in range(2):
         assert got[r][1][0] == 0, got[r][1]
     for step in range(3):
+        x, lg = _step_inputs(c, step)
+        gold = O.moe_layer(x, lg, c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], c["top_k"])
+        out = torch.cat([torch.from_numpy(got[r][0][step]).view(torch.bfloat16) for r in range(2)])
+        close(out, gold)
+
+
+@pytest.mark.gpu
+def test_overlapped_steps_single_rank_match_direct_path():
+    """Steps whose exchange runs on a second stream beside the GEMMs of the step before (one rank, which is
+    its own peer): seven steps enqueued without a host synchronisation give the bits of the direct path,
+    with the GEMMs leaving SMs free and with none reserved; the layer's serial pass and a recorded pass
+    still work afterwards."""
+    from ascend_kernel_b200 import ops
+    from ascend_kernel_b200.moe_layer import GraphedLayer, MoELayer, OverlappedSteps
+
+    c = small_case(T=200, H=256, E=8, I=256, k=2)
+    d = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
+    w = [d[k] for k in ("w13", "s13", "o13", "w2", "s2", "o2")]
+    direct = MoELayer(*w, c["E"], c["top_k"])
+    p2p = MoELayer(*w, c["E"], c["top_k"], exchange="p2p", max_tokens=200, exchange_buffers=2)
+    ins = []
+    for step in range(7):
+        x, lg = _step_inputs(c, step)
+        ins.append((torch.roll(x, step, 0).cuda(), torch.roll(lg, 3 * step, 0).cuda()))
+    want = [direct.forward(x, lg) for x, lg in ins]
+    torch.cuda.synchronize()
+    for reserve in (8, 0):
+        ov = OverlappedSteps(p2p, 200, reserve_sms=reserve)
+        got = [ov.submit(x, lg) for x, lg in ins]
+        ov.drain()
+        assert ops.set_gemm_reserved_sms(0) == 0          # restored after every step
+        for step, (a, b) in enumerate(zip(want, got)):
+            assert torch.equal(a.view(torch.int16), b.view(torch.int16)), (reserve, step)
+    assert p2p.px.read_status()[0] == 0
+    b = p2p.forward(*ins[1])
+    assert torch.equal(want[1].view(torch.int16), b.view(torch.int16))
+    g = GraphedLayer(p2p, 200)
+    out = g(*ins[2]).clone()
+    torch.cuda.synchronize()
+    assert torch.equal(want[2].view(torch.int16), out.view(torch.int16))
+    with pytest.raises(RuntimeError):                     # recorded passes keep the step number on the device
+        p2p.px.post(2, step=5)
+    ov = OverlappedSteps(p2p, 200)                        # ... and overlapped steps take it back
+    got = ov.submit(*ins[3])
+    ov.drain()
+    assert torch.equal(want[3].view(torch.int16), got.view(torch.int16))
+    assert p2p.px.read_status()[0] == 0
+    p2p.px.close()
+
+
+@pytest.mark.gpu
+def test_two_gpu_ranks_overlapped_steps_match_oracle():
+    """Overlapped steps on two GPUs: six steps with changing inputs, all enqueued up front."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    kw = dict(T=200, H=256, E=8, I=256, k=2)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q, True, kw, "p2p+overlap", 6)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    c = small_case(**kw)
+    for r in range(2):
+        assert got[r][1][0] == 0, got[r][1]
+    for step in range(6):
         x, lg = _step_inputs(c, step)
         gold = O.moe_layer(x, lg, c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], c["top_k"])
         out = torch.cat([torch.from_numpy(got[r][0][step]).view(torch.bfloat16) for r in range(2)])
