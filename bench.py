@@ -561,9 +561,9 @@ def run_ours(args):
     if overlap:
         # the phases of a step, from serial passes outside the timed region (overlapped steps have no
         # phase boundaries on one stream)
-        for i in range(4):
-            layer.forward(x, lg, record=i > 0)
-            if i > 0 and layer.phases is not None:
+        for i in range(6):
+            layer.forward(x, lg, record=i > 1)
+            if i > 1 and layer.phases is not None:
                 phase_events.append(layer.phases)
         barrier()
         ov = OverlappedSteps(layer, t_local, reserve_sms=args.reserve_sms)
@@ -583,6 +583,7 @@ def run_ours(args):
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` list only the timed steps
         ev0.record()
+        t_host = time.perf_counter()
         for _ in range(args.steps):
             one_step(record=True)
             if layer.timing is not None:
@@ -590,6 +591,7 @@ def run_ours(args):
             if ov is None and layer.phases is not None:
                 phase_events.append(layer.phases)
         ev1.record()
+        host_ms_per_step = (time.perf_counter() - t_host) * 1e3 / args.steps  # the host's launch work per step
         barrier()
         torch.cuda.profiler.stop()
     launches = ops.LAUNCHES / max(1, args.steps)
@@ -628,8 +630,10 @@ def run_ours(args):
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    t_host = time.perf_counter()
     for i in range(args.steps):
         pipe.submit(x_host, lg_host, outs[i % depth])
+    host_ms_per_submit = (time.perf_counter() - t_host) * 1e3 / args.steps  # the host's own work per step
     pipe.drain()
     e1.record()
     barrier()
@@ -668,8 +672,9 @@ def run_ours(args):
                                 if ov is not None else False),
         "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps_in_flight": depth, "cuda_graph": graphed is not None,
-                "exchange_overlapped": ov is not None,
+                "exchange_overlapped": ov is not None, "host_ms_per_submit_rank0": host_ms_per_submit,
                 "single_step_latency_ms": latency_ms},
+        "host_launch_ms_per_step_rank0": host_ms_per_step,
         "gpu_launches": launches * args.steps, "gpu_launches_per_step": launches,
         "roofline": roofline, "clocks": clk.result, "phases_ms_rank0": {k: round(v, 4) for k, v in phases.items()},
         "parity_check": parity,
