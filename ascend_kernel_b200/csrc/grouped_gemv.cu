@@ -9,7 +9,12 @@
 // partial sums per column are combined with one shuffle and one pass through shared memory;
 // scale and offset are applied in the fp32 epilogue and the result is rounded to bf16 once.
 // Experts with more than 4 rows are processed 4 rows at a time (the weight slab is then re-read
-// from L2).  int8 items with 2..4 rows use the tensor core for the multiply-adds (gv_compute_mma).
+// from L2).  int8 items with 2..4 rows, fp8 items and fp4 items use the tensor core for the multiply-adds
+// (gv_compute_mma, gv_compute_fp4_mma); fp4 falls back to fp32 FMAs for x rows that are not exact in f16.
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -34,6 +39,8 @@ struct GemvArgs {
     int M, K, N, G, gl_type;
     int* status;
     int fp4_stored;  // fp4 weights in the reference's pre-shuffled order, read in place
+    const __half* x16;  // fp4: x as scaled f16 and the rows' exponents (gv_fp4_prepare_x_kernel), or null: fp32 path only
+    const int* xexp;
 };
 
 typedef unsigned long long f32x2;  // two packed fp32 (sm_100 two-wide FP32 instructions)
@@ -539,7 +546,254 @@ __device__ __forceinline__ void gv_compute_fp4_stored(const GemvArgs& a, const _
     __syncthreads();
 }
 
-template <int MODE>
+
+// ---- fp4, 1..4 rows per expert: decode by the e2m1 -> f16 conversion instruction, multiply-adds on the tensor core --
+// The scalar fp4 paths spend their issue slots on the decode and the FMAs (about 6 instructions per weight with
+// four rows; the HBM rate leaves room for fewer than 3).  Here the x rows are held in shared memory as f16 --
+// each row scaled by a power of two so that its largest element lies in [2^14, 2^15); the staging code only
+// takes this path when every element is then exactly representable, so x' * e2m1 products stay exact -- and a
+// warp multiplies a 16 (k) x 128 (columns) block of weights with the x rows using eight mma.sync m16n8k16
+// (f16 operands, fp32 accumulation), the weights as the 16 x 16 operand.  The 16 rows of a step are one scale
+// group: the instruction starts from zero and its fp32 sums are multiplied by the group's bf16 scale per column
+// into the running totals (the scale never touches a weight; gemv_impl.h:147-199 keeps the weights in fp32
+// the same way).  The row's power of two is undone in the epilogue.
+//   lane (g, t) = (lane / 4, lane % 4) owns k rows {2t, 2t+1, 2t+8, 2t+9} of the step -- the instruction's own k
+//   indices -- and 16 columns: rows (2t, 2t+1) of eight columns are two 32-bit words; one shift and two logic
+//   operations put the two rows' codes of a column into one byte, which the conversion instruction turns into
+//   the f16 pair (row 2t, row 2t+1) the operand register wants.
+//   canonical layout: columns 16g .. 16g+15 of the warp's 128 (four 8-byte loads cover four rows x 64 bytes);
+//   stored order: the 8-column groups (p, q) = (4 hc + g / 4 + 2 i, g % 4), i = 0, 1, whose rows (2t, 2t+1) of
+//   an 8-row block are 8 consecutive bytes (each load instruction covers two full 128-byte lines).
+__device__ __forceinline__ void cvt_e2m1x8_f16(uint32_t w, uint32_t (&o)[4]) {
+    // byte i of w = two codes -> f16x2 (low nibble in the low half)
+    asm("{ .reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %4; cvt.rn.f16x2.e2m1x2 %0, b0; "
+        "cvt.rn.f16x2.e2m1x2 %1, b1; cvt.rn.f16x2.e2m1x2 %2, b2; cvt.rn.f16x2.e2m1x2 %3, b3; }"
+        : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3])
+        : "r"(w));
+}
+
+__device__ __forceinline__ void mma_16816_f16_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                   uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+constexpr int kGvFp4Ahead = 4;  // steps whose loads are in flight per warp (6: slower, measured)
+
+constexpr int kGvFp4L2Ahead = 3;  // batches of kGvFp4Ahead steps requested into L2 before their loads are issued
+
+template <bool kStored>
+__device__ __forceinline__ void gv_compute_fp4_mma(const GemvArgs& a, const __half* xs, const int* xexp, float* red,
+                                                   int g_expert, int r0, int rows_valid, int n0) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int hc = warp & 1, kg = warp >> 1;  // column half of the slab, k group
+    const size_t row_bytes = (size_t)a.N >> 1;
+    const uint8_t* wexp = a.weight + (size_t)g_expert * a.K * row_bytes;
+    // first of the lane's 16 columns inside the slab (stored order: of its first group; the second is 64 further)
+    const int c_first = kStored ? 128 * hc + 32 * (g >> 2) + 8 * (g & 3) : 128 * hc + 16 * g;
+    const uint8_t* wbase;
+    size_t p_stride = 0;
+    if constexpr (kStored) {
+        const int J = a.N >> 8, j = n0 >> 8;
+        p_stride = (size_t)J * 128;
+        wbase = wexp + (size_t)j * 128 + (g & 3) * 32 + 8 * t;
+    } else {
+        wbase = wexp + (size_t)(n0 >> 1) + 64 * hc + 8 * g + (size_t)(2 * t) * row_bytes;
+    }
+    const __half* xrow = xs + (size_t)(g < rows_valid ? g : 0) * (a.K + kGvXPad) + 2 * t;
+    const bool x_on = g < rows_valid;
+    const __nv_bfloat16* sbase = static_cast<const __nv_bfloat16*>(a.scale) + (size_t)g_expert * (a.K >> 4) * a.N + n0 + c_first;
+
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+    constexpr int kStepRows = 16 * kGvMmaParts;  // k rows the CTA consumes per step
+    // q[0], q[1]: rows (2t, 2t+1) and (2t+8, 2t+9) of the lane's columns 0..7; q[2], q[3]: of its columns 8..15
+    auto load = [&](int k, uint2 (&q)[4]) {
+        if constexpr (kStored) {
+            const int R = k >> 6, aa = (k >> 4) & 3;
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+                    q[2 * i + b] = ldg_stream8(wbase + ((size_t)((2 * R + b) * 4 + aa) * 8 + 4 * hc + (g >> 2) + 2 * i) * p_stride);
+        } else {
+            const uint8_t* p = wbase + (size_t)k * row_bytes;
+            // rows 2t, 2t+1, 2t+8, 2t+9: 16 columns = 8 bytes each
+            const uint2 r0w = ldg_stream8(p), r1w = ldg_stream8(p + row_bytes);
+            const uint2 r8w = ldg_stream8(p + 8 * row_bytes), r9w = ldg_stream8(p + 9 * row_bytes);
+            q[0] = make_uint2(r0w.x, r1w.x);
+            q[1] = make_uint2(r8w.x, r9w.x);
+            q[2] = make_uint2(r0w.y, r1w.y);
+            q[3] = make_uint2(r8w.y, r9w.y);
+        }
+    };
+    // Four steps of the warp's weights and scales into L2, one line per lane: the weights of a step are 8 lines
+    // (stored order: 2 row blocks x 4 line rows; canonical: 16 rows x 64 bytes, half a line each), its scales 2
+    // lines.  The register loads, issued up to kGvFp4L2Ahead batches later, then wait for L2, not for DRAM.
+    auto prefetch_group = [&](int k0) {
+        const int h = lane >> 3, k = k0 + h * kStepRows;
+        if (k >= a.K) return;
+        const uint8_t* w;
+        if constexpr (kStored) {
+            const int R = k >> 6, aa = (k >> 4) & 3, i = (lane >> 2) & 1, b = (lane >> 1) & 1, gq = lane & 1;
+            w = wexp + (size_t)(n0 >> 8) * 128 + ((size_t)((2 * R + b) * 4 + aa) * 8 + 4 * hc + gq + 2 * i) * p_stride;
+        } else {
+            w = wexp + (size_t)(n0 >> 1) + 64 * hc + (size_t)(k + 2 * (lane & 7)) * row_bytes;  // rows 2l and (same line pair) 2l+1
+        }
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(w));
+        if constexpr (!kStored) asm volatile("prefetch.global.L2 [%0];" ::"l"(w + row_bytes));
+        if ((lane & 7) < 2) {
+            const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(a.scale) + ((size_t)g_expert * (a.K >> 4) + (k >> 4)) * a.N +
+                                      n0 + 128 * hc + 64 * (lane & 7);
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(sp));
+        }
+    };
+    auto compute = [&](int k, const uint2 (&q)[4]) {
+        uint32_t b0 = 0u, b1 = 0u;
+        if (x_on) {
+            b0 = *reinterpret_cast<const uint32_t*>(xrow + k);
+            b1 = *reinterpret_cast<const uint32_t*>(xrow + k + 8);
+        }
+        // the group's scales of the lane's 16 columns
+        const __nv_bfloat16* sp = sbase + (size_t)(k >> 4) * a.N;
+        const uint4 s0 = __ldg(reinterpret_cast<const uint4*>(sp));
+        const uint4 s1 = __ldg(reinterpret_cast<const uint4*>(sp + (kStored ? 64 : 8)));
+        const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {  // columns 8i .. 8i+7 of the lane's 16
+            const uint2 lo = q[2 * i], hi = q[2 * i + 1];
+            // byte b: the codes of rows (r, r + 1) at column 2b (e_*) / 2b + 1 (o_*)
+            const uint32_t e_lo = (lo.x & 0x0F0F0F0Fu) | ((lo.y << 4) & 0xF0F0F0F0u);
+            const uint32_t o_lo = ((lo.x >> 4) & 0x0F0F0F0Fu) | (lo.y & 0xF0F0F0F0u);
+            const uint32_t e_hi = (hi.x & 0x0F0F0F0Fu) | ((hi.y << 4) & 0xF0F0F0F0u);
+            const uint32_t o_hi = ((hi.x >> 4) & 0x0F0F0F0Fu) | (hi.y & 0xF0F0F0F0u);
+            uint32_t a0[4], a1[4], a2[4], a3[4];
+            cvt_e2m1x8_f16(e_lo, a0);
+            cvt_e2m1x8_f16(o_lo, a1);
+            cvt_e2m1x8_f16(e_hi, a2);
+            cvt_e2m1x8_f16(o_hi, a3);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                float d[4];
+                mma_16816_f16_zero(d, a0[b], a1[b], a2[b], a3[b], b0, b1);
+                const float sc_e = __uint_as_float(sw[4 * i + b] << 16), sc_o = __uint_as_float(sw[4 * i + b] & 0xFFFF0000u);
+                float* c = acc[4 * i + b];
+                c[0] = fmaf(d[0], sc_e, c[0]);
+                c[1] = fmaf(d[1], sc_e, c[1]);
+                c[2] = fmaf(d[2], sc_o, c[2]);
+                c[3] = fmaf(d[3], sc_o, c[3]);
+            }
+        }
+    };
+    constexpr int kBatchRows = kGvFp4Ahead * kStepRows;
+    int k0 = kg * 16;
+    int k_pf = k0;  // first step not yet requested into L2 (requests go out four steps at a time)
+    for (; k0 + (kGvFp4Ahead - 1) * kStepRows < a.K; k0 += kBatchRows) {
+        uint2 q[kGvFp4Ahead][4];
+        for (; k_pf < k0 + kGvFp4L2Ahead * kBatchRows; k_pf += 4 * kStepRows) prefetch_group(k_pf);
+#pragma unroll
+        for (int h = 0; h < kGvFp4Ahead; ++h) load(k0 + h * kStepRows, q[h]);
+#pragma unroll
+        for (int h = 0; h < kGvFp4Ahead; ++h) compute(k0 + h * kStepRows, q[h]);
+    }
+    for (; k0 < a.K; k0 += kStepRows) {
+        uint2 q1[4];
+        load(k0, q1);
+        compute(k0, q1);
+    }
+
+    // ---- partial sums of the four k groups -> shared memory -> per-column epilogue ----------------
+    if (t < 2) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int col = c_first + (kStored ? 64 * (j >> 2) : 8 * (j >> 2)) + 2 * (j & 3);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {  // tokens 2t, 2t + 1
+                float* dst = red + (size_t)(kg * kGvRows + 2 * t + e) * kGvSlabN + col;
+                *reinterpret_cast<float2*>(dst) = make_float2(acc[j][e], acc[j][2 + e]);
+            }
+        }
+    }
+    __syncthreads();
+    {
+        const int tc = threadIdx.x;  // column inside the slab
+#pragma unroll
+        for (int m = 0; m < kGvRows; ++m) {
+            if (m < rows_valid) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < kGvMmaParts; ++w) v += red[(w * kGvRows + m) * kGvSlabN + tc];
+                a.y[(size_t)(r0 + m) * a.N + n0 + tc] = __float2bfloat16_rn(scalbnf(v, xexp[m]));
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// fp4 prepass, one CTA per x row: the row as f16, times 2^-e with e chosen so that its largest element lies in
+// [2^14, 2^15), into x16; e into xexp -- or kGvNotF16 when some element is not exactly representable then (more
+// than about 2^-32 below the row's largest, a bf16 subnormal, an infinity or a NaN): such rows take the fp32 path.
+constexpr int kGvNotF16 = -(1 << 30);
+
+__global__ void __launch_bounds__(256) gv_fp4_prepare_x_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ x16,
+                                                               int* __restrict__ xexp, int K) {
+    __shared__ int s_max, s_bad;
+    const size_t row = blockIdx.x;
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(x + row * K);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(x16 + row * K);
+    if (threadIdx.x == 0) { s_max = 0; s_bad = 0; }
+    __syncthreads();
+    uint32_t mx = 0u;
+    for (int i = threadIdx.x; i < K / 2; i += blockDim.x) {
+        const uint32_t w = __ldg(src + i);
+        mx = max(mx, max(w & 0x7FFFu, (w >> 16) & 0x7FFFu));  // bf16 magnitudes order like integers
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(&s_max, (int)mx);
+    __syncthreads();
+    const int e_max = s_max >> 7;                    // biased exponent of the largest magnitude
+    const int sh = e_max == 0 ? 0 : e_max - 127 - 14;
+    int bad = e_max == 255;
+    for (int i = threadIdx.x; i < K / 2; i += blockDim.x) {
+        const uint32_t w = __ldg(src + i);
+        uint32_t out = 0u;
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+            const uint32_t b = hlf ? (w >> 16) : (w & 0xFFFFu);
+            const uint32_t mag = b & 0x7FFFu, sign = b & 0x8000u;
+            uint32_t h = sign;
+            if (mag != 0u) {
+                const int e = (int)(mag >> 7);
+                const int E = e - sh - 112;                       // biased f16 exponent of the scaled value
+                const uint32_t sig = (0x80u | (mag & 0x7Fu)) << 3;  // 11-bit significand, leading one at bit 10
+                if (e == 0 || E > 30) bad = 1;
+                else if (E >= 1) h = sign | ((uint32_t)E << 10) | (sig & 0x3FFu);
+                else {
+                    const int s = 1 - E;                          // f16 subnormal: exact only if no set bit is shifted out
+                    if (s > 10 || (sig & ((1u << s) - 1u)) != 0u) bad = 1;
+                    else h = sign | (sig >> s);
+                }
+            }
+            out |= h << (16 * hlf);
+        }
+        dst[i] = out;
+    }
+    if (bad) atomicOr(&s_bad, 1);
+    __syncthreads();
+    if (threadIdx.x == 0) xexp[row] = s_bad ? kGvNotF16 : sh;
+}
+
+// fp4 is launched as two kernels over the same work items: PATH 1 takes the passes whose x rows are all exact as
+// scaled f16 (tensor-core path), PATH 2 the others (fp32 multiply-adds; normally none, and the kernel leaves after
+// walking the item list); PATH 0: every other mode, and fp4 without the prepass.  Separate kernels keep the
+// registers of one path from weighing on the other.
+template <int MODE, int PATH = 0>
 __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     int* row_start = reinterpret_cast<int*>(smem_raw);
@@ -568,8 +822,9 @@ __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvA
     const int n_act = *n_active_p;
     const int n_items = n_act * n_slabs;
     const int kvec = a.K / 8;  // 16-byte vectors per x row
-    int* ticket = a.status + 2;  // zeroed by the host before the launch
+    int* ticket = a.status + (PATH == 2 ? 3 : 2);  // zeroed by the host before the launch
     __shared__ int s_item;
+    __shared__ int xexp[kGvRows];
     for (;;) {
         __syncthreads();
         if (threadIdx.x == 0) s_item = atomicAdd(ticket, 1);
@@ -583,11 +838,20 @@ __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvA
         const int r0 = row_start[g], r1 = row_start[g + 1];
         for (int r = r0; r < r1; r += kGvRows) {
             const int rows = min(kGvRows, r1 - r);
+            // fp4: the tensor-core path when every row of the pass is exact as scaled f16 (prepared by the prepass)
+            bool fp4_mma = false;
+            if constexpr (PATH != 0) {
+                fp4_mma = true;
+                for (int m = 0; m < rows; ++m) fp4_mma = fp4_mma && a.xexp[r + m] != kGvNotF16;
+                if (fp4_mma != (PATH == 1)) continue;  // the other kernel's pass
+                if (fp4_mma && threadIdx.x < rows) xexp[threadIdx.x] = a.xexp[r + threadIdx.x];
+            }
             // ---- stage the x rows (and their sums, for the offset term) ----
             if (threadIdx.x < 4) xsum[threadIdx.x] = 0.f;
             __syncthreads();
             for (int m = 0; m < rows; ++m) {
-                const uint4* src = reinterpret_cast<const uint4*>(a.x + (size_t)(r + m) * a.K);
+                const uint4* src = fp4_mma ? reinterpret_cast<const uint4*>(a.x16 + (size_t)(r + m) * a.K)
+                                           : reinterpret_cast<const uint4*>(a.x + (size_t)(r + m) * a.K);
                 uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)m * (a.K + kGvXPad));
                 float s = 0.f;
                 for (int i = threadIdx.x; i < kvec; i += kGvThreads) {
@@ -607,8 +871,11 @@ __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvA
             }
             __syncthreads();
             // fp8: the tensor-core path also wins with one row (its decode is two-wide); int8 with one
-            // row is faster on the scalar path
-            if (MODE == B200MOE_CT_FP4 && a.fp4_stored) {
+            // row is faster on the scalar path; fp4 takes the tensor-core path whenever x is exact in f16
+            if constexpr (PATH == 1) {
+                if (a.fp4_stored) gv_compute_fp4_mma<true>(a, reinterpret_cast<const __half*>(xs), xexp, red, g, r, rows, n0);
+                else gv_compute_fp4_mma<false>(a, reinterpret_cast<const __half*>(xs), xexp, red, g, r, rows, n0);
+            } else if (MODE == B200MOE_CT_FP4 && a.fp4_stored) {
                 if (rows == 1) gv_compute_fp4_stored<1>(a, xs, red, g, r, rows, n0);
                 else if (rows == 2) gv_compute_fp4_stored<2>(a, xs, red, g, r, rows, n0);
                 else gv_compute_fp4_stored<4>(a, xs, red, g, r, rows, n0);
@@ -628,14 +895,14 @@ static size_t gv_smem_bytes(int G, int K) {
     return b;
 }
 
-template <int MODE>
+template <int MODE, int PATH = 0>
 static int gv_launch(const GemvArgs& a, cudaStream_t stream) {
     const size_t smem = gv_smem_bytes(a.G, a.K);
     if (smem > 227 * 1024) return B200MOE_ERR_SHAPE;
-    B200MOE_CUDA_TRY(cudaFuncSetAttribute(grouped_gemv_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200MOE_CUDA_TRY(cudaFuncSetAttribute(grouped_gemv_kernel<MODE, PATH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem));
     const int per_sm = smem <= 110 * 1024 ? 2 : 1;
-    grouped_gemv_kernel<MODE><<<per_sm * sm_count(), kGvThreads, smem, stream>>>(a);
+    grouped_gemv_kernel<MODE, PATH><<<per_sm * sm_count(), kGvThreads, smem, stream>>>(a);
     B200MOE_CUDA_TRY(cudaGetLastError());
     return B200MOE_OK;
 }
@@ -644,10 +911,15 @@ static int gv_launch(const GemvArgs& a, cudaStream_t stream) {
 
 using namespace b200moe;
 
-extern "C" size_t b200moe_grouped_gemv_workspace_bytes(int64_t, int64_t K, int64_t N, int64_t G, int compute_type,
+static size_t gv_fp4_exp_bytes(int64_t M) { return ((size_t)M * sizeof(int) + 255) / 256 * 256; }
+
+extern "C" size_t b200moe_grouped_gemv_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t G, int compute_type,
                                                        int weight_layout) {
-    (void)K; (void)N; (void)G; (void)compute_type; (void)weight_layout;
-    return B200MOE_STATUS_BYTES;  // status words and the work-item ticket; no mode needs more
+    (void)N; (void)G; (void)weight_layout;
+    // status words and the work-item ticket; fp4 adds the rows' exponents and x as scaled f16
+    size_t b = B200MOE_STATUS_BYTES;
+    if (compute_type == B200MOE_CT_FP4 && M > 0 && K > 0) b += gv_fp4_exp_bytes(M) + (size_t)M * (size_t)K * 2;
+    return b;
 }
 
 extern "C" int b200moe_grouped_gemv(const void* x, const void* weight, const void* scale, const void* offset,
@@ -690,10 +962,25 @@ extern "C" int b200moe_grouped_gemv(const void* x, const void* weight, const voi
 
     // fp4 in the stored (pre-shuffled) order is read in place
     a.fp4_stored = (compute_type == B200MOE_CT_FP4 && weight_layout == B200MOE_LAYOUT_ASCEND) ? 1 : 0;
+    a.x16 = nullptr;
+    a.xexp = nullptr;
+    // (B200MOE_GEMV_FP4_SCALAR=1 keeps fp4 on the fp32 multiply-adds: comparison runs)
+    static const bool fp4_scalar = [] { const char* e = getenv("B200MOE_GEMV_FP4_SCALAR"); return e && e[0] == '1'; }();
+    if (compute_type == B200MOE_CT_FP4 && !fp4_scalar) {
+        uint8_t* ws = static_cast<uint8_t*>(workspace) + B200MOE_STATUS_BYTES;
+        a.xexp = reinterpret_cast<const int*>(ws);
+        a.x16 = reinterpret_cast<const __half*>(ws + gv_fp4_exp_bytes(M));
+        gv_fp4_prepare_x_kernel<<<(unsigned)M, 256, 0, s>>>(a.x, const_cast<__half*>(a.x16), const_cast<int*>(a.xexp), a.K);
+        B200MOE_CUDA_TRY(cudaGetLastError());
+    }
     switch (compute_type) {
         case B200MOE_CT_INT8: return gv_launch<B200MOE_CT_INT8>(a, s);
         case B200MOE_CT_FP8: return gv_launch<B200MOE_CT_FP8>(a, s);
         case B200MOE_CT_INT4: return gv_launch<B200MOE_CT_INT4>(a, s);
-        default: return gv_launch<B200MOE_CT_FP4>(a, s);
+        default: {
+            if (a.x16 == nullptr) return gv_launch<B200MOE_CT_FP4>(a, s);
+            const int rc = gv_launch<B200MOE_CT_FP4, 1>(a, s);
+            return rc != B200MOE_OK ? rc : gv_launch<B200MOE_CT_FP4, 2>(a, s);
+        }
     }
 }

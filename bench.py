@@ -335,6 +335,8 @@ def kernel_lines(peaks, quick=False, which=("gemm", "gemv", "dequant")):
                                                  "shape": {"M": Mv, "K": K2, "N": N2, "G": G, "active_experts": n_act}}
         del w2, s2, x2, y2
         torch.cuda.empty_cache()
+    if "gemv" in which:
+        gen = torch.Generator(device=dev).manual_seed(12)
         # the reference's own weight formats at the pass-1 shape (same routing): fp8 with fp32 block
         # scales, fp4 (canonical layout) with bf16 scales per 16 k rows
         K1, N1 = 7168, 4096

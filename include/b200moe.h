@@ -179,7 +179,11 @@ int b200moe_noalloc_read_status(int32_t out[2], void* stream);
 
 /* Grouped GEMV for decode-sized expert batches (any number of rows per expert is accepted;
  * it is bandwidth-optimal up to 4 rows per expert).  Dequantised weights stay fp32, x is
- * widened to fp32, one final round to bf16.  `offset` only for int8/int4 (may be NULL). */
+ * widened to fp32, one final round to bf16.  `offset` only for int8/int4 (may be NULL).
+ * fp4: a short first kernel writes x as f16 into the workspace, each row scaled by a power of two, and the
+ * multiply-adds then run on the tensor core -- for the rows where that copy is exact (every element within about
+ * 2^-32 of the row's largest; x' * e2m1 products are then exact, as in fp32); other rows, and rows with an infinity
+ * or a NaN, go through fp32 multiply-adds in a second kernel.  Same results either way up to summation order. */
 int b200moe_grouped_gemv(const void* x, const void* weight, const void* scale, const void* offset,
                          const int64_t* group_list, void* y, int64_t M, int64_t K, int64_t N, int64_t G,
                          int compute_type, int group_list_type, int weight_layout, void* workspace,

@@ -102,7 +102,8 @@ def test_workspace_sizes():
     # pre-shuffled fp4 weights are read in place: no canonical copy in the workspace
     assert abi.lib.b200moe_grouped_gemm_workspace_bytes(8, 256, 512, 4, 1, 1) == 256
     assert abi.lib.b200moe_grouped_gemv_workspace_bytes(8, 256, 512, 4, 2, 0) == 256
-    assert abi.lib.b200moe_grouped_gemv_workspace_bytes(8, 256, 512, 4, 1, 1) == 256
+    # fp4 GEMV: the rows' f16 exponents (padded to 256 bytes) and x as scaled f16
+    assert abi.lib.b200moe_grouped_gemv_workspace_bytes(8, 256, 512, 4, 1, 1) == 256 + 256 + 8 * 256 * 2
 
 
 def test_install_check_lists_the_reference_operators():

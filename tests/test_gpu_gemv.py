@@ -101,6 +101,68 @@ def test_fp4_reference_fixture(prefix, layout):
     assert_close_to_golden(out, gold, ulps=2.0)
 
 
+def _fp4_case(counts, K, N, seed):
+    gen = torch.Generator().manual_seed(seed)
+    G = len(counts)
+    cnt = torch.tensor(counts, dtype=torch.int64)
+    x = torch.randn(int(cnt.sum()), K, generator=gen).to(torch.bfloat16)
+    w = torch.randint(0, 256, (G, K, N // 2), generator=gen, dtype=torch.uint8)      # every code, both signs of zero
+    scale = (torch.rand(G, K // 16, N, generator=gen) * 0.09 + 0.01).to(torch.bfloat16)
+    return x, w, scale, cnt
+
+
+@pytest.mark.parametrize("layout", ["canonical", "ascend"])
+@pytest.mark.parametrize("counts,K,N", [
+    ([1, 1, 1, 1], 64, 256),                 # one step of one k group
+    ([1, 0, 2, 4, 0, 3], 192, 512),          # three steps: the look-ahead of four runs out inside the loop
+    ([0, 5, 9, 1, 3], 448, 768),             # more than four rows per expert
+    ([2, 3, 4, 1], 7168, 512),               # benchmark K
+])
+def test_fp4_tensor_core_path_matches_oracle(counts, K, N, layout):
+    """fp4 on random codes: x rows are held as f16 (each scaled by a power of two) and the products run on the
+    tensor core; rows of very different magnitude, including ones far outside the f16 range, stay exact."""
+    import ascend_kernel_b200 as ak
+
+    x, w, scale, cnt = _fp4_case(counts, K, N, 41)
+    row_mag = torch.tensor([2.0 ** e for e in (0, 60, -70, 17, -3, 100, -110, 5, 30, -45)])[torch.arange(x.shape[0]) % 10]
+    x = (x.float() * row_mag[:, None]).to(torch.bfloat16)
+    gold = O.golden_f32(x, w, scale, None, cnt, "fp4", O.GROUP_LIST_COUNTS, weight_layout="canonical", gemv=True)
+    wd = ak.fp4_layout(w.cuda(), to_ascend=True).cpu() if layout == "ascend" else w
+    out, st = run_gemv(x, wd, scale, cnt, "fp4", gl_type=1, layout=layout)
+    assert st == (0, 0)
+    # row by row, each brought back to unit magnitude (a power of two: exact), so that every row is held to the bar
+    inv = (1.0 / row_mag)[:, None]
+    assert_close_to_golden((out.cpu().float() * inv).to(torch.bfloat16), gold * inv, ulps=2.0)
+
+
+@pytest.mark.parametrize("layout", ["canonical", "ascend"])
+def test_fp4_rows_that_are_not_exact_in_f16_take_the_fp32_path(layout):
+    """A row whose elements span more than the f16 format holds (here 2^-100 beside 1), an infinity and a NaN:
+    those items fall back to the fp32 multiply-adds; the small elements still count where the weights of the
+    large ones are zero."""
+    import ascend_kernel_b200 as ak
+
+    x, w, scale, cnt = _fp4_case([2, 4, 1], 256, 256, 43)
+    x = x.clone()
+    x[0, 5] = 2.0 ** -100                    # expert 0: not representable beside its neighbours
+    x[1] = 0
+    x[1, 7], x[1, 9] = 2.0 ** -60, 3.0       # row 1: the weight under the large element is zero below
+    w[0, 9] = 0                              # (both nibbles of every column: code 0)
+    x[2, 3] = float("inf")                   # expert 1: non-finite values are propagated, not scaled
+    x[6, 1] = float("nan")
+    gold = O.golden_f32(x, w, scale, None, cnt, "fp4", O.GROUP_LIST_COUNTS, weight_layout="canonical", gemv=True)
+    wd = ak.fp4_layout(w.cuda(), to_ascend=True).cpu() if layout == "ascend" else w
+    out, st = run_gemv(x, wd, scale, cnt, "fp4", gl_type=1, layout=layout)
+    assert st == (0, 0)
+    o = out.cpu().float()
+    finite = torch.isfinite(gold)
+    assert torch.equal(torch.isnan(o), torch.isnan(gold)) and torch.equal(torch.isinf(o), torch.isinf(gold))
+    assert_close_to_golden(torch.where(finite, o, torch.zeros_like(o)).to(torch.bfloat16),
+                           torch.where(finite, gold, torch.zeros_like(gold)), ulps=2.0)
+    assert float(o[1].abs().max()) > 0 and float(o[1].abs().max()) < 1e-15   # row 1 is made of its small element only
+    assert_close_to_golden((o[1:2] * 2.0 ** 60).to(torch.bfloat16), gold[1:2] * 2.0 ** 60, ulps=2.0)
+
+
 def test_bad_group_list_is_clamped_and_reported():
     x, w, scale, offset, cnt = _int8_case([1, 2, 1], 128, 256, 9, False)
     bad = torch.tensor([1, 0, 99], dtype=torch.int64)  # not monotone, then beyond M
