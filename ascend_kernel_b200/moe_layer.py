@@ -326,10 +326,17 @@ class OverlappedSteps:
     All ranks must submit the same number of steps.  The layer must have been built with
     ``exchange="p2p", exchange_buffers=2`` and the packed GEMMs."""
 
-    def __init__(self, layer: "MoELayer", n_tokens: int, reserve_sms: int = 8):
+    def __init__(self, layer: "MoELayer", n_tokens: int, reserve_sms: int = 8, late_sum: bool = False):
+        """``late_sum``: the end of a step -- the wait for the other ranks' pushes and the weighted sum -- also
+        runs on the exchange stream, beside the NEXT step's gate/up GEMM, so the caller's stream goes from one
+        step's down projection straight to the next step's gate/up GEMM and a slow peer's pushes are waited for
+        off the critical path; both GEMMs then leave ``reserve_sms`` SMs free.  A step's result is then
+        complete by the event of the handle ``submit`` returns (set by the next ``submit`` or by ``flush``),
+        not in the order of the caller's stream.  Off by default: measured 2-4 % slower on 2 and 4 GPUs (the
+        down projection gives up SMs as well and the sum runs on the few that are free)."""
         if layer.px is None or layer.px.n_buffers != 2 or layer.gemm != "packed":
             raise RuntimeError('OverlappedSteps needs exchange="p2p", exchange_buffers=2 and the packed GEMMs')
-        self.layer, self.n_tokens, self.reserve_sms = layer, n_tokens, reserve_sms
+        self.layer, self.n_tokens, self.reserve_sms, self.late_sum = layer, n_tokens, reserve_sms, late_sum
         dev, px = layer.device, layer.px
         px.use_host_steps()
         self.s_x = torch.cuda.Stream(dev, priority=-1)
@@ -345,10 +352,34 @@ class OverlappedSteps:
                 done=None))
         self.n = 0
         self.rows_sent = None  # event: the rows of the step submitted last have left (its inputs are free)
+        self.tail = None       # late_sum: what is left to enqueue of the step submitted last
 
-    def submit(self, x, logits, ready=None, out=None, record: bool = False):
-        """One step; returns its bf16 [T, H] result, complete in the order of the caller's stream.
-        ``record=True`` leaves CUDA events around the two GEMMs in ``layer.timing``."""
+    def _finish(self, tail):
+        """Exchange stream: waits for every owner's pushes of the step, then sums each token's rows."""
+        layer, px = self.layer, self.layer.px
+        with torch.cuda.stream(self.s_x):
+            self.s_x.wait_event(tail["posted"])
+            px.wait(2, step=tail["step"])
+            handle = tail["handle"]
+            if tail["out_free"] is not None:     # whoever last read the caller's output buffer
+                self.s_x.wait_event(tail["out_free"])
+            if handle.out is None:               # (allocated on the exchange stream: wait for the event before use)
+                handle.out = torch.empty(self.n_tokens, layer.hidden, dtype=torch.bfloat16, device=layer.device)
+            layer.ops.combine(px.ret_sets[tail["parity"]], tail["slot"], tail["wts"], handle.out)
+            handle.event = torch.cuda.Event()
+            handle.event.record(self.s_x)
+
+    def flush(self):
+        """late_sum: enqueues the end of the step submitted last without waiting for a next step."""
+        if self.tail is not None:
+            tail, self.tail = self.tail, None
+            self._finish(tail)
+
+    def submit(self, x, logits, ready=None, out=None, out_free=None, record: bool = False):
+        """One step.  Returns a handle: ``handle.out`` is the bf16 [T, H] result (``out`` if given; it is written
+        once the event ``out_free`` has completed), complete once ``handle.event`` has -- which, without
+        ``late_sum``, is in the order of the caller's stream.  ``record=True`` leaves CUDA events around the
+        two GEMMs in ``layer.timing``."""
         layer, px = self.layer, self.layer.px
         if x.shape[0] != self.n_tokens:
             raise RuntimeError("OverlappedSteps was built for another token count")
@@ -370,11 +401,14 @@ class OverlappedSteps:
             sent = torch.cuda.Event()
             sent.record(self.s_x)
         self.rows_sent = sent
+        # late_sum: the previous step's end follows this step's exchange on the exchange stream (its own set of
+        # buffers is the other one; the step before that, which used this set, ended before this exchange began)
+        self.flush()
         main.wait_event(sent)
         px.wait(1, step=step)                # rows of every source rank have landed
-        # Only the gate/up GEMM makes room: the next step's exchange is released when the previous step's
-        # weighted sum ends, so it runs beside this kernel; by the down projection it has long started (a
-        # kernel that had not would wait for that GEMM's first CTA to leave, which costs time, not correctness).
+        # The gate/up GEMM makes room: the next step's exchange is released when the previous step's weighted
+        # sum ends, so it runs beside this kernel.  Without late_sum the down projection takes every SM (a
+        # late exchange kernel would wait for that GEMM's first CTA to leave: time, not correctness).
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if record else None
         if ev:
             ev[0].record()
@@ -382,27 +416,47 @@ class OverlappedSteps:
         try:
             ops.grouped_gemm_packed(px.recv_x_sets[p], layer.w13, layer.s13, layer.o13, local_counts, st["act"],
                                     group_list_type=1, gate_up_silu=True)
+            if ev:
+                ev[1].record()
+                ev[2].record()
+            if not self.late_sum:
+                ops.set_gemm_reserved_sms(prev)
+            ops.grouped_gemm_packed_scatter(st["act"], layer.w2, layer.s2, layer.o2, local_counts,
+                                            px.ret_code_sets[p], px.ret_ptrs_sets[p], px.cap_send, group_list_type=1)
         finally:
             ops.set_gemm_reserved_sms(prev)
-        if ev:
-            ev[1].record()
-            ev[2].record()
-        ops.grouped_gemm_packed_scatter(st["act"], layer.w2, layer.s2, layer.o2, local_counts, px.ret_code_sets[p],
-                                        px.ret_ptrs_sets[p], px.cap_send, group_list_type=1)
         if ev:
             ev[3].record()
         layer.timing = ev
         px.post(2, step=step)                # this rank's pushes are complete and visible
+        handle = StepResult(out)
+        if self.late_sum:
+            posted = torch.cuda.Event()
+            posted.record(main)
+            self.tail = dict(step=step, parity=p, slot=slot, wts=wts, posted=posted, handle=handle, out_free=out_free)
+            st["done"] = None                # the exchange stream itself orders the sets' reuse
+            return handle
         px.wait(2, step=step)                # every owner has pushed this rank's rows
-        res = layer.ops.combine(px.ret_sets[p], slot, wts) if out is None else layer.ops.combine(px.ret_sets[p], slot, wts, out)
+        if out_free is not None:
+            main.wait_event(out_free)
+        handle.out = layer.ops.combine(px.ret_sets[p], slot, wts) if out is None else layer.ops.combine(px.ret_sets[p], slot, wts, out)
         st["done"] = torch.cuda.Event()
         st["done"].record(main)
-        return res
+        handle.event = st["done"]
+        return handle
 
     def drain(self):
         """Waits (on the host) for everything submitted."""
+        self.flush()
         self.s_x.synchronize()
         torch.cuda.current_stream().synchronize()
+
+
+class StepResult:
+    """Result of a submitted overlapped step: ``out`` once ``event`` (a CUDA event) has completed."""
+
+    def __init__(self, out=None):
+        self.out, self.event = out, None
 
 
 class GraphedLayer:
@@ -536,8 +590,25 @@ class HostPipeline:
             sl["out_done"].record(self.s_out)
         handle.event = sl["out_done"]
 
+    def _copy_out_overlapped(self):
+        """Overlapped steps: enqueues the result copy of the pending step behind the step's own event."""
+        if self.pending is None:
+            return
+        sl, out_host, handle, res = self.pending
+        self.pending = None
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(res.event)
+            out_host.copy_(sl["out"], non_blocking=True)
+            sl["out_done"] = torch.cuda.Event()
+            sl["out_done"].record(self.s_out)
+        handle.event = sl["out_done"]
+
     def flush(self):
         """Enqueues the result copy of the step submitted last without waiting for a next step."""
+        if self.overlapped is not None:
+            self.overlapped.flush()
+            self._copy_out_overlapped()
+            return
         self._copy_out(None)
 
     def submit(self, x_host, logits_host, out_host):
@@ -556,17 +627,16 @@ class HostPipeline:
                 sl["x"].copy_(x_host, non_blocking=True)
                 sl["in_done"] = torch.cuda.Event()
                 sl["in_done"].record(self.s_in)
-            if sl["out_done"] is not None:               # the copy that last read this slot's result
-                main.wait_event(sl["out_done"])
             if sl["out"] is None or sl["out"].shape != x_host.shape:
                 sl["out"] = torch.empty(x_host.shape, dtype=torch.bfloat16, device=self.layer.device)
-            self.overlapped.submit(sl["x"], sl["lg"], ready=sl["in_done"], out=sl["out"])
+            # (with the late sum this call also enqueues the end of the step submitted before: its event exists now)
+            res = self.overlapped.submit(sl["x"], sl["lg"], ready=sl["in_done"], out=sl["out"], out_free=sl["out_done"])
             sl["rows_sent"] = self.overlapped.rows_sent
-            sl["comp_done"] = torch.cuda.Event()
-            sl["comp_done"].record(main)
+            self._copy_out_overlapped()
             handle = PendingResult(self, step)
-            self.pending = (sl, out_host, handle)
-            self._copy_out(None)
+            self.pending = (sl, out_host, handle, res)
+            if res.event is not None:
+                self._copy_out_overlapped()
             return handle
         with torch.cuda.stream(self.s_in):
             # the previous step's rows are with their experts; that step follows, on the same stream,

@@ -568,16 +568,23 @@ def run_ours(args):
             if i > 1 and layer.phases is not None:
                 phase_events.append(layer.phases)
         barrier()
-        ov = OverlappedSteps(layer, t_local, reserve_sms=args.reserve_sms)
+        ov = OverlappedSteps(layer, t_local, reserve_sms=args.reserve_sms, late_sum=args.late_sum)
 
     def one_step(record=False):
         if ov is not None:
-            ov.submit(x, lg, record=record)
-        else:
-            layer.forward(x, lg, record=record)
+            return ov.submit(x, lg, record=record)
+        layer.forward(x, lg, record=record)
+        return None
 
+    def settle(last):  # overlapped steps: the caller's stream waits for the end of the last one
+        if last is not None:
+            ov.flush()
+            torch.cuda.current_stream().wait_event(last.event)
+
+    last = None
     for _ in range(args.warmup):
-        one_step()
+        last = one_step()
+    settle(last)
     barrier()
     ops.LAUNCHES = 0
     with ClockSampler(local_rank) as clk:
@@ -587,11 +594,12 @@ def run_ours(args):
         ev0.record()
         t_host = time.perf_counter()
         for _ in range(args.steps):
-            one_step(record=True)
+            last = one_step(record=True)
             if layer.timing is not None:
                 gemm_events.append(layer.timing)
             if ov is None and layer.phases is not None:
                 phase_events.append(layer.phases)
+        settle(last)
         ev1.record()
         host_ms_per_step = (time.perf_counter() - t_host) * 1e3 / args.steps  # the host's launch work per step
         barrier()
@@ -670,7 +678,7 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16 x int8 -> fp32 accumulate", "data": "synthetic",
         "config": workload_config(world), "exchange": exchange, "exchange_status": exchange_status,
-        "exchange_overlapped": ({"reserved_sms": args.reserve_sms, "phases_from": "serial passes before the timed region"}
+        "exchange_overlapped": ({"reserved_sms": args.reserve_sms, "late_sum": args.late_sum, "phases_from": "serial passes before the timed region"}
                                 if ov is not None else False),
         "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps_in_flight": depth, "cuda_graph": graphed is not None,
@@ -731,6 +739,8 @@ def main():
                     help="token exchange between ranks (N > 1): this package's peer-memory kernels or NCCL all-to-all")
     ap.add_argument("--no-overlap", action="store_true",
                     help="several ranks, p2p: run a step's token exchange serially before its GEMMs")
+    ap.add_argument("--late-sum", action="store_true",
+                    help="overlapped steps: wait for the peers' pushes and sum beside the next step's GEMMs (measured slower)")
     ap.add_argument("--reserve-sms", type=int, default=8,
                     help="SMs the grouped GEMMs leave to the next step's exchange kernels when steps overlap")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel lines (N=1)")

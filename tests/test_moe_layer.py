@@ -137,9 +137,10 @@ def _rank_main(rank, world, port, q, cuda=False, case_kw=None, exchange="nccl", 
 
             ins = [tuple(t[rank * tl:(rank + 1) * tl].to(dev) for t in _step_inputs(c, step)) for step in range(steps)]
             torch.cuda.synchronize()
-            ov = OverlappedSteps(layer, tl, reserve_sms=8)
+            ov = OverlappedSteps(layer, tl, reserve_sms=8, late_sum=(steps % 2 == 0))  # the six-step test runs the late sum
             res = [ov.submit(x, lg) for x, lg in ins]
             ov.drain()
+            res = [h.out for h in res]
             outs = [r.cpu().view(torch.int16).numpy() for r in res]
             # and the serial pass still works on the same layer afterwards
             x, lg = ins[0]
@@ -536,14 +537,28 @@ def test_overlapped_steps_single_rank_match_direct_path():
         ins.append((torch.roll(x, step, 0).cuda(), torch.roll(lg, 3 * step, 0).cuda()))
     want = [direct.forward(x, lg) for x, lg in ins]
     torch.cuda.synchronize()
-    for reserve in (8, 0):
-        ov = OverlappedSteps(p2p, 200, reserve_sms=reserve)
+    for reserve, late in ((8, True), (0, False), (4, False), (8, True)):
+        ov = OverlappedSteps(p2p, 200, reserve_sms=reserve, late_sum=late)
         got = [ov.submit(x, lg) for x, lg in ins]
+        assert all(h.event is not None for h in got[:-1]) and (got[-1].event is None) == late
         ov.drain()
         assert ops.set_gemm_reserved_sms(0) == 0          # restored after every step
         for step, (a, b) in enumerate(zip(want, got)):
-            assert torch.equal(a.view(torch.int16), b.view(torch.int16)), (reserve, step)
+            assert torch.equal(a.view(torch.int16), b.out.view(torch.int16)), (reserve, late, step)
     assert p2p.px.read_status()[0] == 0
+    # host buffers in, host buffers out, three steps in flight over overlapped steps (both kinds of step end)
+    from ascend_kernel_b200.moe_layer import HostPipeline
+
+    for late in (True, False):
+        pipe = HostPipeline(p2p, depth=3, overlapped=OverlappedSteps(p2p, 200, late_sum=late))
+        host_in = [(x.cpu().pin_memory(), lg.cpu().pin_memory()) for x, lg in ins]
+        host_out = [torch.empty(200, 256, dtype=torch.bfloat16).pin_memory() for _ in ins]
+        handles = [pipe.submit(x, lg, o) for (x, lg), o in zip(host_in, host_out)]
+        handles[2].synchronize()
+        assert torch.equal(want[2].cpu().view(torch.int16), host_out[2].view(torch.int16))
+        pipe.drain()
+        for step, (a, b) in enumerate(zip(want, host_out)):
+            assert torch.equal(a.cpu().view(torch.int16), b.view(torch.int16)), (late, step)
     b = p2p.forward(*ins[1])
     assert torch.equal(want[1].view(torch.int16), b.view(torch.int16))
     g = GraphedLayer(p2p, 200)
@@ -555,7 +570,7 @@ def test_overlapped_steps_single_rank_match_direct_path():
     ov = OverlappedSteps(p2p, 200)                        # ... and overlapped steps take it back
     got = ov.submit(*ins[3])
     ov.drain()
-    assert torch.equal(want[3].view(torch.int16), got.view(torch.int16))
+    assert torch.equal(want[3].view(torch.int16), got.out.view(torch.int16))
     assert p2p.px.read_status()[0] == 0
     p2p.px.close()
 
