@@ -518,7 +518,7 @@ def run_ours(args):
     assert E % world == 0 and T % world == 0
     e_local, t_local = E // world, T // world
     c = inputs.config4(dev, expert_lo=rank * e_local, expert_hi=(rank + 1) * e_local, **CFG)
-    exchange = args.exchange if world > 1 else "direct"
+    exchange = args.exchange if (world > 1 or args.single_rank_exchange) else "direct"
     # several ranks on the peer-memory exchange: a step's token exchange runs beside the GEMMs of the step before
     overlap = exchange == "p2p" and not args.no_overlap
     layer = MoELayer(c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], E, CFG["top_k"], group,
@@ -737,6 +737,9 @@ def main():
                     help="moe: the benchmark line; others: one kernel alone (for profiling)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="token exchange between ranks (N > 1): this package's peer-memory kernels or NCCL all-to-all")
+    ap.add_argument("--single-rank-exchange", action="store_true",
+                    help="one GPU: run the peer-memory exchange kernels all the same (the rank is its own peer), "
+                         "which puts the routing and row gather of a step beside the GEMMs of the step before")
     ap.add_argument("--no-overlap", action="store_true",
                     help="several ranks, p2p: run a step's token exchange serially before its GEMMs")
     ap.add_argument("--late-sum", action="store_true",
