@@ -323,7 +323,8 @@ class OverlappedSteps:
 
     ``submit`` takes inputs that are COMPLETE on the device when it is called (or by the ``ready`` event)
     and must stay untouched until the step's ``rows_sent`` event; results come back in submission order.
-    All ranks must submit the same number of steps.  The layer must have been built with
+    All ranks must submit the same number of steps, and ``drain`` before the object is dropped or the layer's
+    serial pass is used again.  The layer must have been built with
     ``exchange="p2p", exchange_buffers=2`` and the packed GEMMs."""
 
     def __init__(self, layer: "MoELayer", n_tokens: int, reserve_sms: int = 8, late_sum: bool = False):
@@ -340,6 +341,8 @@ class OverlappedSteps:
         dev, px = layer.device, layer.px
         px.use_host_steps()
         self.s_x = torch.cuda.Stream(dev, priority=-1)
+        # serial passes enqueued before this point on the caller's stream use the first buffer set
+        self.s_x.wait_stream(torch.cuda.current_stream())
         n_rows = n_tokens * layer.top_k
         self.sets = []
         for _ in range(2):
