@@ -1,7 +1,7 @@
 // Grouped GEMV for decode-sized expert batches (HBM-bandwidth kernel).
 //
 // Work item = (non-empty expert, slab of 256 output columns); persistent CTAs (two per SM) draw
-// items from a ticket counter, experts with the most rows first.  The expert's x rows (up to 4 per pass) are copied to shared memory
+// items from a ticket counter, experts with the most rows first, the slabs of an expert next to one another.  The expert's x rows (up to 4 per pass) are copied to shared memory
 // once per item.  Every warp streams its share of the k rows straight from global memory with
 // 128-bit coalesced loads, eight row pairs (8 x 512 B per warp) in flight before the first is
 // consumed, decodes the packed weights in registers (byte / nibble unpack, no shared-memory
@@ -831,10 +831,11 @@ __global__ void __launch_bounds__(kGvThreads, 2) grouped_gemv_kernel(const GemvA
         __syncthreads();
         const int item = s_item;
         if (item >= n_items) break;
-        // slab-major order: neighbouring CTAs work on different experts, so experts with more rows
-        // (slower items) are spread over the grid instead of landing on 16 adjacent CTAs
-        const int g = active[item % n_act];
-        const int n0 = (item / n_act) * kGvSlabN;
+        // expert-major order: the CTAs that run at the same time hold neighbouring slabs of the same experts and
+        // walk the same k rows together, so whole rows of the weight matrix are fetched close in time (DRAM
+        // pages stay open: measured +1..6 % over slab-major order); the experts with the most rows still come first
+        const int g = active[item / n_slabs];
+        const int n0 = (item % n_slabs) * kGvSlabN;
         const int r0 = row_start[g], r1 = row_start[g + 1];
         for (int r = r0; r < r1; r += kGvRows) {
             const int rows = min(kGvRows, r1 - r);
