@@ -28,6 +28,7 @@ constexpr int kGvIterRows = kGvWarps * kGvWarpRows;     // k rows a CTA consumes
 constexpr int kGvRows = 4;                              // x rows per pass
 constexpr int kGvXPad = 16;                             // bf16 elements between staged x rows (bank spread)
 constexpr int kGvMmaParts = 4;                          // k groups of the tensor-core path
+constexpr int kGvL2Steps = 6;                           // steps a warp requests into L2 ahead of its register loads
 
 struct GemvArgs {
     const __nv_bfloat16* x;
@@ -166,7 +167,19 @@ __device__ __forceinline__ void gv_compute(const GemvArgs& a, const __nv_bfloat1
 #pragma unroll
     for (int c = 0; c < 8; ++c) sc[c] = tc[c] = 0ull;
 
+    // int8 / fp8: the warp's rows of the steps kGvL2Steps ahead are requested into L2, one line per lane (16 rows
+    // x the slab's 256-byte row segment): the register loads then wait for L2 instead of DRAM.  (The nibble
+    // formats' versions of this function have no registers to spare for it.)
+    const uint8_t* pf_base = a.weight + (size_t)g * a.K * row_bytes + n0 + 128 * (lane & 1);
+    auto prefetch_step = [&](int k) {
+        if constexpr (!T::kNibbles) {
+            if (k + (lane >> 1) < a.K) asm volatile("prefetch.global.L2 [%0];" ::"l"(pf_base + (size_t)(k + (lane >> 1)) * row_bytes));
+        }
+    };
+#pragma unroll
+    for (int i = 0; i < kGvL2Steps; ++i) prefetch_step(warp * kGvWarpRows + i * kGvIterRows);
     for (int k0 = warp * kGvWarpRows; k0 < a.K; k0 += kGvIterRows) {
+        prefetch_step(k0 + kGvL2Steps * kGvIterRows);
         // ---- issue all loads of this step first ----
         uint4 q[kGvUnroll];
         const uint8_t* p = wbase + (size_t)(k0 + half) * row_bytes;
@@ -345,7 +358,17 @@ __device__ __forceinline__ void gv_compute_mma(const GemvArgs& a, const __nv_bfl
     constexpr int kStepRows = 16 * kGvMmaParts;  // k rows the CTA consumes per step
     // (fp8 accepts N % 256 == 128: in the last slab the warps of the second column half have no columns)
     const int k_end = (n0 + 128 * hc < a.N) ? a.K : 0;
+    // two steps (2 x 16 rows of the warp's 128-byte row segment) per iteration: one line per lane into L2,
+    // kGvL2Steps / 2 iterations ahead
+    const uint8_t* pf_base = a.weight + (size_t)g_expert * a.K * row_bytes + n0 + 128 * hc;
+    auto prefetch_iter = [&](int k) {
+        const int kk = k + (lane >> 4) * kStepRows + (lane & 15);
+        if (kk < k_end) asm volatile("prefetch.global.L2 [%0];" ::"l"(pf_base + (size_t)kk * row_bytes));
+    };
+#pragma unroll
+    for (int i = 0; i < kGvL2Steps / 2; ++i) prefetch_iter(kg * 16 + i * 2 * kStepRows);
     for (int k0 = kg * 16; k0 < k_end; k0 += 2 * kStepRows) {
+        prefetch_iter(k0 + (kGvL2Steps / 2) * 2 * kStepRows);
         const bool second = k0 + kStepRows < a.K;
         float sf = 1.f;
         if constexpr (kBlockScale)  // k0 and k0 + 64 lie in the same 128-row block (K % 128 == 0)
