@@ -24,29 +24,68 @@ __global__ void silu_mul_kernel(const uint4* __restrict__ h, uint4* __restrict__
     out[i] = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-// dst[i, :] = src[index[i], :]; one CTA per destination row, 16 bytes per thread per step.
-__global__ void gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ index,
-                                   uint4* __restrict__ dst, int width16) {
-    const long long row = blockIdx.x;
-    const long long from = index[row];
-    for (int c = threadIdx.x; c < width16; c += blockDim.x) dst[row * width16 + c] = src[from * width16 + c];
+// dst[i, :] = src[index[i], :].  One warp per destination row at a time (grid-stride over rows); a lane keeps
+// eight 16-byte loads in flight before the first store, and the next row's index is fetched while the current
+// row is being copied: a copy kernel is bound by the bytes in flight, not by its instruction count.
+constexpr int kRowUnroll = 8;
+
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ index,
+                                                          uint4* __restrict__ dst, int width16, int n_rows) {
+    const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    const int n_warps = gridDim.x * wpb;
+    int row = blockIdx.x * wpb + (threadIdx.x >> 5);
+    long long from = row < n_rows ? __ldg(index + row) : 0;
+    for (; row < n_rows; row += n_warps) {
+        const uint4* s = src + from * width16;
+        uint4* d = dst + (long long)row * width16;
+        const int next = row + n_warps;
+        if (next < n_rows) from = __ldg(index + next);
+        for (int c = lane; c < width16; c += 32 * kRowUnroll) {
+            uint4 v[kRowUnroll];
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u)
+                if (c + 32 * u < width16) v[u] = __ldg(s + c + 32 * u);
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u)
+                if (c + 32 * u < width16) d[c + 32 * u] = v[u];
+        }
+    }
 }
 
-// out[t, :] = bf16(sum_j weight[t, j] * y[slot[t, j], :]) in fp32; one CTA per token.
-__global__ void combine_kernel(const uint4* __restrict__ y, const int32_t* __restrict__ slot,
-                               const float* __restrict__ weight, uint4* __restrict__ out, int top_k, int width16) {
+// out[t, :] = bf16(sum_j weight[t, j] * y[slot[t, j], :]) in fp32; one CTA per token.  The token's row indices
+// and weights are read once into shared memory; a thread then has its top_k 16-byte loads of a column chunk
+// in flight together.
+constexpr int kCombineMaxK = 32;
+
+__global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ y, const int32_t* __restrict__ slot,
+                                                      const float* __restrict__ weight, uint4* __restrict__ out, int top_k,
+                                                      int width16) {
     const long long t = blockIdx.x;
+    __shared__ long long s_row[kCombineMaxK];
+    __shared__ float s_w[kCombineMaxK];
+    if ((int)threadIdx.x < top_k) {
+        s_row[threadIdx.x] = (long long)slot[t * top_k + threadIdx.x] * width16;
+        s_w[threadIdx.x] = weight[t * top_k + threadIdx.x];
+    }
+    __syncthreads();
     for (int c = threadIdx.x; c < width16; c += blockDim.x) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int j = 0; j < top_k; ++j) {
-            const long long s = slot[t * top_k + j];
-            const float w = weight[t * top_k + j];
-            const uint4 v = y[s * width16 + c];
-            const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+        for (int j0 = 0; j0 < top_k; j0 += 8) {
+            uint4 v[8];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                acc[2 * q] = fmaf(w, __uint_as_float(vw[q] << 16), acc[2 * q]);
-                acc[2 * q + 1] = fmaf(w, __uint_as_float(vw[q] & 0xFFFF0000u), acc[2 * q + 1]);
+            for (int j = 0; j < 8; ++j)
+                if (j0 + j < top_k) v[j] = __ldg(y + s_row[j0 + j] + c);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (j0 + j < top_k) {
+                    const float w = s_w[j0 + j];
+                    const uint32_t vw[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        acc[2 * q] = fmaf(w, __uint_as_float(vw[q] << 16), acc[2 * q]);
+                        acc[2 * q + 1] = fmaf(w, __uint_as_float(vw[q] & 0xFFFF0000u), acc[2 * q + 1]);
+                    }
+                }
             }
         }
         out[t * width16 + c] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
@@ -229,15 +268,17 @@ extern "C" int b200moe_gather_rows(const void* src, const int32_t* index, void* 
     if (n_rows == 0) return B200MOE_OK;
     if (!src || !index || !dst) return B200MOE_ERR_NULL_POINTER;
     if (!aligned16(src) || !aligned16(dst)) return B200MOE_ERR_ALIGNMENT;
-    gather_rows_kernel<<<(unsigned)n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(src), index, static_cast<uint4*>(dst), (int)(width / 8));
+    // eight warps per CTA, up to eight CTAs per SM: every warp copies a few rows
+    const long long want = (n_rows + 7) / 8, cap = 8LL * sm_count();
+    gather_rows_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(src), index, static_cast<uint4*>(dst), (int)(width / 8), (int)n_rows);
     B200MOE_CUDA_TRY(cudaGetLastError());
     return B200MOE_OK;
 }
 
 extern "C" int b200moe_combine(const void* y, const int32_t* slot, const float* weight, void* out, int64_t n_tokens,
                                int64_t top_k, int64_t width, void* stream) {
-    if (n_tokens < 0 || top_k <= 0 || width <= 0 || (width % 8) != 0 || n_tokens > 0x7FFFFFFFLL)
+    if (n_tokens < 0 || top_k <= 0 || top_k > kCombineMaxK || width <= 0 || (width % 8) != 0 || n_tokens > 0x7FFFFFFFLL)
         return B200MOE_ERR_SHAPE;
     if (n_tokens == 0) return B200MOE_OK;
     if (!y || !slot || !weight || !out) return B200MOE_ERR_NULL_POINTER;

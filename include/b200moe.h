@@ -231,7 +231,7 @@ int b200moe_silu_mul(const void* h, void* out, int64_t rows, int64_t inter, void
 int b200moe_gather_rows(const void* src, const int32_t* index, void* dst, int64_t n_rows, int64_t width,
                         void* stream);
 /* out[t, :] = bf16( sum_j weight[t, j] * y[slot[t, j], :] ), y bf16 [*, width], slot int32 [T, top_k],
- * weight fp32 [T, top_k]. */
+ * weight fp32 [T, top_k]; top_k <= 32. */
 int b200moe_combine(const void* y, const int32_t* slot, const float* weight, void* out, int64_t n_tokens,
                     int64_t top_k, int64_t width, void* stream);
 
