@@ -14,8 +14,11 @@ scaling): each of the N ranks holds 4096/N tokens and 256/N experts.
 Rank 0 prints ONE JSON line.  `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is
 the same metric through the public host-buffer call (`HostPipeline.submit`: pinned host -> device
 copies of every step's inputs and the device -> host read of every step's result inside the timed
-region, two steps in flight so that the copies of neighbouring steps overlap the expert GEMMs;
-`single_step_latency_ms` is the unpipelined `MoELayer.forward_host`); `roofline` covers the
+region, two steps in flight -- three on several GPUs -- so that the copies of neighbouring steps overlap
+the expert GEMMs; `single_step_latency_ms` is the unpipelined `MoELayer.forward_host`).  On several GPUs
+(peer-memory exchange) the steps are `OverlappedSteps`: a step's routing and token dispatch run on a second
+stream beside the previous step's gate/up GEMM; `phases_ms_rank0` then comes from serial passes made before
+the timed region, `--no-overlap` times the serial pass itself.  `roofline` covers the
 dominant kernel of the step (the tcgen05 grouped GEMM, both launches); `kernels` (N=1 only) holds
 the three hot-path kernels at their own benchmark configurations (prefill grouped GEMM, decode
 grouped GEMV, FP4 dequant) with their roofline fractions of the measured peaks; `cpu_baseline` is
