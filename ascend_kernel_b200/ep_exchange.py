@@ -2,8 +2,8 @@
 
 ``PeerExchange`` owns this rank's exchange buffers (allocated by the C library so that the
 other processes of the node can map them through CUDA IPC), maps every peer's buffers, and wraps
-the exchange kernels of ``include/b200moe.h`` (``b200moe_ep_*``).  With ``n_buffers=2`` the row,
-count and return buffers exist twice and a step uses the set its ``parity`` names, so that the
+the exchange kernels of ``include/b200moe.h`` (``b200moe_ep_*``).  With ``n_buffers`` = 2 or 3 the row,
+count and return buffers exist that many times and a step uses the set its ``parity`` names, so that the
 exchange of one step can run while the expert GEMMs of the step before still read the other set
 (moe_layer.OverlappedSteps); the signal words are shared, their step numbers only grow.  torch.distributed is used once,
 at construction, to pass the 64-byte IPC handles around; a layer step itself makes no collective
@@ -39,9 +39,9 @@ class PeerExchange:
     def __init__(self, group, n_experts: int, hidden: int, cap_rows: int, device, n_buffers: int = 1):
         """``group``: the expert-parallel process group (all ranks on one node) or None for a single
         rank.  ``cap_rows``: rows this rank's receive / result buffers hold; the worst case is
-        (tokens of all ranks) x top_k.  ``n_buffers``: 1, or 2 for steps that overlap."""
-        if n_buffers not in (1, 2):
-            raise ValueError("n_buffers must be 1 or 2")
+        (tokens of all ranks) x top_k.  ``n_buffers``: 1, or 2 / 3 for steps that overlap."""
+        if n_buffers not in (1, 2, 3):
+            raise ValueError("n_buffers must be 1, 2 or 3")
         self.n_buffers = n_buffers
         self.device = torch.device(device)
         self.n_experts, self.hidden, self.cap_rows = n_experts, hidden, cap_rows
@@ -60,8 +60,8 @@ class PeerExchange:
         one = {"recv_x": cap_rows * hidden * 2, "y": cap_rows * hidden * 2,
                "counts": -(-self.world * n_experts * 4 // 256) * 256, "signal": 3 * _abi.EP_MAX_WORLD * 8,
                "ret": self.cap_send * hidden * 2, "ret_code": cap_rows * 8}
-        doubled = ("recv_x", "counts", "ret", "ret_code") if n_buffers == 2 else ()
-        sizes = {name: nbytes * (2 if name in doubled else 1) for name, nbytes in one.items()}
+        doubled = ("recv_x", "counts", "ret", "ret_code") if n_buffers > 1 else ()
+        sizes = {name: nbytes * (n_buffers if name in doubled else 1) for name, nbytes in one.items()}
         self._own, handles = {}, {}
         with torch.cuda.device(self.device):
             for name, nbytes in sizes.items():

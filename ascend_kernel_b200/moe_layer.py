@@ -327,17 +327,28 @@ class OverlappedSteps:
     serial pass is used again.  The layer must have been built with
     ``exchange="p2p", exchange_buffers=2`` and the packed GEMMs."""
 
-    def __init__(self, layer: "MoELayer", n_tokens: int, reserve_sms: int = 8, late_sum: bool = False):
+    def __init__(self, layer: "MoELayer", n_tokens: int, reserve_sms: int = 8, late_sum: bool = False,
+                 defer_sum: bool = False):
         """``late_sum``: the end of a step -- the wait for the other ranks' pushes and the weighted sum -- also
         runs on the exchange stream, beside the NEXT step's gate/up GEMM, so the caller's stream goes from one
         step's down projection straight to the next step's gate/up GEMM and a slow peer's pushes are waited for
         off the critical path; both GEMMs then leave ``reserve_sms`` SMs free.  A step's result is then
         complete by the event of the handle ``submit`` returns (set by the next ``submit`` or by ``flush``),
         not in the order of the caller's stream.  Off by default: measured 2-4 % slower on 2 and 4 GPUs (the
-        down projection gives up SMs as well and the sum runs on the few that are free)."""
-        if layer.px is None or layer.px.n_buffers != 2 or layer.gemm != "packed":
-            raise RuntimeError('OverlappedSteps needs exchange="p2p", exchange_buffers=2 and the packed GEMMs')
+        down projection gives up SMs as well and the sum runs on the few that are free).
+        ``defer_sum`` (needs ``exchange_buffers=3``): the end of a step stays on the caller's stream but is
+        enqueued after the NEXT step's GEMMs, so the wait for the slowest peer's pushes finds them long done
+        -- the ranks stop meeting at a barrier every step; steps then rotate over three buffer sets (the
+        exchange of step k+2 must not wait for the sum of step k, which now comes after step k+1's GEMMs).
+        Results are complete by the handle's event, one ``submit`` (or ``flush``) later."""
+        if layer.px is None or layer.px.n_buffers < 2 or layer.gemm != "packed":
+            raise RuntimeError('OverlappedSteps needs exchange="p2p", exchange_buffers=2 or 3 and the packed GEMMs')
+        if late_sum and defer_sum:
+            raise ValueError("late_sum and defer_sum exclude one another")
+        if defer_sum and layer.px.n_buffers < 3:
+            raise RuntimeError("defer_sum needs exchange_buffers=3")
         self.layer, self.n_tokens, self.reserve_sms, self.late_sum = layer, n_tokens, reserve_sms, late_sum
+        self.defer_sum, self.n_sets = defer_sum, (3 if defer_sum else 2)
         dev, px = layer.device, layer.px
         px.use_host_steps()
         self.s_x = torch.cuda.Stream(dev, priority=-1)
@@ -345,7 +356,7 @@ class OverlappedSteps:
         self.s_x.wait_stream(torch.cuda.current_stream())
         n_rows = n_tokens * layer.top_k
         self.sets = []
-        for _ in range(2):
+        for _ in range(self.n_sets):
             self.sets.append(dict(
                 route=ops.moe_route_buffers(n_tokens, layer.n_experts, layer.top_k, dev),
                 disp=(torch.empty(n_rows, dtype=torch.int32, device=dev),
@@ -358,22 +369,26 @@ class OverlappedSteps:
         self.tail = None       # late_sum: what is left to enqueue of the step submitted last
 
     def _finish(self, tail):
-        """Exchange stream: waits for every owner's pushes of the step, then sums each token's rows."""
+        """Waits for every owner's pushes of the step, then sums each token's rows: on the exchange stream
+        (late_sum) or on the caller's (defer_sum)."""
         layer, px = self.layer, self.layer.px
-        with torch.cuda.stream(self.s_x):
-            self.s_x.wait_event(tail["posted"])
+        stream = self.s_x if self.late_sum else torch.cuda.current_stream()
+        with torch.cuda.stream(stream):
+            stream.wait_event(tail["posted"])
             px.wait(2, step=tail["step"])
             handle = tail["handle"]
             if tail["out_free"] is not None:     # whoever last read the caller's output buffer
-                self.s_x.wait_event(tail["out_free"])
-            if handle.out is None:               # (allocated on the exchange stream: wait for the event before use)
+                stream.wait_event(tail["out_free"])
+            if handle.out is None:               # (allocated on that stream: wait for the event before use elsewhere)
                 handle.out = torch.empty(self.n_tokens, layer.hidden, dtype=torch.bfloat16, device=layer.device)
             layer.ops.combine(px.ret_sets[tail["parity"]], tail["slot"], tail["wts"], handle.out)
             handle.event = torch.cuda.Event()
-            handle.event.record(self.s_x)
+            handle.event.record(stream)
+            if self.defer_sum:
+                self.sets[tail["parity"]]["done"] = handle.event
 
     def flush(self):
-        """late_sum: enqueues the end of the step submitted last without waiting for a next step."""
+        """late_sum / defer_sum: enqueues the end of the step submitted last without waiting for a next step."""
         if self.tail is not None:
             tail, self.tail = self.tail, None
             self._finish(tail)
@@ -386,7 +401,7 @@ class OverlappedSteps:
         layer, px = self.layer, self.layer.px
         if x.shape[0] != self.n_tokens:
             raise RuntimeError("OverlappedSteps was built for another token count")
-        p = self.n % 2
+        p = self.n % self.n_sets
         self.n += 1
         st = self.sets[p]
         step = px.begin_step()
@@ -406,7 +421,8 @@ class OverlappedSteps:
         self.rows_sent = sent
         # late_sum: the previous step's end follows this step's exchange on the exchange stream (its own set of
         # buffers is the other one; the step before that, which used this set, ended before this exchange began)
-        self.flush()
+        if self.late_sum:
+            self.flush()
         main.wait_event(sent)
         px.wait(1, step=step)                # rows of every source rank have landed
         # The gate/up GEMM makes room: the next step's exchange is released when the previous step's weighted
@@ -423,7 +439,7 @@ class OverlappedSteps:
                 ev[1].record()
                 ev[2].record()
             if not self.late_sum:
-                ops.set_gemm_reserved_sms(prev)
+                ops.set_gemm_reserved_sms(prev)  # (defer_sum too: nothing runs beside the down projection)
             ops.grouped_gemm_packed_scatter(st["act"], layer.w2, layer.s2, layer.o2, local_counts,
                                             px.ret_code_sets[p], px.ret_ptrs_sets[p], px.cap_send, group_list_type=1)
         finally:
@@ -433,11 +449,14 @@ class OverlappedSteps:
         layer.timing = ev
         px.post(2, step=step)                # this rank's pushes are complete and visible
         handle = StepResult(out)
-        if self.late_sum:
+        if self.late_sum or self.defer_sum:
             posted = torch.cuda.Event()
             posted.record(main)
+            if self.defer_sum:
+                self.flush()                 # the previous step's end, behind this step's GEMMs on this stream
             self.tail = dict(step=step, parity=p, slot=slot, wts=wts, posted=posted, handle=handle, out_free=out_free)
-            st["done"] = None                # the exchange stream itself orders the sets' reuse
+            if self.late_sum:
+                st["done"] = None            # the exchange stream itself orders the sets' reuse
             return handle
         px.wait(2, step=step)                # every owner has pushed this rank's rows
         if out_free is not None:

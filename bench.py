@@ -526,7 +526,7 @@ def run_ours(args):
     overlap = exchange == "p2p" and not args.no_overlap
     layer = MoELayer(c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], E, CFG["top_k"], group,
                      exchange="p2p" if exchange == "p2p" else "nccl", max_tokens=t_local,
-                     exchange_buffers=2 if overlap else 1)
+                     exchange_buffers=(3 if args.defer_sum else 2) if overlap else 1)
     x_host = c["x"][rank * t_local:(rank + 1) * t_local].contiguous().pin_memory()
     lg_host = c["logits"][rank * t_local:(rank + 1) * t_local].contiguous().pin_memory()
     x, lg = x_host.to(dev), lg_host.to(dev)
@@ -571,7 +571,7 @@ def run_ours(args):
             if i > 1 and layer.phases is not None:
                 phase_events.append(layer.phases)
         barrier()
-        ov = OverlappedSteps(layer, t_local, reserve_sms=args.reserve_sms, late_sum=args.late_sum)
+        ov = OverlappedSteps(layer, t_local, reserve_sms=args.reserve_sms, late_sum=args.late_sum, defer_sum=args.defer_sum)
 
     def one_step(record=False):
         if ov is not None:
@@ -681,7 +681,7 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16 x int8 -> fp32 accumulate", "data": "synthetic",
         "config": workload_config(world), "exchange": exchange, "exchange_status": exchange_status,
-        "exchange_overlapped": ({"reserved_sms": args.reserve_sms, "late_sum": args.late_sum, "phases_from": "serial passes before the timed region"}
+        "exchange_overlapped": ({"reserved_sms": args.reserve_sms, "late_sum": args.late_sum, "defer_sum": args.defer_sum, "phases_from": "serial passes before the timed region"}
                                 if ov is not None else False),
         "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps_in_flight": depth, "cuda_graph": graphed is not None,
@@ -745,6 +745,9 @@ def main():
                          "which puts the routing and row gather of a step beside the GEMMs of the step before")
     ap.add_argument("--no-overlap", action="store_true",
                     help="several ranks, p2p: run a step's token exchange serially before its GEMMs")
+    ap.add_argument("--defer-sum", action="store_true",
+                    help="overlapped steps: a step's wait for the peers' pushes and its weighted sum follow the NEXT "
+                         "step's GEMMs on the same stream (three buffer sets): no barrier between the ranks every step")
     ap.add_argument("--late-sum", action="store_true",
                     help="overlapped steps: wait for the peers' pushes and sum beside the next step's GEMMs (measured slower)")
     ap.add_argument("--reserve-sms", type=int, default=8,

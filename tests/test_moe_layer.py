@@ -124,11 +124,11 @@ def _rank_main(rank, world, port, q, cuda=False, case_kw=None, exchange="nccl", 
         el, tl = c["E"] // world, c["x"].shape[0] // world
         sl = slice(rank * el, (rank + 1) * el)
         w = [c[k][sl].contiguous().to(dev) for k in ("w13", "s13", "o13", "w2", "s2", "o2")]
-        overlap = exchange == "p2p+overlap"
+        overlap, defer = exchange in ("p2p+overlap", "p2p+defer"), exchange == "p2p+defer"
         if overlap:
             exchange = "p2p"
         layer = MoELayer(*w, c["E"], c["top_k"], dist.group.WORLD, CudaRowOps if cuda else TorchRowOps,
-                         exchange=exchange, max_tokens=tl, exchange_buffers=2 if overlap else 1)
+                         exchange=exchange, max_tokens=tl, exchange_buffers=(3 if defer else 2) if overlap else 1)
         outs = []
         if overlap:
             # every step enqueued before the host looks at anything: the exchange of a step runs beside the
@@ -137,7 +137,8 @@ def _rank_main(rank, world, port, q, cuda=False, case_kw=None, exchange="nccl", 
 
             ins = [tuple(t[rank * tl:(rank + 1) * tl].to(dev) for t in _step_inputs(c, step)) for step in range(steps)]
             torch.cuda.synchronize()
-            ov = OverlappedSteps(layer, tl, reserve_sms=8, late_sum=(steps % 2 == 0))  # the six-step test runs the late sum
+            # (the six-step test runs the late sum)
+            ov = OverlappedSteps(layer, tl, reserve_sms=8, late_sum=(steps % 2 == 0 and not defer), defer_sum=defer)
             res = [ov.submit(x, lg) for x, lg in ins]
             ov.drain()
             res = [h.out for h in res]
@@ -546,6 +547,16 @@ def test_overlapped_steps_single_rank_match_direct_path():
         for step, (a, b) in enumerate(zip(want, got)):
             assert torch.equal(a.view(torch.int16), b.out.view(torch.int16)), (reserve, late, step)
     assert p2p.px.read_status()[0] == 0
+    # the sum of a step deferred behind the next step's GEMMs: three buffer sets
+    p3 = MoELayer(*w, c["E"], c["top_k"], exchange="p2p", max_tokens=200, exchange_buffers=3)
+    ov = OverlappedSteps(p3, 200, defer_sum=True)
+    got = [ov.submit(x, lg) for x, lg in ins]
+    assert got[-1].event is None and all(h.event is not None for h in got[:-1])
+    ov.drain()
+    for step, (a, b) in enumerate(zip(want, got)):
+        assert torch.equal(a.view(torch.int16), b.out.view(torch.int16)), ("defer", step)
+    assert p3.px.read_status()[0] == 0
+    p3.px.close()
     # host buffers in, host buffers out, three steps in flight over overlapped steps (both kinds of step end)
     from ascend_kernel_b200.moe_layer import HostPipeline
 
@@ -580,13 +591,25 @@ def test_two_gpu_ranks_overlapped_steps_match_oracle():
     """Overlapped steps on two GPUs: six steps with changing inputs, all enqueued up front."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
+    _two_gpu_overlapped(dict(T=200, H=256, E=8, I=256, k=2), "p2p+overlap", 6)
+
+
+@pytest.mark.gpu
+def test_two_gpu_ranks_overlapped_steps_with_deferred_sum_match_oracle():
+    """The same with a step's weighted sum enqueued behind the next step's GEMMs (three buffer sets): seven
+    steps, so every set is used at least twice."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _two_gpu_overlapped(dict(T=200, H=256, E=8, I=256, k=2), "p2p+defer", 7)
+
+
+def _two_gpu_overlapped(kw, exchange, steps):
     import torch.multiprocessing as mp
 
-    kw = dict(T=200, H=256, E=8, I=256, k=2)
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q, True, kw, "p2p+overlap", 6)) for r in range(2)]
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q, True, kw, exchange, steps)) for r in range(2)]
     for p in procs:
         p.start()
     got = dict(q.get(timeout=300) for _ in range(2))
@@ -596,7 +619,7 @@ def test_two_gpu_ranks_overlapped_steps_match_oracle():
     c = small_case(**kw)
     for r in range(2):
         assert got[r][1][0] == 0, got[r][1]
-    for step in range(6):
+    for step in range(steps):
         x, lg = _step_inputs(c, step)
         gold = O.moe_layer(x, lg, c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], c["top_k"])
         out = torch.cat([torch.from_numpy(got[r][0][step]).view(torch.bfloat16) for r in range(2)])
