@@ -494,6 +494,30 @@ def layer_gemm_case(quick: bool):
 # ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
+def bind_to_gpu_numa_node(torch, index: int):
+    """Restricts this process to the CPUs of the NUMA node the GPU hangs off (read from sysfs), so that the
+    pinned host buffers it allocates next are local to that GPU's PCIe root.  One process per GPU only; returns
+    the node, or None when the topology cannot be read (nothing is changed then).  CPU affinity of this process
+    is the only thing touched."""
+    try:
+        p = torch.cuda.get_device_properties(index)
+        bdf = "%04x:%02x:%02x.0" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return node
+    except Exception:  # no sysfs, no such attribute, not permitted: run unbound
+        return None
+
+
 def run_ours(args):
     import torch
 
@@ -504,6 +528,8 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device: the operators have no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    # several ranks share the host: each keeps its pinned buffers on its own GPU's NUMA node
+    numa_node = bind_to_gpu_numa_node(torch, local_rank) if world > 1 else None
     group = None
     if world > 1:
         import torch.distributed as dist
@@ -686,6 +712,7 @@ def run_ours(args):
         "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps_in_flight": depth, "cuda_graph": graphed is not None,
                 "exchange_overlapped": ov is not None, "host_ms_per_submit_rank0": host_ms_per_submit,
+                "host_numa_node_rank0": numa_node,
                 "single_step_latency_ms": latency_ms},
         "host_launch_ms_per_step_rank0": host_ms_per_step,
         "gpu_launches": launches * args.steps, "gpu_launches_per_step": launches,
