@@ -76,7 +76,7 @@ def _load() -> ctypes.CDLL:
     lib.b200moe_grouped_gemm_int8_packed_scatter.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.POINTER(vp), i64, i64, i64, i64, i64,
                                                              i64, i32, vp, sz, vp]
     lib.b200moe_grouped_gemm_int8_packed_scatter.restype = i32
-    lib.b200moe_set_gemm_reserved_sms.argtypes = [i32, i32]
+    lib.b200moe_set_gemm_reserved_sms.argtypes = [i32]
     lib.b200moe_set_gemm_reserved_sms.restype = i32
     lib.b200moe_grouped_gemm_int8_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, vp]
     lib.b200moe_grouped_gemm_int8_noalloc.restype = i32

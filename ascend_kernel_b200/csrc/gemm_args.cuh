@@ -19,9 +19,6 @@ struct GemmArgs {
     __nv_bfloat16* dst_base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     int n_base = 0;
     long long dst_rows = 0;
-    // packed kernel: CTAs that give their SMs to other kernels (b200moe_set_gemm_reserved_sms)
-    int reserve_sms = 0;
-    int reserve_only_if_free = 0;
 };
 
 // out[m] = sum_k x[m, k] in fp32 for the rows the group list uses (grouped_gemm.cu).

@@ -41,15 +41,13 @@
 namespace b200moe {
 namespace pk {
 
-// SMs the persistent kernels of this file leave to other kernels (b200moe_set_gemm_reserved_sms): the number, and
-// whether they are only given up when that adds no wave of tiles.  The grid always has one CTA per SM; the CTAs
-// that give way find out in the kernel, where the number of tiles is known, and leave at once.
-static std::atomic<int> g_reserved_sms{0}, g_reserved_only_if_free{0};
-static void reserved_sms(int* n, int* only_if_free) {
+// SMs the persistent kernels of this file leave to other kernels (b200moe_set_gemm_reserved_sms)
+static std::atomic<int> g_reserved_sms{0};
+static unsigned grid_ctas() {
     const int sms = sm_count();
     int r = g_reserved_sms.load(std::memory_order_relaxed);
-    *n = r < 0 ? 0 : (r > sms - 1 ? sms - 1 : r);
-    *only_if_free = g_reserved_only_if_free.load(std::memory_order_relaxed);
+    r = r < 0 ? 0 : (r > sms - 1 ? sms - 1 : r);
+    return (unsigned)(sms - r);
 }
 
 constexpr int kBK = 64;        // k per stage
@@ -283,14 +281,6 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 
     const int n_tiles = sb->n_tiles;
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&sb->tmem_base);
-    // The last reserve_sms CTAs give their SMs to other kernels: always, or only when the remaining CTAs still
-    // finish the tiles in the same number of waves (tiles of a launch last about equally long).  A CTA that gives
-    // way draws no ticket: its schedule ends at once and it leaves through the ordinary exit.
-    bool give_way = false;
-    if (a.reserve_sms > 0 && (int)blockIdx.x >= (int)gridDim.x - a.reserve_sms) {
-        const int all = (int)gridDim.x, fewer = all - a.reserve_sms;
-        give_way = !a.reserve_only_if_free || (n_tiles + fewer - 1) / fewer == (n_tiles + all - 1) / all;
-    }
 
     if (warp == kWarpProd) {
         // ------------------------------ x-tile producer ------------------------------
@@ -298,7 +288,7 @@ grouped_gemm_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             uint32_t ia = 0, seq = 0, published = 0;
             bool ok = true;
             int* ticket = a.status + 2;  // zeroed by the host before the launch
-            int held = give_way ? n_tiles : atomicAdd(ticket, 1);
+            int held = atomicAdd(ticket, 1);
             TileInfo far_ti;  // the tile published last, resolved
             auto publish = [&]() -> bool {
                 const bool live = held < n_tiles;
@@ -646,10 +636,7 @@ __global__ void pack_weight_int8_kernel(const int8_t* __restrict__ w, uint4* __r
 
 using namespace b200moe;
 
-extern "C" int b200moe_set_gemm_reserved_sms(int n, int only_if_free) {
-    pk::g_reserved_only_if_free.store(only_if_free ? 1 : 0);
-    return pk::g_reserved_sms.exchange(n < 0 ? 0 : n);
-}
+extern "C" int b200moe_set_gemm_reserved_sms(int n) { return pk::g_reserved_sms.exchange(n < 0 ? 0 : n); }
 
 extern "C" int b200moe_pack_weight_int8(const void* weight, void* packed, int64_t G, int64_t K, int64_t N, int gate_up,
                                         void* stream) {
@@ -692,7 +679,6 @@ static int packed_launch(const void* x, const void* packed, const void* scale, c
     a.rowsum = nullptr;
     a.group_list = group_list;
     a.y = static_cast<__nv_bfloat16*>(y);
-    pk::reserved_sms(&a.reserve_sms, &a.reserve_only_if_free);
     a.M = (int)M; a.K = (int)K; a.N = (int)N; a.G = (int)G;
     a.gl_type = group_list_type;
     a.status = static_cast<int*>(workspace);
@@ -723,11 +709,11 @@ static int packed_launch(const void* x, const void* packed, const void* scale, c
     if (gate_up_silu) {
         B200MOE_CUDA_TRY(cudaFuncSetAttribute(pk::grouped_gemm_packed_kernel<true>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        pk::grouped_gemm_packed_kernel<true><<<sm_count(), pk::kThreads, smem, s>>>(tx, txs, static_cast<const uint8_t*>(packed), a);
+        pk::grouped_gemm_packed_kernel<true><<<pk::grid_ctas(), pk::kThreads, smem, s>>>(tx, txs, static_cast<const uint8_t*>(packed), a);
     } else {
         B200MOE_CUDA_TRY(cudaFuncSetAttribute(pk::grouped_gemm_packed_kernel<false>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        pk::grouped_gemm_packed_kernel<false><<<sm_count(), pk::kThreads, smem, s>>>(tx, txs, static_cast<const uint8_t*>(packed), a);
+        pk::grouped_gemm_packed_kernel<false><<<pk::grid_ctas(), pk::kThreads, smem, s>>>(tx, txs, static_cast<const uint8_t*>(packed), a);
     }
     B200MOE_CUDA_TRY(cudaGetLastError());
     return B200MOE_OK;

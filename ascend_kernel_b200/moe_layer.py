@@ -328,7 +328,7 @@ class OverlappedSteps:
     ``exchange="p2p", exchange_buffers=2`` and the packed GEMMs."""
 
     def __init__(self, layer: "MoELayer", n_tokens: int, reserve_sms: int = 8, late_sum: bool = False,
-                 defer_sum: bool = False, yield_in: str = "gate_up"):
+                 defer_sum: bool = False):
         """``late_sum``: the end of a step -- the wait for the other ranks' pushes and the weighted sum -- also
         runs on the exchange stream, beside the NEXT step's gate/up GEMM, so the caller's stream goes from one
         step's down projection straight to the next step's gate/up GEMM and a slow peer's pushes are waited for
@@ -340,14 +340,7 @@ class OverlappedSteps:
         enqueued after the NEXT step's GEMMs, so the wait for the slowest peer's pushes finds them long done
         -- the ranks stop meeting at a barrier every step; steps then rotate over three buffer sets (the
         exchange of step k+2 must not wait for the sum of step k, which now comes after step k+1's GEMMs).
-        Results are complete by the handle's event, one ``submit`` (or ``flush``) later.
-        ``yield_in``: which GEMM gives up the ``reserve_sms`` SMs.  "gate_up": the gate/up GEMM always, the down
-        projection never.  "down": the gate/up GEMM only when that costs it no extra wave of tiles (its tiles
-        are 3.5 x as long as the down projection's, so a wave more of them is the dearer one), the down
-        projection always; the next step's exchange then starts beside whichever of the two has room first."""
-        if yield_in not in ("gate_up", "down"):
-            raise ValueError('yield_in must be "gate_up" or "down"')
-        self.yield_in = yield_in
+        Results are complete by the handle's event, one ``submit`` (or ``flush``) later."""
         if layer.px is None or layer.px.n_buffers < 2 or layer.gemm != "packed":
             raise RuntimeError('OverlappedSteps needs exchange="p2p", exchange_buffers=2 or 3 and the packed GEMMs')
         if late_sum and defer_sum:
@@ -438,19 +431,19 @@ class OverlappedSteps:
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if record else None
         if ev:
             ev[0].record()
-        down_yields = self.late_sum or self.yield_in == "down"
+        prev = ops.set_gemm_reserved_sms(self.reserve_sms)
         try:
-            ops.set_gemm_reserved_sms(self.reserve_sms, only_if_free=self.yield_in == "down")
             ops.grouped_gemm_packed(px.recv_x_sets[p], layer.w13, layer.s13, layer.o13, local_counts, st["act"],
                                     group_list_type=1, gate_up_silu=True)
             if ev:
                 ev[1].record()
                 ev[2].record()
-            ops.set_gemm_reserved_sms(self.reserve_sms if down_yields else 0)
+            if not self.late_sum:
+                ops.set_gemm_reserved_sms(prev)  # (defer_sum too: nothing runs beside the down projection)
             ops.grouped_gemm_packed_scatter(st["act"], layer.w2, layer.s2, layer.o2, local_counts,
                                             px.ret_code_sets[p], px.ret_ptrs_sets[p], px.cap_send, group_list_type=1)
         finally:
-            ops.set_gemm_reserved_sms(0)
+            ops.set_gemm_reserved_sms(prev)
         if ev:
             ev[3].record()
         layer.timing = ev

@@ -246,11 +246,10 @@ def grouped_gemm_packed(x, packed, scale, offset, group_list, output, group_list
     return ws if return_workspace else None
 
 
-def set_gemm_reserved_sms(n: int, only_if_free: bool = False) -> int:
-    """SMs the persistent packed-weight GEMM kernels leave free from now on (process-wide; 0 = none): always, or
-    with ``only_if_free`` only in launches whose tiles still take the same number of waves on the remaining
-    SMs.  Returns the previous number.  For callers that run other kernels beside a grouped GEMM."""
-    return int(_lib.b200moe_set_gemm_reserved_sms(int(n), 1 if only_if_free else 0))
+def set_gemm_reserved_sms(n: int) -> int:
+    """SMs the persistent packed-weight GEMM kernels leave free from now on (process-wide; 0 = none);
+    returns the previous value.  For callers that run other kernels beside a grouped GEMM."""
+    return int(_lib.b200moe_set_gemm_reserved_sms(int(n)))
 
 
 def grouped_gemm_packed_scatter(x, packed, scale, offset, group_list, row_code, dst_ptrs, dst_rows: int,

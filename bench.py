@@ -597,8 +597,7 @@ def run_ours(args):
             if i > 1 and layer.phases is not None:
                 phase_events.append(layer.phases)
         barrier()
-        ov = OverlappedSteps(layer, t_local, reserve_sms=args.reserve_sms, late_sum=args.late_sum, defer_sum=args.defer_sum,
-                             yield_in=args.yield_in)
+        ov = OverlappedSteps(layer, t_local, reserve_sms=args.reserve_sms, late_sum=args.late_sum, defer_sum=args.defer_sum)
 
     def one_step(record=False):
         if ov is not None:
@@ -708,7 +707,7 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16 x int8 -> fp32 accumulate", "data": "synthetic",
         "config": workload_config(world), "exchange": exchange, "exchange_status": exchange_status,
-        "exchange_overlapped": ({"reserved_sms": args.reserve_sms, "late_sum": args.late_sum, "defer_sum": args.defer_sum, "yield_in": args.yield_in, "phases_from": "serial passes before the timed region"}
+        "exchange_overlapped": ({"reserved_sms": args.reserve_sms, "late_sum": args.late_sum, "defer_sum": args.defer_sum, "phases_from": "serial passes before the timed region"}
                                 if ov is not None else False),
         "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps_in_flight": depth, "cuda_graph": graphed is not None,
@@ -773,8 +772,6 @@ def main():
                          "which puts the routing and row gather of a step beside the GEMMs of the step before")
     ap.add_argument("--no-overlap", action="store_true",
                     help="several ranks, p2p: run a step's token exchange serially before its GEMMs")
-    ap.add_argument("--yield-in", default="gate_up", choices=["gate_up", "down"],
-                    help="overlapped steps: the GEMM that gives up --reserve-sms SMs to the next step's exchange")
     ap.add_argument("--defer-sum", action="store_true",
                     help="overlapped steps: a step's wait for the peers' pushes and its weighted sum follow the NEXT "
                          "step's GEMMs on the same stream (three buffer sets): no barrier between the ranks every step")

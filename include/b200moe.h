@@ -146,13 +146,10 @@ int b200moe_grouped_gemm_int8_packed_scatter(const void* x, const void* packed, 
 /* Number of multiprocessors the persistent packed-weight GEMM kernels leave free (default 0: one CTA on
  * every SM).  For callers that run other kernels BESIDE a grouped GEMM -- the expert-parallel layer stores
  * the next step's tokens into their owners' memory on a second stream while the current step's GEMMs run;
- * a persistent CTA fills an SM's register file, so those kernels need SMs of their own.  The grid keeps one
- * CTA per SM; the last n CTAs leave at once, in the kernel, where the number of tiles is known -- always
- * (only_if_free = 0), or only when the remaining CTAs still finish the launch's tiles in the same number of
- * waves (only_if_free = 1: the SMs are then given up at no cost, or not at all).  Process-wide, takes effect
- * for launches made after the call; n is clamped to [0, SM count - 1].  Returns the previous n.
- * (No reference counterpart.) */
-int b200moe_set_gemm_reserved_sms(int n, int only_if_free);
+ * a persistent CTA fills an SM's register file, so those kernels need SMs of their own.  Process-wide,
+ * takes effect for launches made after the call; values outside [0, SM count - 1] are clamped.  Returns
+ * the previous value.  (No reference counterpart.) */
+int b200moe_set_gemm_reserved_sms(int n);
 
 /* Allocation-free int8 grouped GEMM.  (No counterpart in the reference: its host binding always
  * obtains a workspace with aclrtMalloc.)  For callers that must not allocate device memory -- a

@@ -138,8 +138,7 @@ def _rank_main(rank, world, port, q, cuda=False, case_kw=None, exchange="nccl", 
             ins = [tuple(t[rank * tl:(rank + 1) * tl].to(dev) for t in _step_inputs(c, step)) for step in range(steps)]
             torch.cuda.synchronize()
             # (the six-step test runs the late sum)
-            ov = OverlappedSteps(layer, tl, reserve_sms=8, late_sum=(steps % 2 == 0 and not defer), defer_sum=defer,
-                                 yield_in="down" if defer else "gate_up")
+            ov = OverlappedSteps(layer, tl, reserve_sms=8, late_sum=(steps % 2 == 0 and not defer), defer_sum=defer)
             res = [ov.submit(x, lg) for x, lg in ins]
             ov.drain()
             res = [h.out for h in res]
@@ -539,14 +538,14 @@ def test_overlapped_steps_single_rank_match_direct_path():
         ins.append((torch.roll(x, step, 0).cuda(), torch.roll(lg, 3 * step, 0).cuda()))
     want = [direct.forward(x, lg) for x, lg in ins]
     torch.cuda.synchronize()
-    for reserve, late, where in ((8, True, "gate_up"), (0, False, "gate_up"), (4, False, "down"), (8, True, "down")):
-        ov = OverlappedSteps(p2p, 200, reserve_sms=reserve, late_sum=late, yield_in=where)
+    for reserve, late in ((8, True), (0, False), (4, False), (8, True)):
+        ov = OverlappedSteps(p2p, 200, reserve_sms=reserve, late_sum=late)
         got = [ov.submit(x, lg) for x, lg in ins]
         assert all(h.event is not None for h in got[:-1]) and (got[-1].event is None) == late
         ov.drain()
         assert ops.set_gemm_reserved_sms(0) == 0          # restored after every step
         for step, (a, b) in enumerate(zip(want, got)):
-            assert torch.equal(a.view(torch.int16), b.out.view(torch.int16)), (reserve, late, where, step)
+            assert torch.equal(a.view(torch.int16), b.out.view(torch.int16)), (reserve, late, step)
     assert p2p.px.read_status()[0] == 0
     # the sum of a step deferred behind the next step's GEMMs: three buffer sets
     p3 = MoELayer(*w, c["E"], c["top_k"], exchange="p2p", max_tokens=200, exchange_buffers=3)
