@@ -707,6 +707,9 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16 x int8 -> fp32 accumulate", "data": "synthetic",
         "config": workload_config(world), "exchange": exchange, "exchange_status": exchange_status,
+        # what a step spends outside its two grouped GEMMs (routing, exchange, waits, weighted sum, launch gaps): with
+        # overlapped steps the exchange of phases_ms_rank0 is no longer part of it
+        "outside_gemm_ms_per_step_rank0": ms_per_step - gemm_ms_step,
         "exchange_overlapped": ({"reserved_sms": args.reserve_sms, "late_sum": args.late_sum, "defer_sum": args.defer_sum, "phases_from": "serial passes before the timed region"}
                                 if ov is not None else False),
         "e2e": {"value": T / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
