@@ -654,7 +654,8 @@ extern "C" int b200moe_pack_weight_int8(const void* weight, void* packed, int64_
 }
 
 static int packed_launch(const void* x, const void* packed, const void* scale, const void* offset,
-                         const int64_t* group_list, void* y, const int64_t* row_code, void* const* dst_base, int64_t n_base,
+                         const float* x_rowsum, const int64_t* group_list, void* y, const int64_t* row_code,
+                         void* const* dst_base, int64_t n_base,
                          int64_t dst_rows, int64_t M, int64_t K, int64_t N, int64_t G, int group_list_type, int gate_up_silu,
                          void* workspace, size_t workspace_bytes, void* stream) {
     if (group_list_type != B200MOE_GROUP_LIST_CUMSUM && group_list_type != B200MOE_GROUP_LIST_COUNTS)
@@ -693,11 +694,15 @@ static int packed_launch(const void* x, const void* packed, const void* scale, c
         }
     }
     if (offset != nullptr) {
-        float* rowsum = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + B200MOE_STATUS_BYTES);
-        launch_rowsum(x, rowsum, M, K, group_list, G, group_list_type, s);
-        B200MOE_CUDA_TRY(cudaGetLastError());
         a.offset = static_cast<const __nv_bfloat16*>(offset);
-        a.rowsum = rowsum;
+        if (x_rowsum != nullptr) {
+            a.rowsum = x_rowsum;  // the caller already has the fp32 sums of the rows of x (e.g. from the row gather)
+        } else {
+            float* rowsum = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + B200MOE_STATUS_BYTES);
+            launch_rowsum(x, rowsum, M, K, group_list, G, group_list_type, s);
+            B200MOE_CUDA_TRY(cudaGetLastError());
+            a.rowsum = rowsum;
+        }
     }
     CUtensorMap tx, txs;
     int rc = make_tensor_map_2d(&tx, x, 2, (uint64_t)M, (uint64_t)K, pk::kBigBox, pk::kBK, true);
@@ -723,8 +728,18 @@ extern "C" int b200moe_grouped_gemm_int8_packed(const void* x, const void* packe
                                                 const int64_t* group_list, void* y, int64_t M, int64_t K, int64_t N,
                                                 int64_t G, int group_list_type, int gate_up_silu, void* workspace,
                                                 size_t workspace_bytes, void* stream) {
-    return packed_launch(x, packed, scale, offset, group_list, y, nullptr, nullptr, 0, 0, M, K, N, G, group_list_type,
+    return packed_launch(x, packed, scale, offset, nullptr, group_list, y, nullptr, nullptr, 0, 0, M, K, N, G, group_list_type,
                          gate_up_silu, workspace, workspace_bytes, stream);
+}
+
+extern "C" int b200moe_grouped_gemm_int8_packed_rowsum(const void* x, const void* packed, const void* scale,
+                                                       const void* offset, const float* x_rowsum, const int64_t* group_list,
+                                                       void* y, int64_t M, int64_t K, int64_t N, int64_t G,
+                                                       int group_list_type, int gate_up_silu, void* workspace,
+                                                       size_t workspace_bytes, void* stream) {
+    if (offset != nullptr && x_rowsum == nullptr) return B200MOE_ERR_NULL_POINTER;
+    return packed_launch(x, packed, scale, offset, x_rowsum, group_list, y, nullptr, nullptr, 0, 0, M, K, N, G,
+                         group_list_type, gate_up_silu, workspace, workspace_bytes, stream);
 }
 
 extern "C" int b200moe_grouped_gemm_int8_packed_scatter(const void* x, const void* packed, const void* scale,
@@ -734,6 +749,6 @@ extern "C" int b200moe_grouped_gemm_int8_packed_scatter(const void* x, const voi
                                                         int group_list_type, void* workspace, size_t workspace_bytes,
                                                         void* stream) {
     if (row_code == nullptr) return B200MOE_ERR_NULL_POINTER;
-    return packed_launch(x, packed, scale, offset, group_list, nullptr, row_code, dst_base, n_base, dst_rows, M, K, N, G,
+    return packed_launch(x, packed, scale, offset, nullptr, group_list, nullptr, row_code, dst_base, n_base, dst_rows, M, K, N, G,
                          group_list_type, 0, workspace, workspace_bytes, stream);
 }

@@ -29,8 +29,13 @@ __global__ void silu_mul_kernel(const uint4* __restrict__ h, uint4* __restrict__
 // row is being copied: a copy kernel is bound by the bytes in flight, not by its instruction count.
 constexpr int kRowUnroll = 8;
 
+// kSum: also rowsum[i] = the fp32 sum of the row's elements, added up in the order of the grouped GEMM's own
+// row-sum kernel (a lane takes the 16-byte chunks lane, lane + 32, ...; low + high element of each 32-bit word;
+// then the xor-shuffle tree), so the bits are the ones that kernel would produce.
+template <bool kSum>
 __global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ index,
-                                                          uint4* __restrict__ dst, int width16, int n_rows) {
+                                                          uint4* __restrict__ dst, int width16, int n_rows,
+                                                          float* __restrict__ rowsum) {
     const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
     const int n_warps = gridDim.x * wpb;
     int row = blockIdx.x * wpb + (threadIdx.x >> 5);
@@ -40,14 +45,28 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restric
         uint4* d = dst + (long long)row * width16;
         const int next = row + n_warps;
         if (next < n_rows) from = __ldg(index + next);
+        float sum = 0.f;
         for (int c = lane; c < width16; c += 32 * kRowUnroll) {
             uint4 v[kRowUnroll];
 #pragma unroll
             for (int u = 0; u < kRowUnroll; ++u)
                 if (c + 32 * u < width16) v[u] = __ldg(s + c + 32 * u);
 #pragma unroll
-            for (int u = 0; u < kRowUnroll; ++u)
-                if (c + 32 * u < width16) d[c + 32 * u] = v[u];
+            for (int u = 0; u < kRowUnroll; ++u) {
+                if (c + 32 * u < width16) {
+                    d[c + 32 * u] = v[u];
+                    if constexpr (kSum) {
+                        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) sum += __uint_as_float(w[j] << 16) + __uint_as_float(w[j] & 0xFFFF0000u);
+                    }
+                }
+            }
+        }
+        if constexpr (kSum) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) rowsum[row] = sum;
         }
     }
 }
@@ -270,8 +289,21 @@ extern "C" int b200moe_gather_rows(const void* src, const int32_t* index, void* 
     if (!aligned16(src) || !aligned16(dst)) return B200MOE_ERR_ALIGNMENT;
     // eight warps per CTA, up to eight CTAs per SM: every warp copies a few rows
     const long long want = (n_rows + 7) / 8, cap = 8LL * sm_count();
-    gather_rows_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(src), index, static_cast<uint4*>(dst), (int)(width / 8), (int)n_rows);
+    gather_rows_kernel<false><<<(unsigned)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(src), index, static_cast<uint4*>(dst), (int)(width / 8), (int)n_rows, nullptr);
+    B200MOE_CUDA_TRY(cudaGetLastError());
+    return B200MOE_OK;
+}
+
+extern "C" int b200moe_gather_rows_sum(const void* src, const int32_t* index, void* dst, float* rowsum, int64_t n_rows,
+                                       int64_t width, void* stream) {
+    if (n_rows < 0 || width <= 0 || (width % 8) != 0 || n_rows > 0x7FFFFFFFLL) return B200MOE_ERR_SHAPE;
+    if (n_rows == 0) return B200MOE_OK;
+    if (!src || !index || !dst || !rowsum) return B200MOE_ERR_NULL_POINTER;
+    if (!aligned16(src) || !aligned16(dst)) return B200MOE_ERR_ALIGNMENT;
+    const long long want = (n_rows + 7) / 8, cap = 8LL * sm_count();
+    gather_rows_kernel<true><<<(unsigned)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(src), index, static_cast<uint4*>(dst), (int)(width / 8), (int)n_rows, rowsum);
     B200MOE_CUDA_TRY(cudaGetLastError());
     return B200MOE_OK;
 }

@@ -119,6 +119,7 @@ class MoELayer:
                                    n_buffers=exchange_buffers)
         elif exchange != "nccl":
             raise ValueError("exchange must be 'nccl' or 'p2p'")
+        self.gather_sums = True  # one rank: the row gather also produces the row sums of the gate/up GEMM
         self.timing = None  # [ev0..ev3] around GEMM1 / SiLU / GEMM2, filled by forward(record=True)
         self.phases = None  # [(name, event)] phase boundaries of the last forward(record=True)
         # called on the host when the rows of the step have been enqueued to reach their experts and the
@@ -142,12 +143,13 @@ class MoELayer:
         if self.mid_hook is not None:
             self.mid_hook()
 
-    def _experts(self, rows, counts, record, y=None, n_rows=None, scatter=None):
+    def _experts(self, rows, counts, record, y=None, n_rows=None, scatter=None, rows_sum=None):
         """rows [R, H] expert-major with per-local-expert counts -> [R, H] (into ``y`` when given).
         ``n_rows``: int64 device tensor with the number of rows in use when R is only a capacity.
         ``scatter`` = (row_code, destination pointers, destination rows): the down projection stores
         each result row where its code says (the return buffer of the rank the token came from) instead
-        of into ``y``; packed GEMMs only."""
+        of into ``y``; packed GEMMs only.  ``rows_sum``: fp32 sums of the rows when the caller has them (the
+        packed gate/up GEMM then skips its own pass over the rows)."""
         R = rows.shape[0]
         if y is None:
             y = torch.empty(R, self.hidden, dtype=torch.bfloat16, device=self.device)
@@ -175,7 +177,7 @@ class MoELayer:
         if self.gemm == "packed":
             act = torch.empty(R, self.inter, dtype=torch.bfloat16, device=self.device)
             ops.grouped_gemm_packed(rows, self.w13, self.s13, self.o13, counts, act, group_list_type=1,
-                                    gate_up_silu=True)
+                                    gate_up_silu=True, x_rowsum=rows_sum)
             if ev:
                 ev[1].record()
                 ev[2].record()
@@ -254,12 +256,19 @@ class MoELayer:
             mark("combine")
             self.phases = marks
             return out
-        send = self.ops.gather_rows(x, token_of)                 # [T*k, H] sorted by expert
+        # one rank on the packed GEMMs: the gather also adds up each row (the gate/up GEMM's offset term needs
+        # the sums and would otherwise read all rows once more)
+        sums = None
+        if (self.gather_sums and self.world == 1 and self.gemm == "packed" and self.o13 is not None
+                and self.ops is CudaRowOps):
+            send, sums = ops.gather_rows(x, token_of, with_sums=True)
+        else:
+            send = self.ops.gather_rows(x, token_of)             # [T*k, H] sorted by expert
         mark("route+gather")
 
         if self.world == 1:
             self._mid()
-            y = self._experts(send, counts, record)
+            y = self._experts(send, counts, record, rows_sum=sums)
             mark("experts")
             out = finish(y, slot, wts)
             mark("combine")

@@ -218,10 +218,14 @@ def pack_weight_int8(weight, gate_up: bool = False):
 
 
 def grouped_gemm_packed(x, packed, scale, offset, group_list, output, group_list_type: int = 0,
-                        gate_up_silu: bool = False, return_workspace: bool = False):
+                        gate_up_silu: bool = False, return_workspace: bool = False, x_rowsum=None):
     """int8 grouped GEMM on weights from :func:`pack_weight_int8`; ``scale`` / ``offset`` bf16 [G, N] in
-    the original column order.  ``gate_up_silu``: output [M, N/2] = bf16(silu(gate) * up)."""
-    _need_cuda(x=x, packed=packed, scale=scale, offset=offset, group_list=group_list, output=output)
+    the original column order.  ``gate_up_silu``: output [M, N/2] = bf16(silu(gate) * up).  ``x_rowsum``: fp32
+    [M] sums of the rows of x when the caller has them (``gather_rows(..., with_sums=True)``): the launch then
+    makes no pass of its own over x for the offset term."""
+    _need_cuda(x=x, packed=packed, scale=scale, offset=offset, group_list=group_list, output=output, x_rowsum=x_rowsum)
+    if x_rowsum is not None and (x_rowsum.dtype != torch.float32 or x_rowsum.numel() < x.shape[0]):
+        raise RuntimeError("x_rowsum must be float32 with one element per row of x")
     if x.dtype != torch.bfloat16 or output.dtype != torch.bfloat16 or group_list.dtype != torch.int64:
         raise RuntimeError("x and output must be bfloat16, group_list int64")
     if packed.dim() != 3 or packed.element_size() != 1:
@@ -237,12 +241,18 @@ def grouped_gemm_packed(x, packed, scale, offset, group_list, output, group_list
     need = _lib.b200moe_grouped_gemm_workspace_bytes(M, K, N, G, CT["int8"], LAYOUT["canonical"])
     ws = _workspace(need, x.device)
     with torch.cuda.device(x.device):
-        rc = _lib.b200moe_grouped_gemm_int8_packed(_ptr(x), _ptr(packed), _ptr(scale), _ptr(offset), _ptr(group_list),
-                                                   _ptr(output), M, K, N, G, group_list_type, int(bool(gate_up_silu)),
-                                                   _ptr(ws), need, _stream())
+        if x_rowsum is not None and offset is not None:
+            rc = _lib.b200moe_grouped_gemm_int8_packed_rowsum(_ptr(x), _ptr(packed), _ptr(scale), _ptr(offset),
+                                                              _ptr(x_rowsum), _ptr(group_list), _ptr(output), M, K, N, G,
+                                                              group_list_type, int(bool(gate_up_silu)), _ptr(ws), need,
+                                                              _stream())
+        else:
+            rc = _lib.b200moe_grouped_gemm_int8_packed(_ptr(x), _ptr(packed), _ptr(scale), _ptr(offset), _ptr(group_list),
+                                                       _ptr(output), M, K, N, G, group_list_type, int(bool(gate_up_silu)),
+                                                       _ptr(ws), need, _stream())
     _abi.check(rc, "grouped_gemm_packed")
     if M > 0:
-        _count(1 + (offset is not None))
+        _count(1 + (offset is not None and x_rowsum is None))
     return ws if return_workspace else None
 
 
@@ -385,17 +395,26 @@ def silu_mul(h, out=None):
     return out
 
 
-def gather_rows(src, index, out=None):
+def gather_rows(src, index, out=None, with_sums: bool = False):
+    """out[i, :] = src[index[i], :]; ``with_sums``: returns (out, fp32 [n] row sums of out) -- the sums the int8
+    grouped GEMMs need for their offset term, bit for bit."""
     _need_cuda(src=src, index=index, out=out)
     if index.dtype != torch.int32:
         raise RuntimeError("index must be int32")
     if out is None:
         out = torch.empty(index.numel(), src.shape[1], dtype=src.dtype, device=src.device)
     with torch.cuda.device(src.device):
-        rc = _lib.b200moe_gather_rows(_ptr(src), _ptr(index), _ptr(out), index.numel(), src.shape[1], _stream())
+        if with_sums:
+            if src.dtype != torch.bfloat16:
+                raise RuntimeError("row sums are defined for bfloat16 rows")
+            sums = torch.empty(index.numel(), dtype=torch.float32, device=src.device)
+            rc = _lib.b200moe_gather_rows_sum(_ptr(src), _ptr(index), _ptr(out), _ptr(sums), index.numel(), src.shape[1],
+                                              _stream())
+        else:
+            rc = _lib.b200moe_gather_rows(_ptr(src), _ptr(index), _ptr(out), index.numel(), src.shape[1], _stream())
     _abi.check(rc, "gather_rows")
     _count(1)
-    return out
+    return (out, sums) if with_sums else out
 
 
 def combine(y, slot, weight, out=None):

@@ -553,6 +553,7 @@ def run_ours(args):
     layer = MoELayer(c["w13"], c["s13"], c["o13"], c["w2"], c["s2"], c["o2"], E, CFG["top_k"], group,
                      exchange="p2p" if exchange == "p2p" else "nccl", max_tokens=t_local,
                      exchange_buffers=(3 if args.defer_sum else 2) if overlap else 1)
+    layer.gather_sums = not args.no_gather_sums
     x_host = c["x"][rank * t_local:(rank + 1) * t_local].contiguous().pin_memory()
     lg_host = c["logits"][rank * t_local:(rank + 1) * t_local].contiguous().pin_memory()
     x, lg = x_host.to(dev), lg_host.to(dev)
@@ -773,6 +774,8 @@ def main():
     ap.add_argument("--single-rank-exchange", action="store_true",
                     help="one GPU: run the peer-memory exchange kernels all the same (the rank is its own peer), "
                          "which puts the routing and row gather of a step beside the GEMMs of the step before")
+    ap.add_argument("--no-gather-sums", action="store_true",
+                    help="one GPU: the gate/up GEMM adds up the rows of x itself instead of taking the sums from the gather")
     ap.add_argument("--no-overlap", action="store_true",
                     help="several ranks, p2p: run a step's token exchange serially before its GEMMs")
     ap.add_argument("--defer-sum", action="store_true",

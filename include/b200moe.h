@@ -128,6 +128,13 @@ int b200moe_grouped_gemm_int8_packed(const void* x, const void* packed, const vo
                                      const int64_t* group_list, void* y, int64_t M, int64_t K, int64_t N, int64_t G,
                                      int group_list_type, int gate_up_silu, void* workspace, size_t workspace_bytes,
                                      void* stream);
+/* The same for a caller that already holds x_rowsum fp32 [M], the sum of each row of x (needed for the offset
+ * term; b200moe_gather_rows_sum produces it while it gathers the rows): the launch then makes no pass of its
+ * own over x.  x_rowsum may be NULL only when offset is.  (No reference counterpart.) */
+int b200moe_grouped_gemm_int8_packed_rowsum(const void* x, const void* packed, const void* scale, const void* offset,
+                                            const float* x_rowsum, const int64_t* group_list, void* y, int64_t M,
+                                            int64_t K, int64_t N, int64_t G, int group_list_type, int gate_up_silu,
+                                            void* workspace, size_t workspace_bytes, void* stream);
 
 /* b200moe_grouped_gemm_int8_packed (gate_up_silu == 0) whose result rows go where a table says instead of
  * into one [M, N] tensor (no reference counterpart; it is the down projection of an expert-parallel layer
@@ -230,6 +237,10 @@ int b200moe_silu_mul(const void* h, void* out, int64_t rows, int64_t inter, void
 /* dst[i, :] = src[index[i], :] for i < n_rows (bf16 rows of `width` elements, int32 index). */
 int b200moe_gather_rows(const void* src, const int32_t* index, void* dst, int64_t n_rows, int64_t width,
                         void* stream);
+/* The same, and rowsum[i] = the fp32 sum of row i's elements, bit for bit what the int8 grouped GEMMs compute for
+ * their offset term (b200moe_grouped_gemm_int8_packed_rowsum takes it and skips that pass over x). */
+int b200moe_gather_rows_sum(const void* src, const int32_t* index, void* dst, float* rowsum, int64_t n_rows,
+                            int64_t width, void* stream);
 /* out[t, :] = bf16( sum_j weight[t, j] * y[slot[t, j], :] ), y bf16 [*, width], slot int32 [T, top_k],
  * weight fp32 [T, top_k]; top_k <= 32. */
 int b200moe_combine(const void* y, const int32_t* slot, const float* weight, void* out, int64_t n_tokens,

@@ -114,3 +114,27 @@ def test_packed_scatter_stores_rows_where_the_codes_say():
     keep[5] = keep[9] = False
     written[base[keep], perm[keep]] = True
     assert bool((got[~written.cuda()].float() == SENTINEL).all())   # nothing else was touched
+
+
+@pytest.mark.parametrize("K,N", [(192, 256), (7168, 512)])
+def test_row_sums_from_the_gather_give_the_same_bits(K, N):
+    """gather_rows(with_sums=True) adds the rows up in the order of the GEMM's own row-sum pass: a packed GEMM that is
+    handed those sums returns exactly what it returns when it computes them itself."""
+    from ascend_kernel_b200 import ops
+
+    counts = [5, 0, 137, 33, 160, 1]
+    x, w, scale, offset, cnt = _int8_case(counts, K, N, 23, True)
+    src = torch.randn(50, K, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).cuda()
+    index = torch.randint(0, 50, (int(cnt.sum()),), generator=torch.Generator().manual_seed(6), dtype=torch.int32).cuda()
+    rows, sums = ops.gather_rows(src, index, with_sums=True)
+    assert torch.equal(rows, ops.gather_rows(src, index))
+    assert torch.allclose(sums.cpu(), rows.cpu().float().sum(1), rtol=1e-4, atol=1e-2)
+    wp = ops.pack_weight_int8(w.cuda())
+    a = torch.full((rows.shape[0], N), SENTINEL, dtype=torch.bfloat16, device="cuda")
+    b = torch.full_like(a, SENTINEL)
+    ops.grouped_gemm_packed(rows, wp, scale.cuda(), offset.cuda(), cnt.cuda(), a, group_list_type=1)
+    ops.grouped_gemm_packed(rows, wp, scale.cuda(), offset.cuda(), cnt.cuda(), b, group_list_type=1, x_rowsum=sums)
+    torch.cuda.synchronize()
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    gold = O.golden_f32(rows.cpu(), w, scale, offset, cnt, "int8", O.GROUP_LIST_COUNTS)
+    assert_close_to_golden(b, gold)
