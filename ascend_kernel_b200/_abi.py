@@ -43,7 +43,7 @@ class EpComm(ctypes.Structure):
                 ("peer_counts", ctypes.c_void_p * EP_MAX_WORLD), ("peer_signal", ctypes.c_void_p * EP_MAX_WORLD),
                 ("status", ctypes.c_void_p), ("step_counter", ctypes.c_void_p),
                 ("peer_ret", ctypes.c_void_p * EP_MAX_WORLD), ("peer_ret_code", ctypes.c_void_p * EP_MAX_WORLD),
-                ("cap_send", ctypes.c_int64)]
+                ("cap_send", ctypes.c_int64), ("peer_recv_sum", ctypes.c_void_p * EP_MAX_WORLD)]
 
 
 class B200MoeError(RuntimeError):

@@ -47,6 +47,7 @@ struct EpComm {
     int* status;                                       // local: two status words
     unsigned long long* step_counter;                  // local: the step number when the host passes 0
     long long* ret_code[B200MOE_EP_MAX_WORLD];         // optional: where each delivered row's result returns to
+    float* recv_sum[B200MOE_EP_MAX_WORLD];             // optional: fp32 sum of each delivered row, beside it
 };
 
 constexpr int kSigCounts = 0, kSigRows = 1, kSigResults = 2;
@@ -194,7 +195,21 @@ ep_dispatch_kernel(EpComm c, const uint4* __restrict__ x, const int32_t* __restr
         }
         const uint4* src = x + (long long)token_of[i] * c.width16;
         uint4* dst = c.recv_x[d] + pos * c.width16;
-        for (int v = lane; v < c.width16; v += 32) dst[v] = __ldg(src + v);
+        // the row's fp32 sum travels with it (the owner's gate/up GEMM needs it for the offset term): added up
+        // in the order of that GEMM's own row-sum pass, so the bits are the same
+        float sum = 0.f;
+        for (int v = lane; v < c.width16; v += 32) {
+            const uint4 q = __ldg(src + v);
+            dst[v] = q;
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sum += __uint_as_float(w[j] << 16) + __uint_as_float(w[j] & 0xFFFF0000u);
+        }
+        if (c.recv_sum[d] != nullptr) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) c.recv_sum[d][pos] = sum;
+        }
     }
     // completion: the last CTA to finish signals every rank
     __threadfence_system();
@@ -292,8 +307,12 @@ static int to_comm(const b200moe_ep_comm* h, EpComm* c) {
         c->counts[r] = h->peer_counts[r];
         c->signal[r] = reinterpret_cast<unsigned long long*>(h->peer_signal[r]);
         c->ret_code[r] = reinterpret_cast<long long*>(h->peer_ret_code[r]);
+        c->recv_sum[r] = h->peer_recv_sum[r];
     }
-    for (int r = h->world; r < B200MOE_EP_MAX_WORLD; ++r) c->ret_code[r] = nullptr;
+    for (int r = h->world; r < B200MOE_EP_MAX_WORLD; ++r) {
+        c->ret_code[r] = nullptr;
+        c->recv_sum[r] = nullptr;
+    }
     if (!h->status || !h->step_counter) return B200MOE_ERR_NULL_POINTER;
     c->status = h->status;
     c->step_counter = reinterpret_cast<unsigned long long*>(h->step_counter);

@@ -31,7 +31,7 @@ def _as_tensor(ptr: int, shape, dtype, device):
     """Zero-copy torch view of ``ptr`` (bf16 goes through int16: the interface has no bf16 code)."""
     if dtype == torch.bfloat16:
         return torch.as_tensor(_DeviceBuffer(ptr, shape, "<i2"), device=device).view(torch.bfloat16)
-    code = {torch.int32: "<i4", torch.int64: "<i8", torch.uint8: "|u1"}[dtype]
+    code = {torch.int32: "<i4", torch.int64: "<i8", torch.uint8: "|u1", torch.float32: "<f4"}[dtype]
     return torch.as_tensor(_DeviceBuffer(ptr, shape, code), device=device)
 
 
@@ -59,8 +59,9 @@ class PeerExchange:
         # bytes of ONE set; the sets of a doubled buffer follow one another in the same allocation
         one = {"recv_x": cap_rows * hidden * 2, "y": cap_rows * hidden * 2,
                "counts": -(-self.world * n_experts * 4 // 256) * 256, "signal": 3 * _abi.EP_MAX_WORLD * 8,
-               "ret": self.cap_send * hidden * 2, "ret_code": cap_rows * 8}
-        doubled = ("recv_x", "counts", "ret", "ret_code") if n_buffers > 1 else ()
+               "ret": self.cap_send * hidden * 2, "ret_code": cap_rows * 8,
+               "recv_sum": -(-cap_rows * 4 // 256) * 256}
+        doubled = ("recv_x", "counts", "ret", "ret_code", "recv_sum") if n_buffers > 1 else ()
         sizes = {name: nbytes * (n_buffers if name in doubled else 1) for name, nbytes in one.items()}
         self._own, handles = {}, {}
         with torch.cuda.device(self.device):
@@ -107,6 +108,7 @@ class PeerExchange:
                 c.peer_recv_x[r], c.peer_y[r] = at("recv_x", r, p), at("y", r, p)
                 c.peer_counts[r], c.peer_signal[r] = at("counts", r, p), at("signal", r, p)
                 c.peer_ret[r], c.peer_ret_code[r] = at("ret", r, p), at("ret_code", r, p)
+                c.peer_recv_sum[r] = at("recv_sum", r, p)
             c.cap_send = self.cap_send
             c.status = self.status.data_ptr()
             c.step_counter = self._step_dev.data_ptr()
@@ -123,6 +125,10 @@ class PeerExchange:
         self.ret_code_sets = [_as_tensor(at("ret_code", self.rank, p), (cap_rows,), torch.int64, self.device)
                               for p in range(n_buffers)]
         self.ret_ptrs_sets = [[at("ret", r, p) for r in range(self.world)] for p in range(n_buffers)]
+        # fp32 sum of every received row, stored by the sender beside the row
+        self.recv_sum_sets = [_as_tensor(at("recv_sum", self.rank, p), (cap_rows,), torch.float32, self.device)
+                              for p in range(n_buffers)]
+        self.recv_sum = self.recv_sum_sets[0]
         self.recv_x, self.ret, self.ret_code, self.ret_ptrs = (self.recv_x_sets[0], self.ret_sets[0],
                                                                self.ret_code_sets[0], self.ret_ptrs_sets[0])
 
@@ -217,7 +223,8 @@ class PeerExchange:
                 _lib.b200moe_ipc_close(p)
             self._opened = []
             self.recv_x = self.y = self.ret = self.ret_code = None
-            self.recv_x_sets = self.ret_sets = self.ret_code_sets = []
+            self.recv_x_sets = self.ret_sets = self.ret_code_sets = self.recv_sum_sets = []
+            self.recv_sum = None
             for name, p in list(self._own.items()):
                 _lib.b200moe_ipc_free(p)
             self._own = {}

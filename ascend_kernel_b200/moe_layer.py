@@ -243,7 +243,7 @@ class MoELayer:
                 # the down projection hands every result row straight back to the rank its token came from
                 # (stores over NVLink from the GEMM's epilogue); the weighted sum is then local
                 self._experts(px.recv_x, local_counts, record, y=px.y, n_rows=n_recv,
-                              scatter=(px.ret_code, px.ret_ptrs, px.cap_send))
+                              scatter=(px.ret_code, px.ret_ptrs, px.cap_send), rows_sum=px.recv_sum)
                 px.post(2)                                        # this rank's pushes are complete and visible
                 mark("experts")
                 px.wait(2)                                        # every owner has pushed this rank's rows
@@ -443,7 +443,7 @@ class OverlappedSteps:
         prev = ops.set_gemm_reserved_sms(self.reserve_sms)
         try:
             ops.grouped_gemm_packed(px.recv_x_sets[p], layer.w13, layer.s13, layer.o13, local_counts, st["act"],
-                                    group_list_type=1, gate_up_silu=True)
+                                    group_list_type=1, gate_up_silu=True, x_rowsum=px.recv_sum_sets[p])
             if ev:
                 ev[1].record()
                 ev[2].record()

@@ -301,6 +301,10 @@ typedef struct b200moe_ep_comm {
     void* peer_ret[B200MOE_EP_MAX_WORLD];
     int64_t* peer_ret_code[B200MOE_EP_MAX_WORLD];
     int64_t cap_send;
+    /* Optional (all NULL = not used): recv_sum fp32 [cap_rows] on every rank; b200moe_ep_dispatch stores the fp32 sum
+     * of every row it delivers at the row's position (the bits b200moe_grouped_gemm_int8_packed_rowsum wants as
+     * x_rowsum), so the owner's gate/up GEMM makes no pass of its own over the received rows. */
+    float* peer_recv_sum[B200MOE_EP_MAX_WORLD];
 } b200moe_ep_comm;
 enum { B200MOE_EP_SIG_COUNTS = 0, B200MOE_EP_SIG_ROWS = 1, B200MOE_EP_SIG_RESULTS = 2 };
 
