@@ -16,8 +16,12 @@ e // (E / world)).  Per step:
 
 With ``exchange="p2p"`` the two all-to-alls, the count exchange, the host read of the split sizes
 and the regroup passes are replaced by this package's exchange kernels (ep_exchange.py): rows are
-stored straight into the owner's receive buffer over NVLink, already expert-major, and the combine
-kernel loads result rows from the owners' buffers.  A step then has no host synchronisation.
+stored straight into the owner's receive buffer over NVLink, already expert-major, each with its
+fp32 sum beside it; the down projection's epilogue stores every result row into the return buffer of
+the rank the row came from, and the weighted sum is local.  A step then has no host synchronisation,
+and ``OverlappedSteps`` runs the exchange of one step beside the GEMMs of the step before.
+On one rank the row gather also adds up each row, so the gate/up GEMM makes no pass of its own over
+its input for the offset term.
 
 With the NCCL exchange, data from peers lands in this GPU's own memory (the NCCL receive buffer)
 before a kernel reads it.  torch is used for device memory, streams and the process group; routing, permutation
