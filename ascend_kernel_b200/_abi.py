@@ -22,7 +22,7 @@ STATUS_BYTES = 256
 EXPORTS = [
     "b200moe_grouped_gemm", "b200moe_grouped_gemm_workspace_bytes", "b200moe_grouped_gemv",
     "b200moe_grouped_gemv_workspace_bytes", "b200moe_fp4_dequant", "b200moe_fp4_layout", "b200moe_silu_mul",
-    "b200moe_gather_rows", "b200moe_gather_rows_sum", "b200moe_grouped_gemm_int8_packed_rowsum", "b200moe_combine", "b200moe_read_status", "b200moe_read_sticky_status", "b200moe_strerror", "b200moe_version",
+    "b200moe_ep_finish", "b200moe_gather_rows", "b200moe_gather_rows_sum", "b200moe_grouped_gemm_int8_packed_rowsum", "b200moe_combine", "b200moe_read_status", "b200moe_read_sticky_status", "b200moe_strerror", "b200moe_version",
     "b200moe_moe_route", "b200moe_moe_regroup_index", "b200moe_grouped_gemm_int8_noalloc", "b200moe_grouped_gemm_int8_noalloc_max_rows", "b200moe_noalloc_read_status",
     "b200moe_ep_post_counts", "b200moe_ep_dispatch", "b200moe_ep_wait", "b200moe_ep_post", "b200moe_ep_combine",
     "b200moe_fp4_dequant_bf16_scale", "b200moe_fp8_dequant", "b200moe_fp4_scale_fold",
@@ -114,6 +114,8 @@ def _load() -> ctypes.CDLL:
     lib.b200moe_ep_wait.argtypes = [comm, i32, u64, vp]
     lib.b200moe_ep_post.argtypes = [comm, i32, u64, vp]
     lib.b200moe_ep_combine.argtypes = [comm, vp, vp, vp, vp, i64, i64, u64, vp]
+    lib.b200moe_ep_finish.argtypes = [comm, vp, vp, vp, vp, i64, i64, u64, vp]
+    lib.b200moe_ep_finish.restype = i32
     lib.b200moe_silu_mul_dyn.argtypes = [vp, vp, vp, i64, vp]
     lib.b200moe_ipc_alloc.argtypes = [sz, ctypes.POINTER(vp), ctypes.c_char_p]
     lib.b200moe_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]

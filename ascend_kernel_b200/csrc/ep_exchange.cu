@@ -223,6 +223,50 @@ ep_dispatch_kernel(EpComm c, const uint4* __restrict__ x, const int32_t* __restr
     }
 }
 
+// The end of a step whose results were PUSHED to their source ranks, in one kernel: CTA 0 signals that this rank's
+// own pushes (made by an earlier kernel on the stream) are complete, every CTA waits for all ranks' signals, then
+// out[t, :] = bf16(sum_j weight[t, j] * ret[slot[t, j], :]) over this rank's own return buffer.  (Signal kernel,
+// wait kernel and weighted-sum kernel in one launch.)  An expired wait is recorded; the sum then runs over what
+// the buffer holds.
+__global__ void __launch_bounds__(256) ep_finish_kernel(EpComm c, const uint4* __restrict__ ret, const int32_t* __restrict__ slot,
+                                                        const float* __restrict__ weight, uint4* __restrict__ out, int top_k,
+                                                        unsigned long long step) {
+    step = ep_step(c, step);
+    if (blockIdx.x == 0) ep_signal_all(c, kSigResults, step);
+    (void)ep_wait_all(c, kSigResults, step, 3);
+    const long long t = blockIdx.x;
+    __shared__ long long s_off[32];
+    __shared__ float s_w[32];
+    if ((int)threadIdx.x < top_k) {
+        s_off[threadIdx.x] = (long long)slot[t * top_k + threadIdx.x] * c.width16;
+        s_w[threadIdx.x] = weight[t * top_k + threadIdx.x];
+    }
+    __syncthreads();
+    for (int v = threadIdx.x; v < c.width16; v += blockDim.x) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int j0 = 0; j0 < top_k; j0 += 8) {
+            uint4 q[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (j0 + j < top_k) q[j] = ret[s_off[j0 + j] + v];  // (plain loads: the rows were written by other GPUs)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (j0 + j < top_k) {
+                    const float w = s_w[j0 + j];
+                    const uint32_t vw[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        acc[2 * k] = fmaf(w, __uint_as_float(vw[k] << 16), acc[2 * k]);
+                        acc[2 * k + 1] = fmaf(w, __uint_as_float(vw[k] & 0xFFFF0000u), acc[2 * k + 1]);
+                    }
+                }
+            }
+        }
+        out[t * c.width16 + v] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                            pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+    }
+}
+
 // out[t, :] = bf16(sum_j weight[t, j] * result row of pair (t, j)), the row read from its owner.
 __global__ void ep_combine_kernel(EpComm c, const int32_t* __restrict__ remote_pos, const int32_t* __restrict__ slot,
                                   const float* __restrict__ weight, uint4* __restrict__ out, int top_k,
@@ -389,6 +433,20 @@ extern "C" int b200moe_ep_combine(const b200moe_ep_comm* comm, const int32_t* re
     }
     ep_combine_kernel<<<(unsigned)n_tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         c, remote_pos, slot, weight, static_cast<uint4*>(out), (int)top_k, (unsigned long long)step);
+    B200MOE_CUDA_TRY(cudaGetLastError());
+    return B200MOE_OK;
+}
+
+extern "C" int b200moe_ep_finish(const b200moe_ep_comm* comm, const void* ret, const int32_t* slot, const float* weight,
+                                 void* out, int64_t n_tokens, int64_t top_k, uint64_t step, void* stream) {
+    EpComm c;
+    int rc = to_comm(comm, &c);
+    if (rc != B200MOE_OK) return rc;
+    if (n_tokens <= 0 || top_k <= 0 || top_k > 32 || n_tokens > 0x7FFFFFFFLL) return B200MOE_ERR_SHAPE;
+    if (!ret || !slot || !weight || !out) return B200MOE_ERR_NULL_POINTER;
+    if (!aligned16(ret) || !aligned16(out)) return B200MOE_ERR_ALIGNMENT;
+    ep_finish_kernel<<<(unsigned)n_tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        c, static_cast<const uint4*>(ret), slot, weight, static_cast<uint4*>(out), (int)top_k, (unsigned long long)step);
     B200MOE_CUDA_TRY(cudaGetLastError());
     return B200MOE_OK;
 }

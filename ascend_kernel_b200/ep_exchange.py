@@ -199,6 +199,19 @@ class PeerExchange:
             _abi.check(_lib.b200moe_ep_post(ctypes.byref(self._comm), which, self._step_arg(step), self._s()), "ep_post")
         ops._count(1)
 
+    def finish(self, slot, weight, out=None, parity: int = 0, step: int = None):
+        """End of a step whose results were pushed: signals this rank's results, waits for every rank's, then sums
+        each token's rows of this rank's return buffer (set ``parity``) -- one launch."""
+        T, top_k = slot.shape
+        if out is None:
+            out = torch.empty(T, self.hidden, dtype=torch.bfloat16, device=self.device)
+        with torch.cuda.device(self.device):
+            _abi.check(_lib.b200moe_ep_finish(ctypes.byref(self._comms[parity]), self.ret_sets[parity].data_ptr(),
+                                              slot.data_ptr(), weight.data_ptr(), out.data_ptr(), T, top_k,
+                                              self._step_arg(step), self._s()), "ep_finish")
+        ops._count(1)
+        return out
+
     def combine(self, remote_pos, slot, weight, out=None):
         T, top_k = slot.shape
         if out is None:

@@ -248,10 +248,14 @@ class MoELayer:
                 # (stores over NVLink from the GEMM's epilogue); the weighted sum is then local
                 self._experts(px.recv_x, local_counts, record, y=px.y, n_rows=n_recv,
                               scatter=(px.ret_code, px.ret_ptrs, px.cap_send), rows_sum=px.recv_sum)
-                px.post(2)                                        # this rank's pushes are complete and visible
                 mark("experts")
-                px.wait(2)                                        # every owner has pushed this rank's rows
-                out = finish(px.ret, slot, wts)
+                if out_host is None and x.shape[0] > 0:
+                    # one launch: signal this rank's pushes, wait for every owner's, sum each token's rows
+                    out = px.finish(slot, wts)
+                else:
+                    px.post(2)                                    # this rank's pushes are complete and visible
+                    px.wait(2)                                    # every owner has pushed this rank's rows
+                    out = finish(px.ret, slot, wts)
             else:
                 self._experts(px.recv_x, local_counts, record, y=px.y, n_rows=n_recv)
                 px.post(2)                                        # results of this rank are complete
@@ -460,9 +464,9 @@ class OverlappedSteps:
         if ev:
             ev[3].record()
         layer.timing = ev
-        px.post(2, step=step)                # this rank's pushes are complete and visible
         handle = StepResult(out)
         if self.late_sum or self.defer_sum:
+            px.post(2, step=step)            # this rank's pushes are complete and visible
             posted = torch.cuda.Event()
             posted.record(main)
             if self.defer_sum:
@@ -471,10 +475,10 @@ class OverlappedSteps:
             if self.late_sum:
                 st["done"] = None            # the exchange stream itself orders the sets' reuse
             return handle
-        px.wait(2, step=step)                # every owner has pushed this rank's rows
         if out_free is not None:
             main.wait_event(out_free)
-        handle.out = layer.ops.combine(px.ret_sets[p], slot, wts) if out is None else layer.ops.combine(px.ret_sets[p], slot, wts, out)
+        # one launch: signal this rank's pushes, wait for every owner's, sum each token's rows
+        handle.out = px.finish(slot, wts, out=out, parity=p, step=step)
         st["done"] = torch.cuda.Event()
         st["done"].record(main)
         handle.event = st["done"]

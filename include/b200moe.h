@@ -323,6 +323,13 @@ int b200moe_ep_dispatch(const b200moe_ep_comm* comm, const void* x, const int32_
 int b200moe_ep_wait(const b200moe_ep_comm* comm, int which, uint64_t step, void* stream);
 /* Signals `which` for `step` to every rank (everything this stream wrote before is visible first). */
 int b200moe_ep_post(const b200moe_ep_comm* comm, int which, uint64_t step, void* stream);
+/* The end of a step whose results were pushed (b200moe_grouped_gemm_int8_packed_scatter), in one launch: signals
+ * this rank's results for `step` (its pushes, made earlier on the stream, are complete), waits for every rank's
+ * results signal, then out[t, :] = bf16(sum_j weight[t, j] * ret[slot[t, j], :]) over this rank's own return
+ * buffer `ret` -- b200moe_ep_post + b200moe_ep_wait + b200moe_combine.  n_tokens >= 1 (the launch carries the
+ * signal), top_k <= 32. */
+int b200moe_ep_finish(const b200moe_ep_comm* comm, const void* ret, const int32_t* slot, const float* weight, void* out,
+                      int64_t n_tokens, int64_t top_k, uint64_t step, void* stream);
 /* Waits for every rank's results signal, then out[t, :] = bf16(sum_j weight[t, j] * y_owner[pos, :])
  * with (owner, pos) = remote_pos[slot[t, j]]. */
 int b200moe_ep_combine(const b200moe_ep_comm* comm, const int32_t* remote_pos, const int32_t* slot,
