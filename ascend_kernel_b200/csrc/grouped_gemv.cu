@@ -28,7 +28,7 @@ constexpr int kGvIterRows = kGvWarps * kGvWarpRows;     // k rows a CTA consumes
 constexpr int kGvRows = 4;                              // x rows per pass
 constexpr int kGvXPad = 16;                             // bf16 elements between staged x rows (bank spread)
 constexpr int kGvMmaParts = 4;                          // k groups of the tensor-core path
-constexpr int kGvL2Steps = 6;                           // steps a warp requests into L2 ahead of its register loads
+constexpr int kGvL2Steps = 4;                           // steps a warp requests into L2 ahead of its register loads
 
 struct GemvArgs {
     const __nv_bfloat16* x;
