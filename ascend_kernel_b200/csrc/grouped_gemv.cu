@@ -605,7 +605,7 @@ __device__ __forceinline__ void mma_16816_f16_zero(float (&d)[4], uint32_t a0, u
 
 constexpr int kGvFp4Ahead = 4;  // steps whose loads are in flight per warp (6: slower, measured)
 
-constexpr int kGvFp4L2Ahead = 3;  // batches of kGvFp4Ahead steps requested into L2 before their loads are issued
+constexpr int kGvFp4L2Ahead = 1;  // batches of kGvFp4Ahead steps requested into L2 before their loads are issued
 
 template <bool kStored>
 __device__ __forceinline__ void gv_compute_fp4_mma(const GemvArgs& a, const __half* xs, const int* xexp, float* red,
