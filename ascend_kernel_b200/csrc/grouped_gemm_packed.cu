@@ -59,7 +59,7 @@ constexpr int kThreads = 896;
 constexpr int kWarpProd = 0, kWarpMma = 2, kWarpEpi0 = 4, kEpiWarps = 8, kWarpDq0 = 12;
 constexpr int kDqGroups = 2, kDqGroupWarps = 8;
 constexpr int kPrefetch = 2;    // packed stages a dequant thread holds in registers ahead of the conversion
-constexpr int kL2Ahead = 8;     // stages by which the L2 prefetch of packed weights leads the x loads
+constexpr int kL2Ahead = 4;     // stages by which the L2 prefetch of packed weights leads the x loads
 constexpr int kSuperRows = 8;   // m-tiles per L2 super-tile
 constexpr int kTileRing = 32;
 constexpr int kXSlotBytes = kMaxR * kBK * 2;  // 20 KB, a multiple of 1024
